@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the JSON parse + validate path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--records R] [--impl reference]
+
+One step = one pass of the hot path (record index, validation, typed-column emission) over one batch
+of synthetic Petstore `Pet` records held as NDJSON: R = 1,000,000 records per GPU (~292 MB, the
+single-GPU benchmark configuration), regenerated from a fixed seed on every run.
+
+  value       records/s with the input already resident in HBM and the columns left in HBM
+  e2e         the same through the host-buffer route of the C ABI: pinned host text in, every column
+              copied back to pinned host memory, both inside the timed region
+  roofline    algorithmic bytes (input + every produced column) / device time, against the measured
+              HBM copy bandwidth of this pool's B200s
+  reserialise the reverse direction (columns -> JSON) on the parsed columns, reported beside it
+  cpu_baseline the CPU restatement of the reference path (oracle/) on this box's host cores; the JVM
+              reference itself cannot run here
+
+`--impl reference` times only that CPU restatement, on all host threads, and prints the same line
+shape. With N > 1 (torchrun) every rank parses its own byte-range shard, takes the head of the next
+rank's shard as slack over NCCL and all-gathers its counters; timing is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures as cf
+import ctypes as C
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED = 0x5EED
+SLACK = 64 * 1024
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- CPU restatement of the reference path (oracle/) -------------------------------------------------
+class CpuPort:
+    """The scalar C restatement, run on T host threads over LF-aligned byte ranges of the sample."""
+
+    def __init__(self):
+        build = importlib.import_module("micronaut3-bug_b200.build")
+        self.abi = importlib.import_module("micronaut3-bug_b200.abi")
+        self.lib = C.CDLL(build.build_oracle())
+
+    def parse_ranges(self, text: np.ndarray, threads: int) -> tuple[int, float]:
+        abi = self.abi
+        cuts = [0]
+        for t in range(1, threads):
+            p = text.size * t // threads
+            nl = np.nonzero(text[p:p + 100000] == 10)[0]
+            cuts.append(p + int(nl[0]) + 1 if nl.size else text.size)
+        cuts.append(text.size)
+        parts = [text[cuts[i]:cuts[i + 1]] for i in range(threads) if cuts[i + 1] > cuts[i]]
+        outs = [abi.HostColumns(abi.PJ_SCHEMA_PET, abi.default_caps(abi.PJ_SCHEMA_PET, int(np.count_nonzero(p == 10)) + 2, p.size, p.size // 20)) for p in parts]
+
+        def run(i):
+            p = parts[i]
+            st = self.lib.pjo_parse(C.c_uint32(abi.PJ_SCHEMA_PET), C.c_uint32(0), C.c_void_p(p.ctypes.data), C.c_uint64(p.size), C.c_uint64(0), 1, 1,
+                                    C.c_uint64(0), C.byref(outs[i].raw))
+            assert st == 0
+            return outs[i].n_records
+
+        t0 = time.perf_counter()
+        with cf.ThreadPoolExecutor(max_workers=len(parts)) as ex:
+            n = sum(ex.map(run, range(len(parts))))
+        return n, time.perf_counter() - t0
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args, pj, abi):
+    """`--impl reference`: the CPU restatement on all host threads; each step parses a bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = host_threads()
+    sample = min(args.records, 200_000)
+    text = pj.gen_text(abi.PJ_SCHEMA_PET, SEED, 0, sample, 0)
+    port = CpuPort()
+    for _ in range(args.warmup):
+        port.parse_ranges(text, threads)
+    total_t, total_n = 0.0, 0
+    for _ in range(args.steps):
+        n, dt = port.parse_ranges(text, threads)
+        total_t += dt; total_n += n
+    rps = total_n / total_t
+    line = {
+        "impl": "reference", "metric": "pet_ndjson_parse_validate_records_per_s", "value": rps, "unit": "records/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_t / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "1M Pet records as NDJSON, one record per line (BASELINE configs[1])", "records_per_gpu": args.records,
+                   "seed": SEED, "sample_records_per_step": sample},
+        "gb_per_s": rps * text.size / sample / 1e9,
+        "cpu_baseline": {"value": rps, "unit": "records/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample} Pet records ({text.size / 1e6:.1f} MB) per step, split into {threads} LF-aligned ranges, one thread each; "
+                                   "CPU restatement in C (oracle/), not the JVM reference, which cannot run on this box"},
+        "e2e": {"value": rps, "unit": "records/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--records", type=int, default=1_000_000, help="records per GPU and step")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    pj = importlib.import_module("micronaut3-bug_b200")
+    abi = pj.abi
+    importlib.import_module("micronaut3-bug_b200.build").build_library()  # no-op when the .so is up to date
+    if args.impl == "reference":
+        return run_reference(args, pj, abi)
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; there is no CPU fallback for the product path (use --impl reference)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    R = args.records
+    PET = abi.PJ_SCHEMA_PET
+
+    # ---- workload: this rank's byte range of the stream = its R records ------------------------------
+    text_np = pj.gen_text(PET, SEED, rank * R, R, 0)
+    nbytes = int(text_np.size)
+    h_text = torch.empty(nbytes + SLACK, dtype=torch.uint8).pin_memory()
+    h_text[:nbytes].copy_(torch.from_numpy(text_np))
+    d_text = torch.zeros(nbytes + SLACK, dtype=torch.uint8, device=dev)
+    d_text[:nbytes].copy_(h_text[:nbytes], non_blocking=True)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream(device=dev)  # the library launches on this stream; the timing events are recorded on it
+    torch.cuda.set_stream(stream)
+    ctx = pj.Context(device=local, inclusion=abi.PJ_INCLUDE_NON_NULL, stream=stream.cuda_stream)
+    cols = pj.DeviceColumns.sized_for(PET, R + 16, nbytes + SLACK, 6 * R, dev)
+    sharded = None
+    if world > 1:
+        sharded = importlib.import_module("micronaut3-bug_b200.sharded").ShardedParser(ctx, PET, SLACK)
+    torch.cuda.synchronize()
+
+    def step_device():
+        if sharded:
+            return sharded.parse(d_text, nbytes, cols)
+        ctx.parse(PET, d_text[:nbytes], cols)
+        return None
+
+    launches = 0
+    stage_ms = np.zeros(8)
+    for _ in range(args.warmup):
+        step_device()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dev_ms = 0.0
+    stitch_ms = 0.0
+    e0.record(stream)
+    for _ in range(args.steps):
+        info = step_device()
+        st = ctx.stats()
+        launches += st.kernel_launches
+        dev_ms += st.device_ms
+        stage_ms += np.array(list(st.stage_ms))
+        if info:
+            stitch_ms += info["stitch_ms"]
+    e1.record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    n_rec = cols.n_records
+    alg_bytes = ctx.stats().algorithmic_bytes
+    if world > 1:
+        t = torch.tensor([ms, dev_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, dev_ms = float(t[0]), float(t[1])
+        cnt = torch.tensor([n_rec, launches], device=dev, dtype=torch.int64)
+        dist.all_reduce(cnt)
+        total_rec, launches = int(cnt[0]), int(cnt[1])
+    else:
+        total_rec = n_rec
+    if not sharded:
+        assert n_rec == R and cols.n_errors == 0, (n_rec, cols.n_errors)
+
+    # ---- the reverse direction on the parsed columns ------------------------------------------------------
+    d_out = torch.empty(nbytes + 64, dtype=torch.uint8, device=dev)
+    w_ms, w_dev_ms, w_launch, w_alg, w_len = 0.0, 0.0, 0, 0, 0
+    wsteps = max(3, args.steps // 2)
+    if not sharded:
+        for _ in range(3):
+            ctx.write(PET, cols, d_out)
+        torch.cuda.synchronize()
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0.record(stream)
+        for _ in range(wsteps):
+            w_len = ctx.write(PET, cols, d_out)
+            st = ctx.stats()
+            w_dev_ms += st.device_ms; w_launch += st.kernel_launches; w_alg = st.algorithmic_bytes
+        w1.record(stream)
+        torch.cuda.synchronize()
+        w_ms = w0.elapsed_time(w1)
+        assert w_len == nbytes and torch.equal(d_out[:nbytes], d_text[:nbytes]), "re-serialised bytes differ from the input"
+
+    # ---- end to end through host buffers ------------------------------------------------------------------
+    e2e = None
+    if not args.no_e2e and not sharded:
+        pin = lambda n: torch.empty(n, dtype=torch.uint8).pin_memory().numpy()
+        caps = {c.id: int(cols.raw.col[c.id].bytes) for c in abi.schema_columns(PET)}
+        hcols = abi.HostColumns(PET, {k: min(v, max(cols.count(k) * 8 + 64, 64)) for k, v in caps.items()}, alloc=pin)
+        h_np = h_text.numpy()[:nbytes]
+        for _ in range(2):
+            ctx.parse(PET, h_np, hcols)
+        torch.cuda.synchronize()
+        esteps = max(3, args.steps // 4)
+        t0 = time.perf_counter()
+        for _ in range(esteps):
+            ctx.parse(PET, h_np, hcols)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        st = ctx.stats()
+        assert hcols.n_records == R
+        e2e = {"value": R * esteps / dt, "unit": "records/s", "h2d_bytes_per_step": int(st.h2d_bytes), "d2h_bytes_per_step": int(st.d2h_bytes),
+               "ms_per_step": 1e3 * dt / esteps, "steps": esteps}
+    elif sharded:
+        e2e = {"value": None, "unit": "records/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0, "note": "host-buffer route measured at N=1 only"}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peak()
+    step_dev_ms = dev_ms / args.steps
+    achieved = alg_bytes / (step_dev_ms * 1e-3) / 1e9
+    line = {
+        "metric": "pet_ndjson_parse_validate_records_per_s",
+        "value": total_rec * args.steps / (ms * 1e-3),
+        "unit": "records/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "u8",
+        "data": "synthetic",
+        "config": {"workload": "1M Pet records as NDJSON, one record per line (BASELINE configs[1])", "records_per_gpu": R, "seed": SEED,
+                   "input_bytes_per_gpu": nbytes, "l2": "input (292 MB at 1M records) and columns are larger than the 126 MB L2; no flush between steps",
+                   "sharding": "one byte range per GPU, 64 KiB slack from the next rank, counters all-gathered" if world > 1 else "single GPU"},
+        "gb_per_s": total_rec * args.steps / (ms * 1e-3) * nbytes / R / 1e9,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src + " HBM copy bandwidth", "kernel": "whole parse pipeline (all launches of one step)",
+                     "algorithmic_bytes_per_step": int(alg_bytes), "device_ms_per_step": step_dev_ms,
+                     "stage_ms_per_step": {"index": stage_ms[0] / args.steps, "size_pass": stage_ms[1] / args.steps, "scans": stage_ms[2] / args.steps,
+                                           "emit_pass": stage_ms[3] / args.steps, "closing": stage_ms[4] / args.steps}},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "e2e": e2e,
+    }
+    if sharded:
+        line["stitch_ms_per_step"] = stitch_ms / args.steps
+    if w_ms:
+        wa = w_alg / (w_dev_ms / wsteps * 1e-3) / 1e9
+        line["reserialise"] = {"records_per_s": R * wsteps / (w_ms * 1e-3), "gb_per_s_out": nbytes * wsteps / (w_ms * 1e-3) / 1e9, "ms_per_step": w_ms / wsteps,
+                               "steps": wsteps, "gpu_launches": w_launch, "byte_identical_to_input": True,
+                               "roofline": {"bound": "hbm", "achieved": wa, "peak": peak, "unit": "GB/s", "frac": wa / peak, "traffic": None,
+                                            "algorithmic_bytes_per_step": int(w_alg)}}
+    if not args.no_cpu_baseline:
+        threads = host_threads()
+        sample = min(R, 200_000)
+        port = CpuPort()
+        sample_text = text_np[: int(np.nonzero(text_np == 10)[0][sample - 1]) + 1]
+        port.parse_ranges(sample_text, threads)
+        reps, tot = 0, 0.0
+        while tot < 10.0 and reps < 20:
+            n, dt = port.parse_ranges(sample_text, threads)
+            tot += dt; reps += 1
+        n1, dt1 = port.parse_ranges(sample_text, 1)
+        line["cpu_baseline"] = {"value": sample * reps / tot, "unit": "records/s", "cores": threads, "kind": "port",
+                                "single_thread_records_per_s": n1 / dt1,
+                                "sample": f"{sample} Pet records ({sample_text.size / 1e6:.1f} MB) x {reps} passes, {threads} LF-aligned ranges, one thread each; "
+                                          "CPU restatement in C (oracle/), not the JVM reference, which cannot run on this box"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -255,6 +255,10 @@ typedef struct pj_call_stats {
   uint32_t reserved;
   float device_ms;          /* CUDA-event time from first launch to last, on the call's stream  */
   float main_kernel_ms;     /* CUDA-event time of the dominant kernel(s) of the call            */
+  float stage_ms[8];        /* CUDA-event time per stage. parse: [0] record index, [1] size pass,
+                               [2] counter scans, [3] emit pass, [4] closing offsets;
+                               write: [0] size pass, [1] scan, [2] emit pass                     */
+  uint32_t stage_launches[8]; /* kernels launched per stage                                      */
   uint64_t h2d_bytes;       /* bytes copied host->device by the call                            */
   uint64_t d2h_bytes;       /* bytes copied device->host by the call                            */
   uint64_t algorithmic_bytes; /* input bytes + bytes of every produced column (parse), or column
@@ -290,7 +294,9 @@ pj_status pj_columns_sizes(uint32_t schema, uint64_t max_records, uint64_t max_i
 /* Replaces ObjectMapper#readValue (MyEntityConfig.java:34) for a whole batch of records.
  * `in` is `len` bytes of JSON in host or device memory (`in_kind`); `out` carries the caller's
  * buffers (all in out->mem_kind memory). Columns of other schemas are ignored; a column of this
- * schema with ptr == NULL is a capacity error. len must be < 4 GiB. */
+ * schema with ptr == NULL is PJ_ERR_ARG. When the record count itself exceeds the per-record
+ * buffers, only n_records and the per-record counts are exact in the PJ_ERR_CAPACITY answer.
+ * len must be < 4 GiB. */
 pj_status pj_parse(pj_ctx* ctx, uint32_t schema, uint32_t framing, const uint8_t* in,
                    uint64_t len, uint32_t in_kind, pj_columns* out);
 

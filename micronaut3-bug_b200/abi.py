@@ -123,14 +123,16 @@ class pj_options(C.Structure):
 
 class pj_call_stats(C.Structure):
     _fields_ = [("kernel_launches", C.c_uint32), ("reserved", C.c_uint32), ("device_ms", C.c_float),
-                ("main_kernel_ms", C.c_float), ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
+                ("main_kernel_ms", C.c_float), ("stage_ms", C.c_float * 8), ("stage_launches", C.c_uint32 * 8),
+                ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
                 ("algorithmic_bytes", C.c_uint64)]
 
 
 class HostColumns:
     """A pj_columns whose buffers are numpy arrays in host memory."""
 
-    def __init__(self, schema: int, byte_caps: dict[int, int]):
+    def __init__(self, schema: int, byte_caps: dict[int, int], alloc=None):
+        """`alloc(nbytes)` may supply the uint8 arrays (e.g. views of pinned memory); default: np.zeros."""
         self.schema = schema
         self.raw = pj_columns()
         self.raw.schema = schema
@@ -138,7 +140,7 @@ class HostColumns:
         self.arrays: dict[int, np.ndarray] = {}
         for c in schema_columns(schema):
             nbytes = max(int(byte_caps.get(c.id, 0)), 16)
-            a = np.zeros(nbytes, dtype=np.uint8)
+            a = alloc(nbytes) if alloc else np.zeros(nbytes, dtype=np.uint8)
             self.arrays[c.id] = a
             self.raw.col[c.id].ptr = a.ctypes.data
             self.raw.col[c.id].bytes = nbytes

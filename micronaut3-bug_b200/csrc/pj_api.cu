@@ -1,0 +1,611 @@
+/*
+ * pj_api.cu — the C ABI of libpetjson.so (declared in include/petjson.h): argument checking,
+ * staging of host buffers, scratch management and the launch sequence of the kernels.
+ *
+ * There is deliberately no CPU path: without a CUDA device pj_create fails with PJ_ERR_CUDA.
+ */
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "petjson.h"
+#include "pj_kernels.cuh"
+
+using namespace pj;
+
+namespace {
+
+thread_local char g_create_error[256] = "";
+
+struct ColInfo { const char* name; uint8_t elem, owner; };
+/* name, element width, owning model (PJ_TYPE_*, 0 = per record) of every column id */
+const ColInfo* col_info(int col) {
+  static ColInfo t[PJ_MAX_COLS];
+  static bool init = false;
+  if (!init) {
+    auto set = [&](int id, const char* n, int e, int o) { t[id].name = n; t[id].elem = (uint8_t)e; t[id].owner = (uint8_t)o; };
+    set(PJ_COL_REC_START, "rec_start", 8, 0); set(PJ_COL_ERR_KIND, "err_kind", 1, 0); set(PJ_COL_ERR_OFF, "err_off", 4, 0);
+    set(PJ_COL_REC_TYPE, "rec_type", 1, 0); set(PJ_COL_REC_ROW, "rec_row", 4, 0);
+    set(PJ_COL_PET_PRESENT, "pet_present", 1, 1); set(PJ_COL_PET_ID, "pet_id", 8, 1);
+    set(PJ_COL_PET_CAT_PRESENT, "pet_cat_present", 1, 1); set(PJ_COL_PET_CAT_ID, "pet_cat_id", 8, 1);
+    set(PJ_COL_PET_CAT_NAME_OFF, "pet_cat_name_off", 4, 1); set(PJ_COL_PET_CAT_NAME_DATA, "pet_cat_name_data", 1, 1);
+    set(PJ_COL_PET_NAME_OFF, "pet_name_off", 4, 1); set(PJ_COL_PET_NAME_DATA, "pet_name_data", 1, 1);
+    set(PJ_COL_PET_PHOTO_OFF, "pet_photo_off", 4, 1); set(PJ_COL_PET_PHOTO_STR_OFF, "pet_photo_str_off", 4, 1);
+    set(PJ_COL_PET_PHOTO_DATA, "pet_photo_data", 1, 1); set(PJ_COL_PET_TAGS_OFF, "pet_tags_off", 4, 1);
+    set(PJ_COL_PET_TAG_PRESENT, "pet_tag_present", 1, 1); set(PJ_COL_PET_TAG_ID, "pet_tag_id", 8, 1);
+    set(PJ_COL_PET_TAG_NAME_OFF, "pet_tag_name_off", 4, 1); set(PJ_COL_PET_TAG_NAME_DATA, "pet_tag_name_data", 1, 1);
+    set(PJ_COL_PET_STATUS, "pet_status", 1, 1);
+    set(PJ_COL_ORD_PRESENT, "ord_present", 1, 2); set(PJ_COL_ORD_ID, "ord_id", 8, 2); set(PJ_COL_ORD_PET_ID, "ord_pet_id", 8, 2);
+    set(PJ_COL_ORD_QUANTITY, "ord_quantity", 4, 2); set(PJ_COL_ORD_SHIP_EPOCH, "ord_ship_epoch", 8, 2);
+    set(PJ_COL_ORD_SHIP_NANOS, "ord_ship_nanos", 4, 2); set(PJ_COL_ORD_SHIP_OFFSET, "ord_ship_offset", 4, 2);
+    set(PJ_COL_ORD_STATUS, "ord_status", 1, 2); set(PJ_COL_ORD_COMPLETE, "ord_complete", 1, 2);
+    set(PJ_COL_USR_PRESENT, "usr_present", 1, 3); set(PJ_COL_USR_ID, "usr_id", 8, 3);
+    set(PJ_COL_USR_USERNAME_OFF, "usr_username_off", 4, 3); set(PJ_COL_USR_USERNAME_DATA, "usr_username_data", 1, 3);
+    set(PJ_COL_USR_FIRSTNAME_OFF, "usr_firstname_off", 4, 3); set(PJ_COL_USR_FIRSTNAME_DATA, "usr_firstname_data", 1, 3);
+    set(PJ_COL_USR_LASTNAME_OFF, "usr_lastname_off", 4, 3); set(PJ_COL_USR_LASTNAME_DATA, "usr_lastname_data", 1, 3);
+    set(PJ_COL_USR_EMAIL_OFF, "usr_email_off", 4, 3); set(PJ_COL_USR_EMAIL_DATA, "usr_email_data", 1, 3);
+    set(PJ_COL_USR_PASSWORD_OFF, "usr_password_off", 4, 3); set(PJ_COL_USR_PASSWORD_DATA, "usr_password_data", 1, 3);
+    set(PJ_COL_USR_PHONE_OFF, "usr_phone_off", 4, 3); set(PJ_COL_USR_PHONE_DATA, "usr_phone_data", 1, 3);
+    set(PJ_COL_USR_STATUS, "usr_status", 4, 3);
+    init = true;
+  }
+  if (col < 0 || col >= PJ_MAX_COLS || !t[col].name) return nullptr;
+  return &t[col];
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) changed = cudaSetDevice(dev) == cudaSuccess;
+  }
+  ~DeviceGuard() { if (changed) cudaSetDevice(prev); }
+};
+
+struct Buffer {
+  void* p = nullptr;
+  size_t cap = 0;
+};
+
+}  // namespace
+
+struct pj_ctx {
+  int device = 0;
+  int inclusion = PJ_INCLUDE_NON_EMPTY;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  Buffer scratch;  /* tile counts, counter matrix, scan partials, writer offsets */
+  Buffer in_stage; /* device copy of a host input */
+  Buffer col_stage; /* device copies of host columns */
+  Buffer out_stage; /* device copy of a host output (writer) */
+  DevResult* d_res = nullptr;
+  DevResult* h_res = nullptr; /* pinned */
+  cudaEvent_t ev[10] = {};
+  Schema schema;
+  pj_call_stats stats = {};
+  char err[256] = "";
+};
+
+namespace {
+
+pj_status set_err(pj_ctx* c, pj_status st, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(c ? c->err : g_create_error, 256, fmt, ap);
+  va_end(ap);
+  return st;
+}
+#define PJ_CUDA(ctx, call)                                                                              \
+  do {                                                                                                  \
+    cudaError_t e__ = (call);                                                                           \
+    if (e__ != cudaSuccess) return set_err(ctx, e__ == cudaErrorMemoryAllocation ? PJ_ERR_NOMEM : PJ_ERR_CUDA, \
+                                           "%s: %s", #call, cudaGetErrorString(e__));                   \
+  } while (0)
+
+pj_status ensure(pj_ctx* c, Buffer* b, size_t bytes) {
+  if (bytes <= b->cap) return PJ_OK;
+  if (b->p) { PJ_CUDA(c, cudaStreamSynchronize(c->stream)); PJ_CUDA(c, cudaFree(b->p)); b->p = nullptr; b->cap = 0; }
+  size_t want = bytes + bytes / 8 + 4096;
+  cudaError_t e = cudaMalloc(&b->p, want);
+  if (e != cudaSuccess) { want = bytes; e = cudaMalloc(&b->p, want); }
+  if (e != cudaSuccess) { b->p = nullptr; (void)cudaGetLastError(); return set_err(c, PJ_ERR_NOMEM, "cudaMalloc(%zu): %s", want, cudaGetErrorString(e)); }
+  b->cap = want;
+  return PJ_OK;
+}
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+/* per-record columns a parse of `schema` fills */
+int record_cols(uint32_t schema, int* out) {
+  int n = 0;
+  out[n++] = PJ_COL_REC_START; out[n++] = PJ_COL_ERR_KIND; out[n++] = PJ_COL_ERR_OFF;
+  if (schema == PJ_SCHEMA_MIXED) { out[n++] = PJ_COL_REC_TYPE; out[n++] = PJ_COL_REC_ROW; }
+  return n;
+}
+
+struct Stage {
+  pj_ctx* c;
+  int k = 0;
+  explicit Stage(pj_ctx* ctx) : c(ctx) { cudaEventRecord(c->ev[0], c->stream); }
+  /* closes stage k (its launches were counted by the caller) */
+  void next() { ++k; cudaEventRecord(c->ev[k], c->stream); }
+};
+inline void count_launch(pj_ctx* c, int stage, uint32_t n = 1) { c->stats.kernel_launches += n; c->stats.stage_launches[stage] += n; }
+
+void collect_times(pj_ctx* c, int stages) {
+  for (int i = 0; i < stages && i < 8; ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, c->ev[i], c->ev[i + 1]) == cudaSuccess) c->stats.stage_ms[i] = ms;
+  }
+  float ms = 0.f;
+  if (cudaEventElapsedTime(&ms, c->ev[0], c->ev[stages]) == cudaSuccess) c->stats.device_ms = ms;
+}
+
+pj_status run_scan_u32(pj_ctx* c, uint32_t* data, uint64_t stride, uint32_t nslots, uint32_t slot_lo, uint64_t n_cap,
+                       uint32_t* partial, uint32_t nchunks, int stage) {
+  if (!nslots) return PJ_OK;
+  ScanArgs a;
+  a.data = data; a.stride = stride; a.partial = partial; a.nchunks = nchunks; a.slot_lo = slot_lo;
+  a.n_dev = &c->d_res->n_records; a.n_cap = n_cap; a.totals = c->d_res->total;
+  dim3 grid(nchunks, nslots);
+  k_scan_reduce<uint32_t><<<grid, SCAN_THREADS, 0, c->stream>>>(a);
+  k_scan_mid<uint32_t><<<nslots, 1024, 0, c->stream>>>(a);
+  k_scan_apply<uint32_t><<<grid, SCAN_THREADS, 0, c->stream>>>(a);
+  count_launch(c, stage, 3);
+  PJ_CUDA(c, cudaGetLastError());
+  return PJ_OK;
+}
+
+int persistent_grid(pj_ctx* c, uint64_t items, int threads) {
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
+  uint64_t want = (items + threads - 1) / threads;
+  uint64_t cap = (uint64_t)sms * 16;
+  if (want < 1) want = 1;
+  return (int)(want < cap ? want : cap);
+}
+
+pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack,
+                     int is_first, int is_last, uint64_t goff, uint32_t in_kind, pj_columns* out) {
+  if (!c) return PJ_ERR_ARG;
+  if (!out || (!in && len + slack) || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED || in_kind > PJ_MEM_DEVICE ||
+      out->mem_kind > PJ_MEM_DEVICE)
+    return set_err(c, PJ_ERR_ARG, "pj_parse: bad argument");
+  if (framing != PJ_FRAMING_NDJSON) return set_err(c, PJ_ERR_ARG, "pj_parse: framing %u is not available", framing);
+  const uint64_t limit = len + slack;
+  if (limit >= (1ull << 32)) return set_err(c, PJ_ERR_TOO_LARGE, "pj_parse: %llu input bytes do not fit 32-bit offsets", (unsigned long long)limit);
+  DeviceGuard guard(c->device);
+  c->stats = pj_call_stats{};
+
+  /* columns of this schema */
+  FinalizeArgs fa;
+  memset(&fa, 0, sizeof fa);
+  build_finalize_plan(c->schema, schema, &fa.plan);
+  int rcols[5];
+  const int nrc = record_cols(schema, rcols);
+  int need[PJ_MAX_COLS], nneed = 0;
+  for (int i = 0; i < nrc; ++i) need[nneed++] = rcols[i];
+  for (uint32_t k = 0; k < fa.plan.n; ++k) need[nneed++] = fa.plan.item[k].col;
+  for (int i = 0; i < nneed; ++i)
+    if (!out->col[need[i]].ptr) return set_err(c, PJ_ERR_ARG, "pj_parse: column %s has no buffer", col_info(need[i])->name);
+
+  /* stage host memory */
+  const bool host_out = out->mem_kind == PJ_MEM_HOST;
+  const uint8_t* d_in = in;
+  if (in_kind == PJ_MEM_HOST && limit) {
+    pj_status st = ensure(c, &c->in_stage, limit + 64);
+    if (st) return st;
+    PJ_CUDA(c, cudaMemcpyAsync(c->in_stage.p, in, limit, cudaMemcpyHostToDevice, c->stream));
+    c->stats.h2d_bytes += limit;
+    d_in = (const uint8_t*)c->in_stage.p;
+  }
+  DevCols dcols;
+  memset(&dcols, 0, sizeof dcols);
+  if (host_out) {
+    size_t tot = 0;
+    for (int i = 0; i < nneed; ++i) tot += align_up(out->col[need[i]].bytes, 256);
+    pj_status st = ensure(c, &c->col_stage, tot + 256);
+    if (st) return st;
+    size_t at = 0;
+    for (int i = 0; i < nneed; ++i) { dcols.ptr[need[i]] = (uint8_t*)c->col_stage.p + at; at += align_up(out->col[need[i]].bytes, 256); }
+  } else {
+    for (int i = 0; i < nneed; ++i) dcols.ptr[need[i]] = out->col[need[i]].ptr;
+  }
+  uint64_t cap_records = ~0ull;
+  for (int i = 0; i < nneed; ++i) fa.cap_elems[need[i]] = out->col[need[i]].bytes / col_info(need[i])->elem;
+  for (int i = 0; i < nrc; ++i) if (fa.cap_elems[rcols[i]] < cap_records) cap_records = fa.cap_elems[rcols[i]];
+  if (cap_records > (1ull << 32)) cap_records = 1ull << 32;
+  /* no more records than candidate line starts */
+  if (cap_records > limit / 2 + 2) cap_records = limit / 2 + 2;
+  fa.cap_records = cap_records;
+  fa.res = c->d_res;
+  fa.cols = dcols;
+
+  /* scratch */
+  uint32_t slot_lo, slot_hi;
+  slot_range(schema, &slot_lo, &slot_hi);
+  const uint32_t nslots = slot_hi - slot_lo;
+  const uint64_t ntiles = (len + 15 + INDEX_TILE) / INDEX_TILE; /* covers the worst misalignment of `in` */
+  const uint64_t stride = align_up(cap_records + 1, 4);
+  const uint32_t nchunks = (uint32_t)((cap_records + 1 + SCAN_CHUNK - 1) / SCAN_CHUNK);
+  size_t off_tile = 0;
+  size_t off_cnt = align_up(off_tile + (ntiles + 1) * 4, 256);
+  size_t off_part = align_up(off_cnt + (size_t)nslots * stride * 4, 256);
+  size_t total_scratch = off_part + (size_t)nslots * nchunks * 4 + 256;
+  { pj_status st = ensure(c, &c->scratch, total_scratch); if (st) return st; }
+  uint32_t* d_tile = (uint32_t*)((uint8_t*)c->scratch.p + off_tile);
+  uint32_t* d_cnt = (uint32_t*)((uint8_t*)c->scratch.p + off_cnt);
+  uint32_t* d_part = (uint32_t*)((uint8_t*)c->scratch.p + off_part);
+
+  PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream));
+  Stage stage(c);
+
+  /* stage 0: record index */
+  IndexArgs ia;
+  ia.in = d_in; ia.len = len; ia.limit = limit; ia.is_first = is_first; ia.is_last = is_last;
+  ia.tile = d_tile; ia.rec_start = (uint64_t*)dcols.ptr[PJ_COL_REC_START]; ia.cap = cap_records; ia.goff = goff;
+  k_nd_index<false><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
+  k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles, &c->d_res->n_records);
+  k_nd_index<true><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
+  count_launch(c, 0, 3);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+
+  /* stage 1: size pass */
+  ParseArgs pa;
+  pa.in = d_in; pa.limit = limit; pa.goff = goff; pa.cap_records = cap_records;
+  pa.lf_ws = 0; pa.open_end = is_last ? 0u : 1u; pa.schema = schema; pa.slot_lo = slot_lo; pa.slot_hi = slot_hi;
+  pa.cnt = d_cnt - (size_t)slot_lo * stride; /* indexed by absolute slot */
+  pa.stride = stride; pa.rec_end = nullptr; pa.rec_blank = nullptr; pa.res = c->d_res; pa.cols = dcols;
+  const int pgrid = persistent_grid(c, cap_records, PARSE_THREADS);
+  k_parse_size<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
+  count_launch(c, 1);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+
+  /* stage 2: where every record starts in every arena */
+  { pj_status st = run_scan_u32(c, d_cnt, stride, nslots, slot_lo, cap_records, d_part, nchunks, 2); if (st) return st; }
+  k_check<<<1, 32, 0, c->stream>>>(fa);
+  count_launch(c, 2);
+  stage.next();
+
+  /* stage 3: emit pass */
+  k_parse_emit<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
+  count_launch(c, 3);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+
+  /* stage 4: closing offsets */
+  k_finalize<<<1, 64, 0, c->stream>>>(fa);
+  count_launch(c, 4);
+  stage.next();
+
+  PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+  PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  PJ_CUDA(c, cudaGetLastError());
+  collect_times(c, 5);
+  c->stats.main_kernel_ms = c->stats.stage_ms[1] + c->stats.stage_ms[3];
+
+  const DevResult& r = *c->h_res;
+  const uint64_t N = r.n_records;
+  out->schema = schema;
+  out->n_records = N;
+  out->n_errors = r.n_errors;
+  out->doc_err_kind = 0; out->doc_err_off = 0;
+  for (int t = 0; t < 4; ++t) out->n_rows[t] = 0;
+  if (schema == PJ_SCHEMA_MIXED) { out->n_rows[1] = r.total[SLOT_ROWS_PET]; out->n_rows[2] = r.total[SLOT_ROWS_ORD]; out->n_rows[3] = r.total[SLOT_ROWS_USR]; }
+  else out->n_rows[schema] = N;
+  for (int i = 0; i < nrc; ++i) out->col[rcols[i]].count = N;
+  for (uint32_t k = 0; k < fa.plan.n; ++k) {
+    const FinalizeItem& it = fa.plan.item[k];
+    uint64_t rows = it.rows_slot == 0xFF ? N : r.total[it.rows_slot];
+    out->col[it.col].count = rows + (it.sentinel_slot != 0xFF ? 1 : 0);
+  }
+  uint64_t alg = len;
+  for (int i = 0; i < nneed; ++i) alg += out->col[need[i]].count * col_info(need[i])->elem;
+  c->stats.algorithmic_bytes = alg;
+  if (!r.ok) return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records need larger output buffers", (unsigned long long)N);
+  if (host_out) {
+    for (int i = 0; i < nneed; ++i) {
+      size_t nb = (size_t)out->col[need[i]].count * col_info(need[i])->elem;
+      if (!nb) continue;
+      PJ_CUDA(c, cudaMemcpyAsync(out->col[need[i]].ptr, dcols.ptr[need[i]], nb, cudaMemcpyDeviceToHost, c->stream));
+      c->stats.d2h_bytes += nb;
+    }
+    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  }
+  return PJ_OK;
+}
+
+}  // namespace
+
+/* ================================================================================================ */
+extern "C" {
+
+int32_t pj_version(void) { return PJ_VERSION_MAJOR * 1000 + PJ_VERSION_MINOR; }
+
+const char* pj_status_str(pj_status s) {
+  switch (s) {
+    case PJ_OK: return "PJ_OK";
+    case PJ_ERR_ARG: return "PJ_ERR_ARG";
+    case PJ_ERR_CAPACITY: return "PJ_ERR_CAPACITY";
+    case PJ_ERR_CUDA: return "PJ_ERR_CUDA";
+    case PJ_ERR_TIMEOUT: return "PJ_ERR_TIMEOUT";
+    case PJ_ERR_NOMEM: return "PJ_ERR_NOMEM";
+    case PJ_ERR_TOO_LARGE: return "PJ_ERR_TOO_LARGE";
+    default: return "PJ_ERR_?";
+  }
+}
+const char* pj_error_kind_str(int32_t kind) {
+  static const char* const names[PJ_E_KIND_COUNT] = {"NONE", "SYNTAX", "EOF", "CTRL_CHAR", "BAD_ESCAPE", "BAD_SURROGATE", "UTF8", "TYPE",
+                                                     "NUM_RANGE", "ENUM", "REQUIRED", "DATETIME", "DEPTH", "AMBIGUOUS", "TOO_LONG"};
+  return kind >= 0 && kind < PJ_E_KIND_COUNT ? names[kind] : "?";
+}
+pj_status pj_column_info(int32_t col, const char** name, uint32_t* elem_bytes, uint32_t* owner) {
+  const ColInfo* ci = col_info(col);
+  if (!ci) return PJ_ERR_ARG;
+  if (name) *name = ci->name;
+  if (elem_bytes) *elem_bytes = ci->elem;
+  if (owner) *owner = ci->owner;
+  return PJ_OK;
+}
+
+pj_status pj_create(const pj_options* opt, pj_ctx** out) {
+  if (!out) return PJ_ERR_ARG;
+  *out = nullptr;
+  int dev = opt ? opt->device : -1;
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  if (e != cudaSuccess || ndev == 0) { (void)cudaGetLastError(); return set_err(nullptr, PJ_ERR_CUDA, "no CUDA device: %s", cudaGetErrorString(e)); }
+  if (dev < 0) { if (cudaGetDevice(&dev) != cudaSuccess) return set_err(nullptr, PJ_ERR_CUDA, "cudaGetDevice failed"); }
+  if (dev >= ndev) return set_err(nullptr, PJ_ERR_ARG, "device %d of %d", dev, ndev);
+  if (opt && (opt->inclusion < PJ_INCLUDE_NON_EMPTY || opt->inclusion > PJ_INCLUDE_ALWAYS)) return set_err(nullptr, PJ_ERR_ARG, "bad inclusion policy");
+  pj_ctx* c = new (std::nothrow) pj_ctx();
+  if (!c) return PJ_ERR_NOMEM;
+  c->device = dev;
+  c->inclusion = opt ? opt->inclusion : PJ_INCLUDE_NON_EMPTY;
+  DeviceGuard guard(dev);
+  auto fail_create = [&](cudaError_t err, const char* what) {
+    set_err(nullptr, PJ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+    pj_destroy(c);
+    return PJ_ERR_CUDA;
+  };
+  if (opt && opt->stream) c->stream = (cudaStream_t)opt->stream;
+  else {
+    e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return fail_create(e, "cudaStreamCreate");
+    c->own_stream = true;
+  }
+  e = cudaMalloc(&c->d_res, sizeof(DevResult));
+  if (e != cudaSuccess) return fail_create(e, "cudaMalloc");
+  e = cudaMallocHost(&c->h_res, sizeof(DevResult));
+  if (e != cudaSuccess) return fail_create(e, "cudaMallocHost");
+  for (auto& ev : c->ev) { e = cudaEventCreate(&ev); if (e != cudaSuccess) return fail_create(e, "cudaEventCreate"); }
+  build_schema(&c->schema);
+  e = cudaMemcpyToSymbol(c_schema, &c->schema, sizeof(Schema));
+  if (e != cudaSuccess) return fail_create(e, "cudaMemcpyToSymbol");
+  *out = c;
+  return PJ_OK;
+}
+
+void pj_destroy(pj_ctx* c) {
+  if (!c) return;
+  DeviceGuard guard(c->device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  for (Buffer* b : {&c->scratch, &c->in_stage, &c->col_stage, &c->out_stage}) if (b->p) cudaFree(b->p);
+  if (c->d_res) cudaFree(c->d_res);
+  if (c->h_res) cudaFreeHost(c->h_res);
+  for (auto& ev : c->ev) if (ev) cudaEventDestroy(ev);
+  if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
+  delete c;
+}
+
+const char* pj_last_error(const pj_ctx* c) { return c ? c->err : g_create_error; }
+
+pj_status pj_last_stats(const pj_ctx* c, pj_call_stats* out) {
+  if (!c || !out) return PJ_ERR_ARG;
+  *out = c->stats;
+  return PJ_OK;
+}
+
+pj_status pj_trim(pj_ctx* c) {
+  if (!c) return PJ_ERR_ARG;
+  DeviceGuard guard(c->device);
+  PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  for (Buffer* b : {&c->scratch, &c->in_stage, &c->col_stage, &c->out_stage}) {
+    if (b->p) { PJ_CUDA(c, cudaFree(b->p)); b->p = nullptr; b->cap = 0; }
+  }
+  return PJ_OK;
+}
+
+pj_status pj_columns_sizes(uint32_t schema, uint64_t max_records, uint64_t max_input_bytes, uint64_t max_list_items,
+                           pj_columns* out) {
+  if (!out || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED) return PJ_ERR_ARG;
+  Schema S;
+  build_schema(&S);
+  FinalizePlan plan;
+  build_finalize_plan(S, schema, &plan);
+  /* a list item costs at least two input bytes ("" or {}) plus a separator on average */
+  const uint64_t items = max_list_items ? max_list_items : max_input_bytes / 2 + 1;
+  out->schema = schema;
+  int rcols[5];
+  const int nrc = record_cols(schema, rcols);
+  for (int i = 0; i < nrc; ++i) out->col[rcols[i]].bytes = (max_records + 1) * col_info(rcols[i])->elem;
+  for (uint32_t k = 0; k < plan.n; ++k) {
+    const FinalizeItem& it = plan.item[k];
+    uint64_t rows;
+    if (it.rows_slot == 0xFF || it.rows_slot <= SLOT_ROWS_USR) rows = max_records;
+    else if (it.elem == 1 && it.sentinel_slot == 0xFF && it.col != S.obj[OBJ_TAG].present_col) rows = max_input_bytes; /* arena: never more bytes than the input */
+    else rows = items;
+    out->col[it.col].bytes = (rows + 1) * it.elem;
+  }
+  return PJ_OK;
+}
+
+pj_status pj_parse(pj_ctx* ctx, uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len, uint32_t in_kind,
+                   pj_columns* out) {
+  return parse_impl(ctx, schema, framing, in, len, 0, 1, 1, 0, in_kind, out);
+}
+
+pj_status pj_parse_shard(pj_ctx* ctx, uint32_t schema, const uint8_t* in, uint64_t len, uint64_t slack, int32_t is_first,
+                         int32_t is_last, uint64_t global_offset, uint32_t in_kind, pj_columns* out) {
+  return parse_impl(ctx, schema, PJ_FRAMING_NDJSON, in, len, slack, is_first != 0, is_last != 0, global_offset, in_kind, out);
+}
+
+pj_status pj_index_records(pj_ctx* c, uint32_t framing, const uint8_t* in, uint64_t len, uint32_t kind, uint64_t* rec_start,
+                           uint64_t cap, uint64_t* n) {
+  if (!c) return PJ_ERR_ARG;
+  if ((!in && len) || !n || (!rec_start && cap) || kind > PJ_MEM_DEVICE) return set_err(c, PJ_ERR_ARG, "pj_index_records: bad argument");
+  if (framing != PJ_FRAMING_NDJSON) return set_err(c, PJ_ERR_ARG, "pj_index_records: framing %u is not available", framing);
+  if (len >= (1ull << 32)) return set_err(c, PJ_ERR_TOO_LARGE, "pj_index_records: input too large");
+  DeviceGuard guard(c->device);
+  c->stats = pj_call_stats{};
+  const uint8_t* d_in = in;
+  uint64_t* d_rs = rec_start;
+  const uint64_t ntiles = (len + 15 + INDEX_TILE) / INDEX_TILE;
+  size_t off_rs = align_up((ntiles + 1) * 4, 256);
+  { pj_status st = ensure(c, &c->scratch, off_rs + (kind == PJ_MEM_HOST ? cap * 8 : 0) + 256); if (st) return st; }
+  if (kind == PJ_MEM_HOST) {
+    if (len) {
+      pj_status st = ensure(c, &c->in_stage, len + 64);
+      if (st) return st;
+      PJ_CUDA(c, cudaMemcpyAsync(c->in_stage.p, in, len, cudaMemcpyHostToDevice, c->stream));
+      c->stats.h2d_bytes += len;
+      d_in = (const uint8_t*)c->in_stage.p;
+    }
+    d_rs = (uint64_t*)((uint8_t*)c->scratch.p + off_rs);
+  }
+  uint32_t* d_tile = (uint32_t*)c->scratch.p;
+  PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream));
+  Stage stage(c);
+  IndexArgs ia;
+  ia.in = d_in; ia.len = len; ia.limit = len; ia.is_first = 1; ia.is_last = 1;
+  ia.tile = d_tile; ia.rec_start = d_rs; ia.cap = cap; ia.goff = 0;
+  k_nd_index<false><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
+  k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles, &c->d_res->n_records);
+  k_nd_index<true><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
+  count_launch(c, 0, 3);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+  PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+  PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  collect_times(c, 1);
+  c->stats.main_kernel_ms = c->stats.stage_ms[0];
+  *n = c->h_res->n_records;
+  uint64_t got = *n < cap ? *n : cap;
+  c->stats.algorithmic_bytes = len + got * 8;
+  if (kind == PJ_MEM_HOST && got) {
+    PJ_CUDA(c, cudaMemcpyAsync(rec_start, d_rs, got * 8, cudaMemcpyDeviceToHost, c->stream));
+    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+    c->stats.d2h_bytes += got * 8;
+  }
+  return *n > cap ? set_err(c, PJ_ERR_CAPACITY, "pj_index_records: %llu records, room for %llu", (unsigned long long)*n, (unsigned long long)cap) : PJ_OK;
+}
+
+pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_columns* cols, uint8_t* out, uint64_t cap,
+                   uint32_t out_kind, uint64_t* out_len) {
+  if (!c) return PJ_ERR_ARG;
+  if (!cols || !out_len || (!out && cap) || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED || framing > PJ_FRAMING_ARRAY ||
+      out_kind > PJ_MEM_DEVICE || cols->mem_kind > PJ_MEM_DEVICE)
+    return set_err(c, PJ_ERR_ARG, "pj_write: bad argument");
+  DeviceGuard guard(c->device);
+  c->stats = pj_call_stats{};
+  const bool mixed = schema == PJ_SCHEMA_MIXED;
+  const uint64_t n = mixed ? cols->n_records : cols->n_rows[schema];
+  FinalizePlan plan;
+  build_finalize_plan(c->schema, schema, &plan);
+  int need[PJ_MAX_COLS], nneed = 0;
+  if (mixed) { need[nneed++] = PJ_COL_REC_TYPE; need[nneed++] = PJ_COL_REC_ROW; }
+  for (uint32_t k = 0; k < plan.n; ++k) need[nneed++] = plan.item[k].col;
+  uint64_t col_bytes = 0;
+  for (int i = 0; i < nneed; ++i) {
+    const pj_buf& b = cols->col[need[i]];
+    if (b.count && !b.ptr) return set_err(c, PJ_ERR_ARG, "pj_write: column %s has no buffer", col_info(need[i])->name);
+    col_bytes += b.count * col_info(need[i])->elem;
+  }
+  /* the columns must describe n rows */
+  if (mixed && (cols->col[PJ_COL_REC_TYPE].count < n || cols->col[PJ_COL_REC_ROW].count < n)) return set_err(c, PJ_ERR_ARG, "pj_write: record map shorter than n_records");
+  for (uint32_t k = 0; k < plan.n; ++k) {
+    const FinalizeItem& it = plan.item[k];
+    if (it.rows_slot == 0xFF && cols->col[it.col].count < n + (it.sentinel_slot != 0xFF ? 1 : 0))
+      return set_err(c, PJ_ERR_ARG, "pj_write: column %s holds %llu elements for %llu rows", col_info(it.col)->name,
+                     (unsigned long long)cols->col[it.col].count, (unsigned long long)n);
+  }
+  DevCols dcols;
+  memset(&dcols, 0, sizeof dcols);
+  if (cols->mem_kind == PJ_MEM_HOST) {
+    size_t tot = 0;
+    for (int i = 0; i < nneed; ++i) tot += align_up(cols->col[need[i]].count * col_info(need[i])->elem, 256);
+    pj_status st = ensure(c, &c->col_stage, tot + 256);
+    if (st) return st;
+    size_t at = 0;
+    for (int i = 0; i < nneed; ++i) {
+      size_t nb = (size_t)cols->col[need[i]].count * col_info(need[i])->elem;
+      dcols.ptr[need[i]] = (uint8_t*)c->col_stage.p + at;
+      if (nb) PJ_CUDA(c, cudaMemcpyAsync(dcols.ptr[need[i]], cols->col[need[i]].ptr, nb, cudaMemcpyHostToDevice, c->stream));
+      c->stats.h2d_bytes += nb;
+      at += align_up(nb, 256);
+    }
+  } else {
+    for (int i = 0; i < nneed; ++i) dcols.ptr[need[i]] = cols->col[need[i]].ptr;
+  }
+  uint8_t* d_out = out;
+  if (out_kind == PJ_MEM_HOST) {
+    pj_status st = ensure(c, &c->out_stage, cap + 256);
+    if (st) return st;
+    d_out = (uint8_t*)c->out_stage.p;
+  }
+  const uint32_t nchunks = (uint32_t)((n + 1 + SCAN_CHUNK - 1) / SCAN_CHUNK);
+  size_t off_part = align_up((n + 1) * 8, 256);
+  { pj_status st = ensure(c, &c->scratch, off_part + (size_t)nchunks * 8 + 256); if (st) return st; }
+  uint64_t* d_off = (uint64_t*)c->scratch.p;
+  uint64_t* d_part = (uint64_t*)((uint8_t*)c->scratch.p + off_part);
+
+  DevResult init;
+  memset(&init, 0, sizeof init);
+  init.n_records = n;
+  *c->h_res = init;
+  PJ_CUDA(c, cudaMemcpyAsync(c->d_res, c->h_res, sizeof(DevResult), cudaMemcpyHostToDevice, c->stream));
+  Stage stage(c);
+  WriteArgs wa;
+  wa.n = n; wa.schema = schema; wa.array = framing == PJ_FRAMING_ARRAY; wa.inclusion = c->inclusion;
+  wa.off = d_off; wa.out = d_out; wa.cap = cap; wa.res = c->d_res; wa.cols = dcols;
+  const int grid = persistent_grid(c, n, PARSE_THREADS);
+  k_write_size<<<grid, PARSE_THREADS, 0, c->stream>>>(wa);
+  count_launch(c, 0);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+  ScanArgs sa;
+  sa.data = d_off; sa.stride = n + 1; sa.partial = d_part; sa.nchunks = nchunks; sa.slot_lo = 0;
+  sa.n_dev = &c->d_res->n_records; sa.n_cap = n; sa.totals = &c->d_res->out_bytes;
+  dim3 sgrid(nchunks, 1);
+  k_scan_reduce<uint64_t><<<sgrid, SCAN_THREADS, 0, c->stream>>>(sa);
+  k_scan_mid<uint64_t><<<1, 1024, 0, c->stream>>>(sa);
+  k_scan_apply<uint64_t><<<sgrid, SCAN_THREADS, 0, c->stream>>>(sa);
+  k_write_check<<<1, 32, 0, c->stream>>>(wa);
+  count_launch(c, 1, 4);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+  k_write_emit<<<grid, PARSE_THREADS, 0, c->stream>>>(wa);
+  count_launch(c, 2);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+  PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+  PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  PJ_CUDA(c, cudaGetLastError());
+  collect_times(c, 3);
+  c->stats.main_kernel_ms = c->stats.stage_ms[0] + c->stats.stage_ms[2];
+  *out_len = c->h_res->out_bytes;
+  c->stats.algorithmic_bytes = col_bytes + *out_len;
+  if (!c->h_res->ok) return set_err(c, PJ_ERR_CAPACITY, "pj_write: %llu bytes needed, room for %llu", (unsigned long long)*out_len, (unsigned long long)cap);
+  if (out_kind == PJ_MEM_HOST && *out_len) {
+    PJ_CUDA(c, cudaMemcpyAsync(out, d_out, *out_len, cudaMemcpyDeviceToHost, c->stream));
+    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+    c->stats.d2h_bytes += *out_len;
+  }
+  return PJ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,381 @@
+/*
+ * pj_kernels.cuh — the sm_100a kernels of the staged pipeline: NDJSON record index, per-record
+ * size / emit passes, the counter scans between them, and the JSON writer.
+ *
+ *   input bytes --k_nd_index<false>--> records per 16 KiB tile --scan--> tile bases
+ *               --k_nd_index<true>--> rec_start[]
+ *               --k_parse<false>----> err_kind / err_off / model, counters[slot][record]
+ *               --scan (per slot)--> start of every record in every arena; totals; capacity check
+ *               --k_parse<true>-----> every column, string bytes, list offsets
+ *               --k_finalize--------> closing offsets
+ *
+ * Nothing here waits on another thread block, so no kernel can hang on a peer.
+ */
+#ifndef PJ_KERNELS_CUH
+#define PJ_KERNELS_CUH
+
+#include <cuda_runtime.h>
+
+#include "pj_core.cuh"
+#include "pj_index.cuh"
+#include "pj_write_core.cuh"
+
+namespace pj {
+
+__constant__ Schema c_schema;
+
+/* Written by the kernels, read back by the host once per call. */
+struct DevResult {
+  unsigned long long n_records;
+  unsigned long long n_errors;
+  unsigned long long total[NSLOT];
+  unsigned long long out_bytes; /* writer: JSON bytes */
+  unsigned long long doc_err_off;
+  uint32_t doc_err_kind;
+  uint32_t ok; /* every output fits its buffer */
+};
+
+static constexpr int INDEX_THREADS = 256;
+static constexpr int INDEX_BYTES_PER_THREAD = 64;
+static constexpr int INDEX_TILE = INDEX_THREADS * INDEX_BYTES_PER_THREAD; /* 16 KiB */
+
+/* ---- block-wide exclusive scan ---------------------------------------------------------------- */
+template <class T>
+__device__ __forceinline__ T warp_incl_scan(T v) {
+  const unsigned lane = threadIdx.x & 31;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    T u = __shfl_up_sync(0xFFFFFFFFu, v, d);
+    if (lane >= (unsigned)d) v += u;
+  }
+  return v;
+}
+/* Exclusive prefix of v over the block (any multiple of 32 threads up to 1024); *total = block sum.
+ * `sh` needs 33 entries. Safe to call repeatedly. */
+template <class T>
+__device__ __forceinline__ T block_excl_scan(T v, T* total, T* sh) {
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  T inc = warp_incl_scan(v);
+  __syncthreads(); /* protect sh from the previous call */
+  if (lane == 31) sh[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    T w = lane < nwarps ? sh[lane] : T(0);
+    T wi = warp_incl_scan(w);
+    if (lane < nwarps) sh[lane] = wi - w;
+    if (lane == nwarps - 1) sh[32] = wi;
+  }
+  __syncthreads();
+  *total = sh[32];
+  return sh[warp] + inc - v;
+}
+
+/* ---- NDJSON record index ---------------------------------------------------------------------- */
+/* 64-bit mask of the LF bytes among the 64 bytes at the 16-byte aligned address a, of which the
+ * first `valid` (>= 1) belong to the input. */
+__device__ __forceinline__ uint64_t lf_mask64(const uint8_t* a, uint64_t valid) {
+  const uint4* q = reinterpret_cast<const uint4*>(a);
+  uint64_t m = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if ((uint64_t)(k * 16) >= valid) break; /* never touch a 16-byte block that holds no input byte */
+    uint4 v = __ldg(q + k);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t e = __vcmpeq4(w[j], 0x0A0A0A0Au) & 0x01010101u; /* 1 per matching byte */
+      uint32_t nib = (e * 0x01020408u) >> 24;                  /* gather the four flags */
+      m |= (uint64_t)(nib & 0xF) << (k * 16 + j * 4);
+    }
+  }
+  return m;
+}
+
+struct IndexArgs {
+  const uint8_t* in;
+  uint64_t len, limit;
+  int is_first, is_last;
+  uint32_t* tile; /* [tiles + 1]: counts, then (after the scan) exclusive bases */
+  uint64_t* rec_start;
+  uint64_t cap, goff;
+};
+
+/* One thread looks at 64 input bytes. Every LF inside [0, len) makes the following byte a candidate
+ * line start; byte 0 is one too when the shard is the first of its stream. WRITE = false counts the
+ * candidates that are records per tile; WRITE = true stores their offsets at the scanned positions. */
+template <bool WRITE>
+__global__ void __launch_bounds__(INDEX_THREADS) k_nd_index(const __grid_constant__ IndexArgs a) {
+  __shared__ uint32_t sh[33];
+  const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(a.in) & 15u);
+  const uint8_t* base = a.in - mis; /* 16-byte aligned */
+  const uint64_t v0 = (uint64_t)blockIdx.x * INDEX_TILE + (uint64_t)threadIdx.x * INDEX_BYTES_PER_THREAD; /* offset from base */
+  const uint64_t vend = a.len ? a.len + mis : 0; /* an empty input is never dereferenced */
+  uint64_t m = 0;
+  if (v0 < vend) {
+    m = lf_mask64(base + v0, vend - v0);
+    if (v0 < mis) m &= ~0ull << (mis - v0);               /* bytes before in[0] */
+    if (vend - v0 < 64) m &= ~(~0ull << (vend - v0));      /* bytes at or after in[len] */
+  }
+  const bool head = a.is_first && blockIdx.x == 0 && threadIdx.x == 0; /* candidate at byte 0 */
+  uint32_t cnt = 0;
+  if (!WRITE) {
+    if (head && nd_is_record(a.in, 0, a.limit, a.is_last)) cnt++;
+    for (uint64_t t = m; t; t &= t - 1) {
+      uint64_t p = v0 + (uint64_t)(__ffsll((long long)t) - 1) - mis + 1;
+      if (nd_is_record(a.in, p, a.limit, a.is_last)) cnt++;
+    }
+    uint32_t total;
+    block_excl_scan(cnt, &total, sh);
+    if (threadIdx.x == 0) a.tile[blockIdx.x] = total;
+  } else {
+    /* recount, then place */
+    uint64_t keep = 0;
+    bool head_keep = head && nd_is_record(a.in, 0, a.limit, a.is_last);
+    cnt = head_keep ? 1u : 0u;
+    for (uint64_t t = m; t; t &= t - 1) {
+      int b = __ffsll((long long)t) - 1;
+      uint64_t p = v0 + (uint64_t)b - mis + 1;
+      if (nd_is_record(a.in, p, a.limit, a.is_last)) { keep |= 1ull << b; cnt++; }
+    }
+    uint32_t total;
+    uint64_t at = (uint64_t)a.tile[blockIdx.x] + block_excl_scan(cnt, &total, sh);
+    if (head_keep) { if (at < a.cap) a.rec_start[at] = a.goff; at++; }
+    for (uint64_t t = keep; t; t &= t - 1) {
+      uint64_t p = v0 + (uint64_t)(__ffsll((long long)t) - 1) - mis + 1;
+      if (at < a.cap) a.rec_start[at] = p + a.goff;
+      at++;
+    }
+  }
+}
+
+/* ---- scans over device-resident lengths -------------------------------------------------------- */
+static constexpr int SCAN_THREADS = 256;
+static constexpr int SCAN_ITEMS = 8;
+static constexpr int SCAN_CHUNK = SCAN_THREADS * SCAN_ITEMS;
+
+/* Single block: exclusive scan of data[0..n) in place, data[n] = total; also *total_out. */
+template <class T>
+__global__ void __launch_bounds__(1024) k_scan_single(T* data, uint64_t n, unsigned long long* total_out) {
+  __shared__ T sh[33];
+  T carry = 0;
+  for (uint64_t b = 0; b < n; b += blockDim.x) {
+    uint64_t i = b + threadIdx.x;
+    T v = i < n ? data[i] : T(0), tot;
+    T ex = block_excl_scan(v, &tot, sh);
+    if (i < n) data[i] = carry + ex;
+    carry += tot;
+  }
+  if (threadIdx.x == 0) { data[n] = carry; if (total_out) *total_out = (unsigned long long)carry; }
+}
+
+struct ScanArgs {
+  void* data;                      /* [nslots][stride] */
+  uint64_t stride;
+  void* partial;                   /* [nslots][nchunks] */
+  uint32_t nchunks, slot_lo;
+  const unsigned long long* n_dev; /* number of valid entries per slot (device resident) */
+  uint64_t n_cap;                  /* entries the buffers can hold (excluding the closing entry) */
+  unsigned long long* totals;      /* [NSLOT] indexed by slot_lo + blockIdx.y */
+};
+template <class T>
+__global__ void __launch_bounds__(SCAN_THREADS) k_scan_reduce(const __grid_constant__ ScanArgs a) {
+  __shared__ T sh[33];
+  uint64_t n = min((uint64_t)*a.n_dev, a.n_cap);
+  uint64_t c0 = (uint64_t)blockIdx.x * SCAN_CHUNK;
+  if (c0 >= n) return;
+  const T* d = (const T*)a.data + (uint64_t)blockIdx.y * a.stride;
+  T s = 0;
+#pragma unroll
+  for (int k = 0; k < SCAN_ITEMS; ++k) {
+    uint64_t i = c0 + (uint64_t)k * SCAN_THREADS + threadIdx.x;
+    if (i < n) s += d[i];
+  }
+  T tot;
+  block_excl_scan(s, &tot, sh);
+  if (threadIdx.x == 0) ((T*)a.partial)[(uint64_t)blockIdx.y * a.nchunks + blockIdx.x] = tot;
+}
+template <class T>
+__global__ void __launch_bounds__(1024) k_scan_mid(const __grid_constant__ ScanArgs a) {
+  __shared__ T sh[33];
+  uint64_t n = min((uint64_t)*a.n_dev, a.n_cap);
+  uint32_t used = (uint32_t)((n + SCAN_CHUNK - 1) / SCAN_CHUNK);
+  T* p = (T*)a.partial + (uint64_t)blockIdx.x * a.nchunks;
+  T carry = 0;
+  for (uint32_t b = 0; b < used; b += blockDim.x) {
+    uint32_t i = b + threadIdx.x;
+    T v = i < used ? p[i] : T(0), tot;
+    T ex = block_excl_scan(v, &tot, sh);
+    if (i < used) p[i] = carry + ex;
+    carry += tot;
+  }
+  if (threadIdx.x == 0) a.totals[a.slot_lo + blockIdx.x] = (unsigned long long)carry;
+}
+/* In-place exclusive scan of each chunk plus its base; entry [n] receives the slot total. */
+template <class T>
+__global__ void __launch_bounds__(SCAN_THREADS) k_scan_apply(const __grid_constant__ ScanArgs a) {
+  __shared__ T sh[33];
+  uint64_t n = min((uint64_t)*a.n_dev, a.n_cap);
+  uint64_t c0 = (uint64_t)blockIdx.x * SCAN_CHUNK;
+  if (c0 > n) return;
+  T* d = (T*)a.data + (uint64_t)blockIdx.y * a.stride;
+  T base = c0 < n ? ((const T*)a.partial)[(uint64_t)blockIdx.y * a.nchunks + blockIdx.x] : (T)a.totals[a.slot_lo + blockIdx.y];
+  /* thread t owns SCAN_ITEMS consecutive entries */
+  uint64_t i0 = c0 + (uint64_t)threadIdx.x * SCAN_ITEMS;
+  T v[SCAN_ITEMS], s = 0;
+#pragma unroll
+  for (int k = 0; k < SCAN_ITEMS; ++k) { v[k] = (i0 + k < n) ? d[i0 + k] : T(0); s += v[k]; }
+  T tot;
+  T ex = base + block_excl_scan(s, &tot, sh);
+#pragma unroll
+  for (int k = 0; k < SCAN_ITEMS; ++k) { if (i0 + k <= n) d[i0 + k] = ex; ex += v[k]; }
+}
+
+/* ---- per-record passes -------------------------------------------------------------------------- */
+struct ParseArgs {
+  const uint8_t* in;
+  uint64_t limit, goff, cap_records;
+  uint32_t lf_ws, open_end, schema, slot_lo, slot_hi;
+  uint32_t* cnt;          /* [NSLOT][stride] */
+  uint64_t stride;
+  const uint64_t* rec_end;   /* array framing: end of every extent, else null */
+  const uint8_t* rec_blank;  /* array framing: extent without a value */
+  DevResult* res;
+  DevCols cols;
+};
+
+static constexpr int PARSE_THREADS = 128;
+
+/* Size pass: one record per thread. */
+__global__ void __launch_bounds__(PARSE_THREADS) k_parse_size(const __grid_constant__ ParseArgs a) {
+  const uint64_t n = min((uint64_t)a.res->n_records, a.cap_records);
+  const uint64_t* rec_start = colp<uint64_t>(&a.cols, PJ_COL_REC_START);
+  uint32_t nerr = 0;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    Rd r;
+    r.in = a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end;
+    r.limit = a.rec_end ? a.rec_end[i] : a.limit;
+    PS s;
+    s.p = rec_start[i] - a.goff; s.err = 0; s.err_pos = 0;
+    const uint64_t start = s.p;
+    Out<false> o;
+    o.cols = &a.cols;
+    uint32_t type;
+    if (a.rec_blank && a.rec_blank[i]) { fail(s, PJ_E_SYNTAX, r.limit); type = PJ_TYPE_NONE; for (uint32_t k = 0; k < NSLOT; ++k) o.cnt[k] = 0; }
+    else type = parse_record<false>(c_schema, r, s, a.schema, o, i);
+    if (s.err) { type = PJ_TYPE_NONE; nerr++; }
+    colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i] = (uint8_t)s.err;
+    colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = s.err ? (uint32_t)(s.err_pos - start) : 0u;
+    if (a.schema == PJ_SCHEMA_MIXED) colp<uint8_t>(&a.cols, PJ_COL_REC_TYPE)[i] = (uint8_t)type;
+    for (uint32_t k = a.slot_lo; k < a.slot_hi; ++k) a.cnt[(uint64_t)k * a.stride + i] = s.err ? 0u : o.cnt[k];
+  }
+  /* one atomic per warp */
+  for (int d = 16; d; d >>= 1) nerr += __shfl_down_sync(0xFFFFFFFFu, nerr, d);
+  if ((threadIdx.x & 31) == 0 && nerr) atomicAdd(&a.res->n_errors, (unsigned long long)nerr);
+}
+
+/* Emit pass. */
+__global__ void __launch_bounds__(PARSE_THREADS) k_parse_emit(const __grid_constant__ ParseArgs a) {
+  if (!a.res->ok) return;
+  const uint64_t n = (uint64_t)a.res->n_records;
+  const uint64_t* rec_start = colp<uint64_t>(&a.cols, PJ_COL_REC_START);
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    Out<true> o;
+    o.cols = &a.cols;
+    for (uint32_t k = 0; k < NSLOT; ++k) { o.base[k] = 0; o.room[k] = 0; }
+    for (uint32_t k = a.slot_lo; k < a.slot_hi; ++k) {
+      uint32_t b0 = a.cnt[(uint64_t)k * a.stride + i], b1 = a.cnt[(uint64_t)k * a.stride + i + 1];
+      o.base[k] = b0; o.room[k] = b1 - b0;
+    }
+    const uint32_t err = colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i];
+    if (a.schema == PJ_SCHEMA_MIXED) {
+      uint32_t type = colp<uint8_t>(&a.cols, PJ_COL_REC_TYPE)[i];
+      colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = type == PJ_TYPE_NONE ? 0xFFFFFFFFu : o.base[type - 1];
+    }
+    if (err) {
+      if (a.schema != PJ_SCHEMA_MIXED) store_absent<true>(c_schema, a.schema, o, i);
+      continue;
+    }
+    Rd r;
+    r.in = a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end;
+    r.limit = a.rec_end ? a.rec_end[i] : a.limit;
+    PS s;
+    s.p = rec_start[i] - a.goff; s.err = 0; s.err_pos = 0;
+    parse_record<true>(c_schema, r, s, a.schema, o, i);
+  }
+}
+
+/* Capacity check and closing offsets. */
+struct FinalizeArgs {
+  FinalizePlan plan;
+  uint64_t cap_elems[PJ_MAX_COLS];
+  uint64_t cap_records;
+  DevResult* res;
+  DevCols cols;
+};
+__global__ void k_check(const __grid_constant__ FinalizeArgs a) {
+  if (threadIdx.x || blockIdx.x) return;
+  uint64_t n = a.res->n_records;
+  uint32_t ok = n <= a.cap_records;
+  for (uint32_t k = 0; k < a.plan.n; ++k) {
+    FinalizeItem it = a.plan.item[k];
+    uint64_t rows = it.rows_slot == 0xFF ? n : a.res->total[it.rows_slot];
+    if (rows + (it.sentinel_slot != 0xFF) > a.cap_elems[it.col]) ok = 0;
+  }
+  a.res->ok = ok;
+}
+__global__ void k_finalize(const __grid_constant__ FinalizeArgs a) {
+  if (!a.res->ok) return;
+  uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= a.plan.n) return;
+  FinalizeItem it = a.plan.item[k];
+  if (it.sentinel_slot == 0xFF) return;
+  uint64_t rows = it.rows_slot == 0xFF ? a.res->n_records : a.res->total[it.rows_slot];
+  colp<uint32_t>(&a.cols, it.col)[rows] = (uint32_t)a.res->total[it.sentinel_slot];
+}
+
+/* ---- writer ---------------------------------------------------------------------------------- */
+struct WriteArgs {
+  uint64_t n;             /* records (mixed) or rows */
+  uint32_t schema, array; /* array: wrap as [r,r,...] */
+  int inclusion;
+  uint64_t* off;          /* [n + 1] lengths, then exclusive offsets */
+  uint8_t* out;
+  uint64_t cap;
+  DevResult* res;
+  DevCols cols;
+};
+__global__ void __launch_bounds__(PARSE_THREADS) k_write_size(const __grid_constant__ WriteArgs a) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
+    uint32_t type; uint64_t row;
+    uint64_t len = 0;
+    if (write_locate(a.schema, &a.cols, i, &type, &row)) {
+      WOut w; w.dst = nullptr; w.n = 0;
+      write_record<false>(c_schema, &a.cols, type, row, a.inclusion, w);
+      len = w.n + 1; /* LF, or the comma / closing bracket that follows the record */
+    }
+    a.off[i] = len;
+  }
+}
+__global__ void k_write_check(const __grid_constant__ WriteArgs a) {
+  if (threadIdx.x || blockIdx.x) return;
+  uint64_t body = a.res->out_bytes; /* sum of the record lengths, set by the scan */
+  uint64_t total = a.array ? (body ? body + 1 : 2) : body;
+  a.res->out_bytes = total;
+  a.res->ok = total <= a.cap;
+  if (a.array && total <= a.cap) { a.out[0] = '['; if (!body) a.out[1] = ']'; }
+}
+__global__ void __launch_bounds__(PARSE_THREADS) k_write_emit(const __grid_constant__ WriteArgs a) {
+  if (!a.res->ok) return;
+  const uint64_t total = a.res->out_bytes;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
+    uint32_t type; uint64_t row;
+    if (!write_locate(a.schema, &a.cols, i, &type, &row)) continue;
+    uint64_t at = a.off[i] + (a.array ? 1 : 0);
+    WOut w; w.dst = a.out + at; w.n = 0;
+    write_record<true>(c_schema, &a.cols, type, row, a.inclusion, w);
+    a.out[at + w.n] = a.array ? (uint8_t)(at + w.n + 1 == total ? ']' : ',') : (uint8_t)'\n';
+  }
+}
+
+}  // namespace pj
+#endif

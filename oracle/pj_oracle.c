@@ -864,6 +864,21 @@ int pjo_index(uint32_t framing, const uint8_t* in, uint64_t len, uint64_t* rec_s
   return xl.n > cap ? PJ_ERR_CAPACITY : PJ_OK;
 }
 
+/* Record extents as the framing rules define them (start, end, "blank extent that is a record"). */
+int pjo_extents(uint32_t framing, const uint8_t* in, uint64_t len, uint64_t* s, uint64_t* e, uint8_t* blank,
+                uint64_t cap, uint64_t* n, uint32_t* doc_kind, uint64_t* doc_off) {
+  extlist xl; memset(&xl, 0, sizeof xl);
+  uint32_t dk = 0; uint64_t doff = 0;
+  if (framing == PJ_FRAMING_NDJSON) extents_ndjson(in, len, 0, 1, 1, &xl);
+  else extents_array(in, len, &xl, &dk, &doff);
+  for (size_t i = 0; i < xl.n && i < cap; ++i) { s[i] = xl.x[i].s; e[i] = xl.x[i].e; blank[i] = (uint8_t)xl.x[i].blank_err; }
+  *n = xl.n;
+  if (doc_kind) *doc_kind = dk;
+  if (doc_off) *doc_off = doff;
+  free(xl.x);
+  return xl.n > cap ? PJ_ERR_CAPACITY : PJ_OK;
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* writer (W1-W5)                                                                              */
 /* ------------------------------------------------------------------------------------------ */

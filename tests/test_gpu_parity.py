@@ -1,0 +1,236 @@
+"""Parity of the CUDA path with the CPU checker, through the C ABI. Needs a B200 (run with -m gpu)."""
+import random
+
+import numpy as np
+import pytest
+
+from golden.kat_cases import CASES
+from pj_testlib import SCHEMA_BY_NAME, abi, as_u8, nrec_bound, pj, same_result
+from test_oracle_crosscheck import mutate
+from test_oracle_kat import check_case
+
+pytestmark = pytest.mark.gpu
+
+NDJSON, ARRAY = abi.PJ_FRAMING_NDJSON, abi.PJ_FRAMING_ARRAY
+FLAG_SETS = [0, abi.PJ_GEN_ESCAPES, abi.PJ_GEN_WHITESPACE, abi.PJ_GEN_MALFORMED, abi.PJ_GEN_SPARSE,
+             abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE | abi.PJ_GEN_MALFORMED | abi.PJ_GEN_SPARSE,
+             abi.PJ_GEN_ZIPF_LISTS | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE]
+
+
+def gpu_parse_host(ctx, schema, buf, framing=NDJSON):
+    """Host buffers in, host columns out (the end-to-end route)."""
+    buf = as_u8(buf)
+    out = abi.HostColumns(schema, abi.default_caps(schema, nrec_bound(buf), buf.size))
+    ctx.parse(schema, buf, out, framing)
+    return out
+
+
+def gpu_parse_device(ctx, schema, buf, framing=NDJSON, misalign=0):
+    """Device buffers in and out."""
+    import torch
+
+    buf = as_u8(buf)
+    t = torch.empty(buf.size + misalign + 64, dtype=torch.uint8, device="cuda")
+    t[misalign:misalign + buf.size].copy_(torch.from_numpy(buf))
+    out = pj.DeviceColumns(schema, abi.default_caps(schema, nrec_bound(buf), buf.size), "cuda")
+    torch.cuda.synchronize()
+    ctx.parse(schema, t[misalign:misalign + buf.size], out, framing)
+    return out
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if c[2] == "ndjson"], ids=[c[0] for c in CASES if c[2] == "ndjson"])
+def test_known_answers_on_gpu(ctx, case):
+    check_case(lambda sch, buf, fr: gpu_parse_host(ctx, sch, buf, fr), *case)
+
+
+@pytest.mark.parametrize("schema", [1, 2, 3, 4])
+@pytest.mark.parametrize("flags", FLAG_SETS)
+def test_generated_corpora(ctx, oracle, schema, flags):
+    text = pj.gen_text(schema, 0x5EED, 0, 3000, flags)
+    want = oracle.parse(schema, text)
+    assert same_result(want, gpu_parse_device(ctx, schema, text)) == ""
+    assert same_result(want, gpu_parse_host(ctx, schema, text)) == ""
+    assert same_result(want, pj.gen_columns(schema, 0x5EED, 0, 3000, flags, text.size)) == ""
+
+
+@pytest.mark.parametrize("misalign", [0, 1, 7, 15, 16, 33])
+def test_unaligned_device_input(ctx, oracle, misalign):
+    text = pj.gen_text(4, 3, 0, 500, abi.PJ_GEN_WHITESPACE)
+    assert same_result(oracle.parse(4, text), gpu_parse_device(ctx, 4, text, misalign=misalign)) == ""
+
+
+@pytest.mark.parametrize("schema", [1, 2, 3, 4])
+def test_mutated_corpora(ctx, oracle, schema):
+    rng = random.Random(schema * 17)
+    for rnd in range(4):
+        lines = bytes(pj.gen_text(schema, 100 + rnd, 0, 1500, rng.choice([0, abi.PJ_GEN_ESCAPES, abi.PJ_GEN_SPARSE]))).split(b"\n")[:-1]
+        out = []
+        for ln in lines:
+            out.append(ln if rng.random() < 0.2 else mutate(rng, ln))
+            if rng.random() < 0.05:
+                out.append(rng.choice([b"", b"  ", b"\r", b"\t \r"]))
+        body = as_u8(b"\n".join(out) + (b"\n" if rnd % 2 else b""))
+        want = oracle.parse(schema, body)
+        assert want.n_errors > 100
+        assert same_result(want, gpu_parse_device(ctx, schema, body)) == ""
+
+
+@pytest.mark.parametrize("size", [0, 1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 16383, 16384, 16385])
+def test_tiny_and_tile_edge_inputs(ctx, oracle, size):
+    """Inputs around the 64-byte thread span and the 16 KiB tile of the record index."""
+    text = pj.gen_text(2, 5, 0, 400, 0)
+    for body in (text[:size], np.concatenate([np.full(size, 0x20, np.uint8), as_u8(b"\n"), text[:300]]),
+                 np.concatenate([text[:size], as_u8(b"\n" * 70), text[:200]])):
+        assert same_result(oracle.parse(2, body), gpu_parse_device(ctx, 2, body)) == ""
+
+
+def test_line_feeds_at_every_offset_of_a_tile(ctx, oracle):
+    rec = b'{"quantity":1}'
+    for pad in range(0, 70, 3):
+        body = as_u8((b" " * pad + rec + b"\n") * 600)
+        assert same_result(oracle.parse(2, body), gpu_parse_device(ctx, 2, body)) == ""
+
+
+def test_shards_reassemble(ctx, oracle):
+    """Byte-range shards with slack give, together, exactly the records of the whole stream."""
+    text = pj.gen_text(4, 11, 0, 4000, abi.PJ_GEN_MALFORMED | abi.PJ_GEN_ZIPF_LISTS)
+    whole = oracle.parse(4, text)
+    rng = random.Random(5)
+    for nshards in (2, 3, 8):
+        cuts = sorted(rng.sample(range(1, text.size), nshards - 1))
+        bounds = [0] + cuts + [text.size]
+        starts = []
+        for g in range(nshards):
+            lo, hi = bounds[g], bounds[g + 1]
+            slack = min(65536, text.size - hi)
+            sub = text[lo:hi + slack]
+            out = abi.HostColumns(4, abi.default_caps(4, nrec_bound(sub), sub.size))
+            ctx.parse_shard(4, sub, hi - lo, slack, g == 0, hi + slack == text.size, lo, out)
+            want = oracle.parse(4, sub, slack=slack, is_first=g == 0, is_last=hi + slack == text.size, goff=lo)
+            assert same_result(want, out) == ""
+            starts.append(out.get("rec_start"))
+        assert np.array_equal(np.concatenate(starts), whole.get("rec_start"))
+
+
+def test_slack_too_short_is_reported_per_record(ctx, oracle):
+    text = pj.gen_text(1, 12, 0, 50, 0)
+    cut = int(text.size // 2)
+    for slack in (0, 1, 10, 100):
+        sub = text[:cut + slack]
+        out = abi.HostColumns(1, abi.default_caps(1, nrec_bound(sub), sub.size))
+        ctx.parse_shard(1, sub, cut, slack, True, False, 0, out)
+        assert same_result(oracle.parse(1, sub, slack=slack, is_first=1, is_last=0), out) == ""
+        assert out.get("err_kind")[-1] == abi.PJ_E_TOO_LONG
+
+
+def test_capacity_error_reports_needed_counts(ctx, oracle):
+    text = pj.gen_text(1, 13, 0, 1000, 0)
+    want = oracle.parse(1, text)
+    caps = abi.default_caps(1, 1000, text.size)
+    small = dict(caps)
+    small[abi.COL_BY_NAME["pet_photo_data"].id] = 64
+    out = abi.HostColumns(1, small)
+    assert ctx.parse(1, text, out, allow_capacity=True) == abi.PJ_ERR_CAPACITY
+    for c in abi.schema_columns(1):
+        assert out.count(c.id) == want.count(c.id), c.name
+    few = dict(caps)
+    few[abi.COL_BY_NAME["err_kind"].id] = 10
+    out = abi.HostColumns(1, few)
+    assert ctx.parse(1, text, out, allow_capacity=True) == abi.PJ_ERR_CAPACITY
+    assert out.n_records == 1000
+    # the context stays usable
+    assert same_result(want, gpu_parse_host(ctx, 1, text)) == ""
+
+
+def test_index_records_only(ctx, oracle):
+    import torch
+
+    text = pj.gen_text(4, 14, 0, 5000, abi.PJ_GEN_WHITESPACE)
+    want = oracle.index(text)
+    rs = np.zeros(6000, np.uint64)
+    assert ctx.index_records(text, rs) == want.size and np.array_equal(rs[:want.size], want)
+    d_text = torch.from_numpy(text).cuda()
+    d_rs = torch.zeros(6000, dtype=torch.int64, device="cuda")
+    assert ctx.index_records(d_text, d_rs) == want.size
+    assert np.array_equal(d_rs[:want.size].cpu().numpy().view(np.uint64), want)
+    assert ctx.index_records(text, np.zeros(10, np.uint64), allow_capacity=True) == want.size
+
+
+# ---- writer ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("schema", [1, 2, 3, 4])
+@pytest.mark.parametrize("framing", [NDJSON, ARRAY])
+@pytest.mark.parametrize("inclusion", [abi.PJ_INCLUDE_NON_EMPTY, abi.PJ_INCLUDE_NON_NULL, abi.PJ_INCLUDE_ALWAYS])
+def test_writer_matches_checker(native, oracle, schema, framing, inclusion):
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    flags = abi.PJ_GEN_ESCAPES | abi.PJ_GEN_SPARSE | abi.PJ_GEN_MALFORMED
+    text = pj.gen_text(schema, 21, 0, 2500, flags)
+    cols = oracle.parse(schema, text)
+    want = oracle.write(schema, cols, framing, inclusion)
+    with native.Context(device=0, inclusion=inclusion) as c:
+        out = np.zeros(want.size + 16, np.uint8)
+        n = c.write(schema, cols, out, framing)
+        assert n == want.size and np.array_equal(out[:n], want)
+        dcols = pj.DeviceColumns.from_host(cols, "cuda")
+        d_out = torch.zeros(want.size + 16, dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        n = c.write(schema, dcols, d_out, framing)
+        assert n == want.size and np.array_equal(d_out[:n].cpu().numpy(), want)
+        assert c.write(schema, cols, np.zeros(100, np.uint8), framing, allow_capacity=True) == want.size
+
+
+def test_writer_empty_tables(native):
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    with native.Context(device=0) as c:
+        empty = abi.HostColumns(1, abi.default_caps(1, 0, 0))
+        c.parse(1, np.zeros(0, np.uint8), empty)
+        out = np.zeros(8, np.uint8)
+        assert c.write(1, empty, out, NDJSON) == 0
+        assert c.write(1, empty, out, ARRAY) == 2 and bytes(out[:2]) == b"[]"
+
+
+def test_canonical_text_round_trips(native, oracle):
+    """write(parse(x)) == x for the generator's compact, schema-order text."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    with native.Context(device=0, inclusion=abi.PJ_INCLUDE_NON_NULL) as c:
+        for schema in (1, 2, 3, 4):
+            text = pj.gen_text(schema, 31, 0, 4000, 0)
+            d_text = torch.from_numpy(text).cuda()
+            cols = pj.DeviceColumns(schema, abi.default_caps(schema, 4000, text.size), "cuda")
+            torch.cuda.synchronize()
+            c.parse(schema, d_text, cols)
+            assert cols.n_errors == 0
+            d_out = torch.zeros(text.size + 16, dtype=torch.uint8, device="cuda")
+            n = c.write(schema, cols, d_out)
+            assert n == text.size and torch.equal(d_out[:n], d_text)
+
+
+def test_one_million_pets(native, oracle):
+    """The benchmark workload at full size against the checker, column by column."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    n = 1_000_000
+    text = pj.gen_text(1, 0x5EED, 0, n, 0)
+    want = oracle.parse(1, text)
+    assert want.n_records == n and want.n_errors == 0
+    with native.Context(device=0, inclusion=abi.PJ_INCLUDE_NON_NULL) as c:
+        d_text = torch.from_numpy(text).cuda()
+        cols = pj.DeviceColumns.sized_for(1, n, text.size, 8 * n, "cuda")
+        torch.cuda.synchronize()
+        c.parse(1, d_text, cols)
+        assert same_result(want, cols) == ""
+        st = c.stats()
+        assert st.kernel_launches >= 5 and st.algorithmic_bytes == text.size + cols.total_bytes()
+        d_out = torch.zeros(text.size + 16, dtype=torch.uint8, device="cuda")
+        m = c.write(1, cols, d_out)
+        assert m == text.size and torch.equal(d_out[:m], d_text)
