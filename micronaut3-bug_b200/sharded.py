@@ -1,0 +1,112 @@
+"""Byte-range sharding of one NDJSON stream over the ranks of a torch.distributed group.
+
+Every rank holds one contiguous byte range of the stream in its own memory. A shard owns the
+records whose preceding LF lies in its range (rank 0 also owns the record at byte 0), so the only
+data that has to move is the head of the following shard, up to `slack` bytes, which the owner of
+the straddling record appends to its own buffer before parsing. That is one send/recv per rank;
+after the parse one all-gather of a few counters gives every rank the global position of its rows.
+No kernel ever reads another GPU's memory.
+"""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import abi
+
+N_COUNTERS = 6 + abi.PJ_MAX_COLS  # records, errors, rows[1..3], bytes, then one count per column
+
+
+class ShardedParser:
+    """Runs pj_parse_shard on every rank and stitches the results.
+
+    `engine` is anything with parse_shard(schema, buf, length, slack, is_first, is_last, global_offset, out)
+    -- a petjson Context on GPUs; the tests pass a stand-in to exercise the exchange on CPU ranks.
+    """
+
+    def __init__(self, engine, schema: int, slack: int = 64 * 1024, group=None):
+        self.engine = engine
+        self.schema = schema
+        self.slack = int(slack)
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+
+    def parse(self, buf: torch.Tensor, nbytes: int, out) -> dict:
+        """`buf` holds this rank's `nbytes` bytes followed by at least `slack` writable bytes.
+        Fills `out` with this shard's columns (offsets local to the shard) and returns the stitch:
+        global byte offset, global first record / row / arena positions, totals, and the time spent
+        on the exchange."""
+        g, r, w = self.group, self.rank, self.world
+        on_gpu = buf.is_cuda
+        t0 = time.perf_counter()
+        if on_gpu:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        # 1. shard sizes -> global byte offsets and how much of the next shard each rank may read
+        sizes_h = self._all_gather(torch.tensor([nbytes], dtype=torch.int64, device=buf.device)).view(-1).tolist()
+        goff = int(sum(sizes_h[:r]))
+        recv_n = min(self.slack, sizes_h[r + 1]) if r + 1 < w else 0
+        send_n = min(self.slack, nbytes) if r > 0 else 0
+        is_last = r == w - 1 or (r + 1 == w - 1 and sizes_h[r + 1] <= self.slack)
+        # 2. the head of the next shard becomes this shard's slack
+        ops = []
+        if send_n:
+            ops.append(dist.P2POp(dist.isend, buf[:send_n], self._peer(r - 1), group=g))
+        if recv_n:
+            ops.append(dist.P2POp(dist.irecv, buf[nbytes:nbytes + recv_n], self._peer(r + 1), group=g))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        if on_gpu:
+            ev1.record()
+            torch.cuda.current_stream().synchronize()
+            exchange_ms = ev0.elapsed_time(ev1)
+        else:
+            exchange_ms = 1e3 * (time.perf_counter() - t0)
+        # 3. the local parse
+        self.engine.parse_shard(self.schema, buf, nbytes, recv_n, r == 0, is_last, goff, out)
+        # 4. counters -> global bases
+        t1 = time.perf_counter()
+        c = torch.zeros(N_COUNTERS, dtype=torch.int64)
+        c[0], c[1] = out.n_records, out.n_errors
+        for t in (1, 2, 3):
+            c[1 + t] = out.n_rows(t)
+        c[5] = nbytes
+        for col in abi.schema_columns(self.schema):
+            c[6 + col.id] = out.count(col.id)
+        allc = self._all_gather(c.to(buf.device)).numpy()
+        gather_ms = 1e3 * (time.perf_counter() - t1)
+        before = allc[:r].sum(axis=0)
+        total = allc.sum(axis=0)
+        # an _OFF column of a shard has rows + 1 entries; globally the closing entries collapse
+        bases, totals = {}, {}
+        for col in abi.schema_columns(self.schema):
+            closing = 1 if col.shape.endswith("+1") else 0
+            bases[col.name] = int(before[6 + col.id] - closing * r)
+            totals[col.name] = int(total[6 + col.id] - closing * (w - 1))
+        return {"global_offset": goff, "first_record": int(before[0]), "total_records": int(total[0]), "total_errors": int(total[1]),
+                "first_row": {t: int(before[1 + t]) for t in (1, 2, 3)}, "total_rows": {t: int(total[1 + t]) for t in (1, 2, 3)},
+                "column_base": bases, "column_total": totals, "slack_used": recv_n, "is_last": is_last,
+                "stitch_ms": exchange_ms + gather_ms, "exchange_ms": exchange_ms, "gather_ms": gather_ms}
+
+    def _all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        """[world, len(t)] on the host."""
+        if t.is_cuda:
+            out = torch.empty(self.world * t.numel(), dtype=t.dtype, device=t.device)
+            dist.all_gather_into_tensor(out, t, group=self.group)
+            return out.view(self.world, -1).cpu()
+        parts = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(parts, t, group=self.group)
+        return torch.stack(parts)
+
+    def _peer(self, group_rank: int) -> int:
+        return dist.get_global_rank(self.group, group_rank) if self.group is not None else group_rank
+
+
+def split_even(total_bytes: int, world: int) -> list[tuple[int, int]]:
+    """Equal contiguous byte ranges [lo, hi) of a stream, one per rank."""
+    return [(total_bytes * r // world, total_bytes * (r + 1) // world) for r in range(world)]
