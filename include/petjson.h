@@ -239,11 +239,17 @@ typedef struct pj_columns {
   pj_buf col[PJ_MAX_COLS];
 } pj_columns;
 
+/* pj_options.flags */
+enum {
+  PJ_OPT_STAGED_PIPELINE = 1u << 0 /* parse with the multi-pass pipeline (index, size pass, scans, emit pass)
+                                      instead of the single-pass tile kernel; same results, kept for cross-checks */
+};
+
 typedef struct pj_options {
   int32_t device;            /* CUDA device ordinal; -1 = the calling thread's current device   */
   int32_t inclusion;         /* PJ_INCLUDE_* for pj_write                                       */
   void* stream;              /* a cudaStream_t to run on, or NULL for a stream the context owns */
-  uint32_t flags;            /* reserved, 0                                                     */
+  uint32_t flags;            /* PJ_OPT_* bits                                                   */
   uint32_t reserved;
 } pj_options;
 
@@ -255,14 +261,20 @@ typedef struct pj_call_stats {
   uint32_t reserved;
   float device_ms;          /* CUDA-event time from first launch to last, on the call's stream  */
   float main_kernel_ms;     /* CUDA-event time of the dominant kernel(s) of the call            */
-  float stage_ms[8];        /* CUDA-event time per stage. parse: [0] record index, [1] size pass,
-                               [2] counter scans, [3] emit pass, [4] closing offsets;
-                               write: [0] size pass, [1] scan, [2] emit pass                     */
+  float stage_ms[8];        /* CUDA-event time per stage. parse: [0] record index, [1] set-up between
+                               the kernels (record count read-back, state reset), [2] the tile kernel
+                               (with PJ_OPT_STAGED_PIPELINE: [1] size pass, [2] counter scans, [3] emit
+                               pass, [4] closing offsets); write: [0] size pass, [1] scan, [2] emit pass */
   uint32_t stage_launches[8]; /* kernels launched per stage                                      */
   uint64_t h2d_bytes;       /* bytes copied host->device by the call                            */
   uint64_t d2h_bytes;       /* bytes copied device->host by the call                            */
   uint64_t algorithmic_bytes; /* input bytes + bytes of every produced column (parse), or column
                                  bytes read + JSON bytes written (write)                        */
+  uint64_t fast_records;    /* parse: records decoded by the speculative word-at-a-time pass alone */
+  uint64_t phase_cycles[4]; /* parse: SM cycles summed over the blocks of the tile kernel: staging,
+                               tokenising, look-back wait, emission                              */
+  uint32_t tile_records;    /* parse: records per block of the tile kernel                       */
+  uint32_t tiles;           /* parse: blocks of the tile kernel                                   */
 } pj_call_stats;
 
 /* Library version as major * 1000 + minor. */

@@ -29,6 +29,8 @@ PJ_INCLUDE_NON_EMPTY, PJ_INCLUDE_NON_NULL, PJ_INCLUDE_ALWAYS = 0, 1, 2
 PJ_GEN_ZIPF_LISTS, PJ_GEN_ESCAPES, PJ_GEN_WHITESPACE, PJ_GEN_MALFORMED, PJ_GEN_ARRAY, PJ_GEN_SPARSE = (
     1, 2, 4, 8, 16, 32)
 
+PJ_OPT_STAGED_PIPELINE = 1
+
 PJ_MAX_COLS = 64
 
 
@@ -125,7 +127,8 @@ class pj_call_stats(C.Structure):
     _fields_ = [("kernel_launches", C.c_uint32), ("reserved", C.c_uint32), ("device_ms", C.c_float),
                 ("main_kernel_ms", C.c_float), ("stage_ms", C.c_float * 8), ("stage_launches", C.c_uint32 * 8),
                 ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
-                ("algorithmic_bytes", C.c_uint64)]
+                ("algorithmic_bytes", C.c_uint64), ("fast_records", C.c_uint64), ("phase_cycles", C.c_uint64 * 4),
+                ("tile_records", C.c_uint32), ("tiles", C.c_uint32)]
 
 
 class HostColumns:

@@ -81,6 +81,8 @@ struct pj_ctx {
   Buffer in_stage; /* device copy of a host input */
   Buffer col_stage; /* device copies of host columns */
   Buffer out_stage; /* device copy of a host output (writer) */
+  Buffer tiles;     /* look-back state of the tile kernel + its ticket */
+  bool staged = false; /* use the multi-pass pipeline instead of the tile kernel */
   DevResult* d_res = nullptr;
   DevResult* h_res = nullptr; /* pinned */
   cudaEvent_t ev[10] = {};
@@ -232,8 +234,8 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   const uint32_t nchunks = (uint32_t)((cap_records + 1 + SCAN_CHUNK - 1) / SCAN_CHUNK);
   size_t off_tile = 0;
   size_t off_cnt = align_up(off_tile + (ntiles + 1) * 4, 256);
-  size_t off_part = align_up(off_cnt + (size_t)nslots * stride * 4, 256);
-  size_t total_scratch = off_part + (size_t)nslots * nchunks * 4 + 256;
+  size_t off_part = align_up(off_cnt + (c->staged ? (size_t)nslots * stride * 4 : 0), 256);
+  size_t total_scratch = off_part + (c->staged ? (size_t)nslots * nchunks * 4 : 0) + 256;
   { pj_status st = ensure(c, &c->scratch, total_scratch); if (st) return st; }
   uint32_t* d_tile = (uint32_t*)((uint8_t*)c->scratch.p + off_tile);
   uint32_t* d_cnt = (uint32_t*)((uint8_t*)c->scratch.p + off_cnt);
@@ -253,42 +255,100 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   PJ_CUDA(c, cudaGetLastError());
   stage.next();
 
-  /* stage 1: size pass */
-  ParseArgs pa;
-  pa.in = d_in; pa.limit = limit; pa.goff = goff; pa.cap_records = cap_records;
-  pa.lf_ws = 0; pa.open_end = is_last ? 0u : 1u; pa.schema = schema; pa.slot_lo = slot_lo; pa.slot_hi = slot_hi;
-  pa.cnt = d_cnt - (size_t)slot_lo * stride; /* indexed by absolute slot */
-  pa.stride = stride; pa.rec_end = nullptr; pa.rec_blank = nullptr; pa.res = c->d_res; pa.cols = dcols;
-  const int pgrid = persistent_grid(c, cap_records, PARSE_THREADS);
-  k_parse_size<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
-  count_launch(c, 1);
-  PJ_CUDA(c, cudaGetLastError());
-  stage.next();
+  int n_stages = 5;
+  if (c->staged) {
+    /* stage 1: size pass */
+    ParseArgs pa;
+    pa.in = d_in; pa.limit = limit; pa.goff = goff; pa.cap_records = cap_records;
+    pa.lf_ws = 0; pa.open_end = is_last ? 0u : 1u; pa.schema = schema; pa.slot_lo = slot_lo; pa.slot_hi = slot_hi;
+    pa.cnt = d_cnt - (size_t)slot_lo * stride; /* indexed by absolute slot */
+    pa.stride = stride; pa.rec_end = nullptr; pa.rec_blank = nullptr; pa.res = c->d_res; pa.cols = dcols;
+    const int pgrid = persistent_grid(c, cap_records, PARSE_THREADS);
+    k_parse_size<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
+    count_launch(c, 1);
+    PJ_CUDA(c, cudaGetLastError());
+    stage.next();
 
-  /* stage 2: where every record starts in every arena */
-  { pj_status st = run_scan_u32(c, d_cnt, stride, nslots, slot_lo, cap_records, d_part, nchunks, 2); if (st) return st; }
-  k_check<<<1, 32, 0, c->stream>>>(fa);
-  count_launch(c, 2);
-  stage.next();
+    /* stage 2: where every record starts in every arena */
+    { pj_status st = run_scan_u32(c, d_cnt, stride, nslots, slot_lo, cap_records, d_part, nchunks, 2); if (st) return st; }
+    k_check<<<1, 32, 0, c->stream>>>(fa);
+    count_launch(c, 2);
+    stage.next();
 
-  /* stage 3: emit pass */
-  k_parse_emit<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
-  count_launch(c, 3);
-  PJ_CUDA(c, cudaGetLastError());
-  stage.next();
+    /* stage 3: emit pass */
+    k_parse_emit<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
+    count_launch(c, 3);
+    PJ_CUDA(c, cudaGetLastError());
+    stage.next();
 
-  /* stage 4: closing offsets */
-  k_finalize<<<1, 64, 0, c->stream>>>(fa);
-  count_launch(c, 4);
-  stage.next();
+    /* stage 4: closing offsets */
+    k_finalize<<<1, 64, 0, c->stream>>>(fa);
+    count_launch(c, 4);
+    stage.next();
+  } else {
+    /* the tile kernel needs the record count to size its grid */
+    PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+    const uint64_t N0 = c->h_res->n_records;
+    if (N0 > cap_records) {
+      out->schema = schema; out->n_records = N0; out->n_errors = 0;
+      for (int i = 0; i < nrc; ++i) out->col[rcols[i]].count = N0;
+      return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records, per-record buffers hold %llu", (unsigned long long)N0, (unsigned long long)cap_records);
+    }
+    TileArgs ta;
+    memset(&ta, 0, sizeof ta);
+    ta.in = d_in; ta.limit = limit; ta.goff = goff; ta.n_records = N0;
+    ta.lf_ws = 0; ta.open_end = is_last ? 0u : 1u; ta.schema = schema; ta.slot_lo = slot_lo; ta.slot_hi = slot_hi;
+    ta.win_bytes = TILE_WIN_BYTES; ta.tape_cap = TILE_TAPE_CAP;
+    /* as many records per tile as fit the staging window on average */
+    const uint64_t avg = N0 ? limit / N0 + 1 : 1;
+    uint32_t tile_recs = TILE_THREADS;
+    while (tile_recs > 4 && (uint64_t)tile_recs * avg + 3584 > TILE_WIN_BYTES) tile_recs >>= 1;
+    ta.tile_recs = tile_recs;
+    const uint64_t ntiles = N0 ? (N0 + tile_recs - 1) / tile_recs : 1;
+    ta.ntiles = (uint32_t)ntiles;
+    c->stats.tile_records = tile_recs; c->stats.tiles = (uint32_t)ntiles;
+    ta.rec_end = nullptr; ta.rec_blank = nullptr;
+    { pj_status st = ensure(c, &c->tiles, ntiles * sizeof(TileState) + 256); if (st) return st; }
+    ta.ticket = (uint32_t*)c->tiles.p;
+    ta.tiles = (TileState*)((uint8_t*)c->tiles.p + 128);
+    ta.res = c->d_res;
+    for (uint32_t k = 0; k < NSLOT; ++k) ta.slot_cap[k] = ~0ull;
+    for (uint32_t k = 0; k < fa.plan.n; ++k) {
+      const FinalizeItem& it = fa.plan.item[k];
+      if (it.rows_slot == 0xFF) continue;
+      uint64_t room = fa.cap_elems[it.col];
+      if (it.sentinel_slot != 0xFF) room = room ? room - 1 : 0;
+      if (room < ta.slot_cap[it.rows_slot]) ta.slot_cap[it.rows_slot] = room;
+    }
+    ta.plan = fa.plan;
+    ta.cols = dcols;
+    PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, ntiles * sizeof(TileState) + 128, c->stream));
+    const uint32_t one = 1;
+    PJ_CUDA(c, cudaMemcpyAsync(&c->d_res->ok, &one, sizeof one, cudaMemcpyHostToDevice, c->stream));
+    stage.next(); /* stage 1: set-up */
+    switch (schema) {
+      case PJ_SCHEMA_PET: k_parse_tile<PJ_SCHEMA_PET><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+      case PJ_SCHEMA_ORDER: k_parse_tile<PJ_SCHEMA_ORDER><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+      case PJ_SCHEMA_USER: k_parse_tile<PJ_SCHEMA_USER><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+      default: k_parse_tile<PJ_SCHEMA_MIXED><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+    }
+    count_launch(c, 2);
+    PJ_CUDA(c, cudaGetLastError());
+    stage.next(); /* stage 2: the tile kernel */
+    n_stages = 3;
+  }
 
   PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
   PJ_CUDA(c, cudaStreamSynchronize(c->stream));
   PJ_CUDA(c, cudaGetLastError());
-  collect_times(c, 5);
-  c->stats.main_kernel_ms = c->stats.stage_ms[1] + c->stats.stage_ms[3];
+  collect_times(c, n_stages);
+  c->stats.main_kernel_ms = c->staged ? c->stats.stage_ms[1] + c->stats.stage_ms[3] : c->stats.stage_ms[2];
 
   const DevResult& r = *c->h_res;
+  c->stats.fast_records = r.n_fast;
+  for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] = r.phase_cycles[k];
+  if (r.timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_parse: a bounded device-side wait ran out");
   const uint64_t N = r.n_records;
   out->schema = schema;
   out->n_records = N;
@@ -366,6 +426,7 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   if (!c) return PJ_ERR_NOMEM;
   c->device = dev;
   c->inclusion = opt ? opt->inclusion : PJ_INCLUDE_NON_EMPTY;
+  c->staged = opt && (opt->flags & PJ_OPT_STAGED_PIPELINE);
   DeviceGuard guard(dev);
   auto fail_create = [&](cudaError_t err, const char* what) {
     set_err(nullptr, PJ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
@@ -383,6 +444,11 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   e = cudaMallocHost(&c->h_res, sizeof(DevResult));
   if (e != cudaSuccess) return fail_create(e, "cudaMallocHost");
   for (auto& ev : c->ev) { e = cudaEventCreate(&ev); if (e != cudaSuccess) return fail_create(e, "cudaEventCreate"); }
+  e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_PET>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_ORDER>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_USER>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_MIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
+  if (e != cudaSuccess) return fail_create(e, "cudaFuncSetAttribute");
   build_schema(&c->schema);
   e = cudaMemcpyToSymbol(c_schema, &c->schema, sizeof(Schema));
   if (e != cudaSuccess) return fail_create(e, "cudaMemcpyToSymbol");
@@ -394,7 +460,7 @@ void pj_destroy(pj_ctx* c) {
   if (!c) return;
   DeviceGuard guard(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
-  for (Buffer* b : {&c->scratch, &c->in_stage, &c->col_stage, &c->out_stage}) if (b->p) cudaFree(b->p);
+  for (Buffer* b : {&c->scratch, &c->in_stage, &c->col_stage, &c->out_stage, &c->tiles}) if (b->p) cudaFree(b->p);
   if (c->d_res) cudaFree(c->d_res);
   if (c->h_res) cudaFreeHost(c->h_res);
   for (auto& ev : c->ev) if (ev) cudaEventDestroy(ev);
@@ -414,7 +480,7 @@ pj_status pj_trim(pj_ctx* c) {
   if (!c) return PJ_ERR_ARG;
   DeviceGuard guard(c->device);
   PJ_CUDA(c, cudaStreamSynchronize(c->stream));
-  for (Buffer* b : {&c->scratch, &c->in_stage, &c->col_stage, &c->out_stage}) {
+  for (Buffer* b : {&c->scratch, &c->in_stage, &c->col_stage, &c->out_stage, &c->tiles}) {
     if (b->p) { PJ_CUDA(c, cudaFree(b->p)); b->p = nullptr; b->cap = 0; }
   }
   return PJ_OK;

@@ -42,13 +42,8 @@ struct PS {
   uint32_t err;
 };
 
-PJ_HD uint32_t ld_byte(const uint8_t* a) {
-#if defined(__CUDA_ARCH__)
-  return __ldg(a);
-#else
-  return *a;
-#endif
-}
+/* generic load: the byte source may be global memory or a window staged in shared memory */
+PJ_HD uint32_t ld_byte(const uint8_t* a) { return *a; }
 PJ_HD uint32_t rd_get(const Rd& r, uint64_t p) { return p < r.limit ? ld_byte(r.in + p) : 0u; }
 
 PJ_HD bool fail(PS& s, uint32_t kind, uint64_t pos) {

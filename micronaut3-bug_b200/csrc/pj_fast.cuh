@@ -1,0 +1,608 @@
+/*
+ * pj_fast.cuh — the speculative word-at-a-time record tokeniser, instantiated on the compile-time
+ * model tables of pj_schema.h.
+ *
+ * fast_record<>() reads a record 8 bytes at a time from a window staged in shared memory and accepts
+ * it only when it is "plain": valid, every key known and met once, no null, no escape, printable
+ * ASCII strings, no date-time. Such a record never needs the byte-at-a-time machinery of
+ * pj_core.cuh, so its values, counts and the place of every string are known after ONE pass; they
+ * are kept (values in registers, strings as 8-byte tape entries in shared memory) until the record's
+ * output positions are known, and then replayed by fast_emit<>(). Anything else makes fast_record<>()
+ * return false, and the caller runs the exact generic parser on the record. fast_record<>() therefore
+ * never reports a validation failure itself: it may refuse, but what it accepts it must decode
+ * exactly as the generic parser would.
+ *
+ * All positions here are 32-bit offsets into the window; every property index, kind, column and
+ * counter slot is a template constant, so per-record state lives in registers.
+ */
+#ifndef PJ_FAST_CUH
+#define PJ_FAST_CUH
+
+#include "pj_core.cuh"
+
+namespace pj {
+
+/* A staged window: window byte k is input byte w0 + k. The staged bytes are followed by at least 32
+ * bytes of LF padding, so 16-byte look-ahead from any byte of a staged record is safe. */
+struct Win {
+  const uint8_t* s; /* window bytes; 4-byte aligned */
+  int64_t w0;       /* input offset of s[0] (can be negative by < 16 for a misaligned input) */
+};
+
+PJ_HD uint32_t wbyte(const Win& w, uint32_t p) { return w.s[p]; }
+/* 4 / 8 bytes at window offset p, little endian */
+PJ_HD uint32_t wpeek4(const Win& w, uint32_t p) {
+  const uint32_t* a = reinterpret_cast<const uint32_t*>(w.s) + (p >> 2);
+  const uint32_t sh = (p & 3u) * 8u;
+  const uint32_t x0 = a[0], x1 = a[1];
+#if defined(__CUDA_ARCH__)
+  return __funnelshift_r(x0, x1, sh);
+#else
+  return sh ? (x0 >> sh) | (x1 << (32 - sh)) : x0;
+#endif
+}
+PJ_HD uint64_t wpeek8(const Win& w, uint32_t p) {
+  const uint32_t* a = reinterpret_cast<const uint32_t*>(w.s) + (p >> 2);
+  const uint32_t sh = (p & 3u) * 8u;
+  const uint32_t x0 = a[0], x1 = a[1], x2 = a[2];
+#if defined(__CUDA_ARCH__)
+  const uint32_t lo = __funnelshift_r(x0, x1, sh), hi = __funnelshift_r(x1, x2, sh);
+#else
+  const uint32_t lo = sh ? (x0 >> sh) | (x1 << (32 - sh)) : x0, hi = sh ? (x1 >> sh) | (x2 << (32 - sh)) : x1;
+#endif
+  return (uint64_t)lo | ((uint64_t)hi << 32);
+}
+
+PJ_HD uint32_t ctz64(uint64_t x) {
+#if defined(__CUDA_ARCH__)
+  return (uint32_t)(__ffsll((long long)x) - 1);
+#else
+  return (uint32_t)__builtin_ctzll(x);
+#endif
+}
+
+#define PJ_ONES 0x0101010101010101ull
+#define PJ_HIGH 0x8080808080808080ull
+/* flag (0x80) in the lowest byte of w that equals c; flags above it may be spurious */
+PJ_HD uint64_t swar_eq(uint64_t w, uint32_t c) {
+  const uint64_t x = w ^ (PJ_ONES * c);
+  return (x - PJ_ONES) & ~x & PJ_HIGH;
+}
+/* flags for bytes that end a plain string run: '"', '\\', < 0x20, >= 0x80 (lowest flag exact) */
+PJ_HD uint64_t swar_str_special(uint64_t w) {
+  const uint64_t lt20 = (w - PJ_ONES * 0x20) & ~w & PJ_HIGH;
+  return swar_eq(w, '"') | swar_eq(w, '\\') | lt20 | (w & PJ_HIGH);
+}
+/* flags for bytes that are not ASCII digits (lowest flag exact) */
+PJ_HD uint64_t swar_nondigit(uint64_t w) { return ((w + PJ_ONES * 0x46) | (w - PJ_ONES * 0x30) | w) & PJ_HIGH; }
+/* value of 8 ASCII digits, first digit in the lowest byte */
+PJ_HD uint32_t swar_parse8(uint64_t w) {
+  w -= PJ_ONES * 0x30;
+  w = w * 10 + (w >> 8);
+  const uint64_t mask = 0x000000FF000000FFull;
+  w = ((w & mask) * 0x000F424000000064ull + ((w >> 16) & mask) * 0x0000271000000001ull) >> 32;
+  return (uint32_t)w;
+}
+/* value of the first k (1..8) digits of w */
+PJ_HD uint32_t swar_parse_k(uint64_t w, uint32_t k) {
+  if (k < 8) w = (w << (64 - 8 * k)) | ((PJ_ONES * 0x30) >> (8 * k));
+  return swar_parse8(w);
+}
+
+/* ---- tape ---------------------------------------------------------------------------------------
+ * One 64-bit entry per string of the record itself and per element of a list of objects, in reading order:
+ *   bits  0..7   slot: byte-counter slot of a string, or TAPE_ELEM for a list element
+ *   bits  8..23  j: element index inside its list
+ *   bits 24..39  len: string length in bytes / for an element: the list's item-counter slot
+ *   bits 40..63  pos: start of the string / of the element, as a window offset                     */
+enum { TAPE_ELEM = 0xFE, ELEM_STRINGS = 4 /* strings a list element may hold on the fast path */ };
+struct Tape {
+  uint64_t* e; /* entry k of this thread is e[k * stride] */
+  uint32_t stride, cap, n;
+};
+PJ_HD void tape_push(Tape& t, uint64_t v) {
+  if (t.n < t.cap) t.e[(size_t)t.n * t.stride] = v;
+  t.n++; /* n > cap afterwards means overflow */
+}
+PJ_HD uint64_t tape_entry(uint32_t slot, uint32_t j, uint32_t len, uint32_t pos) {
+  return (uint64_t)slot | ((uint64_t)j << 8) | ((uint64_t)len << 24) | ((uint64_t)pos << 40);
+}
+
+/* tokeniser position: window offsets */
+struct FastState {
+  uint32_t p, limit; /* limit: window offset of the first byte that is not the record's */
+  uint32_t lf_ws;
+};
+
+PJ_HD void fast_ws(const Win& w, FastState& f) {
+  for (;;) {
+    const uint32_t x = wbyte(w, f.p);
+    if ((x == ' ' || x == '\t' || x == '\r' || (f.lf_ws && x == '\n')) && f.p < f.limit) f.p++; else break;
+  }
+}
+
+/* A plain string at f.p (opening quote): *pos = offset of the first content byte, *len = bytes. */
+PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len) {
+  uint32_t q = f.p + 1;
+  for (;;) {
+    const uint64_t m = swar_str_special(wpeek8(w, q));
+    if (m) { q += ctz64(m) >> 3; break; }
+    q += 8;
+    if (q > f.limit) return false;
+  }
+  if (q >= f.limit || wbyte(w, q) != '"') return false;
+  const uint32_t n = q - (f.p + 1);
+  if (n > 0xFFFF) return false;
+  *pos = f.p + 1; *len = n;
+  f.p = q + 1;
+  return true;
+}
+
+/* A plain short string (key or enum literal, <= 14 bytes) at f.p, packed like the model tables. */
+PJ_HD bool fast_short(const Win& w, FastState& f, uint32_t* len, uint64_t* lo, uint64_t* hi) {
+  const uint64_t a = wpeek8(w, f.p + 1);
+  const uint64_t ma = swar_str_special(a);
+  uint32_t n;
+  uint64_t b = 0;
+  if (ma) n = ctz64(ma) >> 3;
+  else {
+    b = wpeek8(w, f.p + 9);
+    const uint64_t mb = swar_str_special(b);
+    if (!mb) return false;
+    n = 8 + (ctz64(mb) >> 3);
+  }
+  if (f.p + 1 + n >= f.limit || wbyte(w, f.p + 1 + n) != '"') return false;
+  if (n < 8) { *lo = n ? a & (~0ull >> (64 - 8 * n)) : 0; *hi = 0; }
+  else { *lo = a; *hi = n > 8 ? b & (~0ull >> (64 - 8 * (n - 8))) : 0; }
+  *len = n;
+  f.p += n + 2;
+  return true;
+}
+
+/* An integer at f.p: -?(0|[1-9][0-9]{0,18}) not followed by '.', 'e', 'E'. */
+PJ_HD bool fast_int(const Win& w, FastState& f, bool is64, int64_t* out) {
+  uint32_t p = f.p;
+  const bool neg = wbyte(w, p) == '-';
+  if (neg) p++;
+  const uint32_t first = wbyte(w, p);
+  uint64_t mag = 0;
+  uint32_t nd = 0;
+  for (;;) {
+    const uint64_t x = wpeek8(w, p);
+    const uint64_t m = swar_nondigit(x);
+    const uint32_t k = m ? ctz64(m) >> 3 : 8;
+    if (k) {
+      const uint32_t scale = k == 8 ? 100000000u : (k == 1 ? 10u : k == 2 ? 100u : k == 3 ? 1000u : k == 4 ? 10000u : k == 5 ? 100000u : k == 6 ? 1000000u : 10000000u);
+      mag = mag * scale + swar_parse_k(x, k);
+    }
+    nd += k; p += k;
+    if (k < 8) break;
+    if (nd > 19) return false;
+  }
+  if (nd == 0 || nd > 19 || (first == '0' && nd > 1)) return false;
+  const uint32_t t = wbyte(w, p);
+  if (t == '.' || (t | 0x20) == 'e') return false;
+  /* 19 digits can exceed 2^63 but not 2^64 */
+  const uint64_t lim = is64 ? (neg ? 0x8000000000000000ull : 0x7FFFFFFFFFFFFFFFull) : (neg ? 0x80000000ull : 0x7FFFFFFFull);
+  if (mag > lim) return false;
+  *out = neg ? (int64_t)(0 - mag) : (int64_t)mag;
+  f.p = p;
+  return p <= f.limit;
+}
+
+/* ---- compile-time view of one property ------------------------------------------------------------ */
+template <int OBJ, int I>
+struct FK {
+  static constexpr uint32_t kind = CObj<OBJ>::f[I].kind, col = CObj<OBJ>::f[I].col, cnt = CObj<OBJ>::f[I].cnt,
+                            child = CObj<OBJ>::f[I].child, len = CObj<OBJ>::f[I].len;
+  static constexpr uint64_t lo = CObj<OBJ>::f[I].lo, hi = CObj<OBJ>::f[I].hi;
+};
+template <int E, int I>
+struct EK {
+  static constexpr uint32_t len = CEnum<E>::lit[I].len;
+  static constexpr uint64_t lo = CEnum<E>::lit[I].lo, hi = CEnum<E>::lit[I].hi;
+};
+/* index of the property / literal with this packed name, -1 if none (an unrolled compare chain) */
+template <int OBJ, int I = 0>
+PJ_HD int match_key(uint32_t len, uint64_t lo, uint64_t hi) {
+  if constexpr (I >= CObj<OBJ>::N) return -1;
+  else {
+    if (lo == FK<OBJ, I>::lo && len == FK<OBJ, I>::len && hi == FK<OBJ, I>::hi) return I;
+    return match_key<OBJ, I + 1>(len, lo, hi);
+  }
+}
+template <int E, int I = 0>
+PJ_HD int match_enum(uint32_t len, uint64_t lo, uint64_t hi) {
+  if constexpr (I >= CEnum<E>::N) return -1;
+  else {
+    if (lo == EK<E, I>::lo && len == EK<E, I>::len && hi == EK<E, I>::hi) return I;
+    return match_enum<E, I + 1>(len, lo, hi);
+  }
+}
+/* the object embedded in OBJ (its single K_OBJ property), or OBJ_CATEGORY as a placeholder */
+template <int OBJ>
+constexpr int embedded_child() {
+  for (int i = 0; i < CObj<OBJ>::N; ++i) if (CObj<OBJ>::f[i].kind == K_OBJ) return CObj<OBJ>::f[i].child;
+  return OBJ_CATEGORY;
+}
+
+/* values of one object; only ever indexed with constants, so it lives in registers */
+struct FVals {
+  int64_t v[8];
+  uint32_t present;
+};
+
+/* Where strings go: while tokenising, onto the tape (and into the counters); while emitting a list
+ * element, straight into the arena. Arrays are indexed by constant slot numbers only. */
+struct FSink {
+  Tape* t;
+  uint32_t* cnt;         /* [NSLOT] bytes / items counted so far */
+  const DevCols* cols;   /* emit only */
+  const uint32_t* base;  /* emit only: [NSLOT] start of this record in every arena */
+  uint32_t* cur;         /* emit only: [NSLOT] bytes already emitted */
+};
+
+/* n bytes from window offset pos to dst (global memory): bytes up to 4-byte alignment of dst, then words */
+PJ_HD void copy_win(uint8_t* dst, const Win& w, uint32_t pos, uint32_t n) {
+  while (n && (reinterpret_cast<uintptr_t>(dst) & 3u)) { *dst++ = (uint8_t)wbyte(w, pos++); n--; }
+  while (n >= 4) { *reinterpret_cast<uint32_t*>(dst) = wpeek4(w, pos); dst += 4; pos += 4; n -= 4; }
+  while (n) { *dst++ = (uint8_t)wbyte(w, pos++); n--; }
+}
+
+/* Value of scalar property I of OBJ at f.p (kinds I64, I32, BOOL, STR, ENUM); j = element index of the
+ * enclosing list element (0 otherwise). DATETIME and null are left to the generic parser. */
+template <int OBJ, int I, bool EMIT>
+PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v, uint32_t j) {
+  constexpr uint32_t kind = FK<OBJ, I>::kind, slot = FK<OBJ, I>::cnt;
+  if (v.present & (1u << I)) return false; /* repeated key */
+  if constexpr (kind == K_I64 || kind == K_I32) {
+    int64_t val;
+    if (!fast_int(w, f, kind == K_I64, &val)) return false;
+    v.v[I] = val;
+  } else if constexpr (kind == K_BOOL) {
+    const uint64_t k = wpeek8(w, f.p);
+    if ((k & 0xFFFFFFFFull) == 0x65757274ull) { v.v[I] = 1; f.p += 4; }
+    else if ((k & 0xFFFFFFFFFFull) == 0x65736C6166ull) { v.v[I] = 0; f.p += 5; }
+    else return false;
+  } else if constexpr (kind == K_STR) {
+    if (wbyte(w, f.p) != '"') return false;
+    uint32_t pos, len;
+    if (!fast_string(w, f, &pos, &len)) return false;
+    if constexpr (EMIT) {
+      copy_win(colp<uint8_t>(s.cols, FK<OBJ, I>::col + 1) + s.base[slot] + s.cur[slot], w, pos, len);
+      s.cur[slot] += len;
+    } else {
+      tape_push(*s.t, tape_entry(slot, j, len, pos));
+      s.cnt[slot] += len;
+    }
+  } else if constexpr (kind == K_ENUM) {
+    if (wbyte(w, f.p) != '"') return false;
+    uint32_t len; uint64_t lo, hi;
+    if (!fast_short(w, f, &len, &lo, &hi)) return false;
+    const int e = match_enum<FK<OBJ, I>::child>(len, lo, hi);
+    if (e < 0) return false;
+    v.v[I] = e;
+  } else return false;
+  v.present |= 1u << I;
+  return true;
+}
+
+/* `ws* : ws*` */
+PJ_HD bool fast_colon(const Win& w, FastState& f) {
+  fast_ws(w, f);
+  if (wbyte(w, f.p) != ':') return false;
+  f.p++;
+  fast_ws(w, f);
+  return true;
+}
+/* key at f.p -> property index of OBJ, positioned at the value; -1: refuse */
+template <int OBJ>
+PJ_HD int fast_key(const Win& w, FastState& f) {
+  if (wbyte(w, f.p) != '"') return -1;
+  uint32_t len; uint64_t lo, hi;
+  if (!fast_short(w, f, &len, &lo, &hi)) return -1;
+  const int i = match_key<OBJ>(len, lo, hi);
+  if (i < 0 || !fast_colon(w, f)) return -1;
+  return i;
+}
+
+template <int OBJ, bool EMIT, int I = 0>
+PJ_HD bool flat_dispatch(int i, const Win& w, FastState& f, FSink& s, FVals& v, uint32_t j) {
+  if constexpr (I >= CObj<OBJ>::N) return false;
+  else {
+    if (i == I) {
+      if constexpr (FK<OBJ, I>::kind <= K_ENUM) return fast_scalar<OBJ, I, EMIT>(w, f, s, v, j);
+      else return false;
+    }
+    return flat_dispatch<OBJ, EMIT, I + 1>(i, w, f, s, v, j);
+  }
+}
+/* Flat object (Category, Tag) at f.p == '{'. */
+template <int OBJ, bool EMIT>
+PJ_HD bool fast_flat(const Win& w, FastState& f, FSink& s, FVals& v, uint32_t j) {
+  v.present = 0;
+  f.p++;
+  fast_ws(w, f);
+  if (wbyte(w, f.p) == '}') { f.p++; return true; }
+  for (;;) {
+    const int i = fast_key<OBJ>(w, f);
+    if (i < 0) return false;
+    if (!flat_dispatch<OBJ, EMIT>(i, w, f, s, v, j)) return false;
+    fast_ws(w, f);
+    const uint32_t x = wbyte(w, f.p);
+    if (x == ',') { f.p++; fast_ws(w, f); continue; }
+    if (x == '}') { f.p++; return true; }
+    return false;
+  }
+}
+
+/* Property I of a model root at f.p: scalars as above; an embedded object into cv; lists entry by entry. */
+template <int OBJ, int I = 0>
+PJ_HD bool root_dispatch(int i, const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv) {
+  if constexpr (I >= CObj<OBJ>::N) return false;
+  else {
+    if (i == I) {
+      constexpr uint32_t kind = FK<OBJ, I>::kind, cnt = FK<OBJ, I>::cnt;
+      if constexpr (kind <= K_ENUM) return fast_scalar<OBJ, I, false>(w, f, s, v, 0);
+      else if constexpr (kind == K_DATETIME) return false;
+      else {
+        if (v.present & (1u << I)) return false;
+        if constexpr (kind == K_OBJ) {
+          if (wbyte(w, f.p) != '{' || !fast_flat<FK<OBJ, I>::child, false>(w, f, s, cv, 0)) return false;
+        } else {
+          if (wbyte(w, f.p) != '[') return false;
+          f.p++;
+          fast_ws(w, f);
+          uint32_t j = 0;
+          if (wbyte(w, f.p) == ']') f.p++;
+          else {
+            for (;;) {
+              if (j >= 0xFFFF) return false;
+              if constexpr (kind == K_LIST_STR) {
+                if (wbyte(w, f.p) != '"') return false;
+                uint32_t pos, len;
+                if (!fast_string(w, f, &pos, &len)) return false;
+                tape_push(*s.t, tape_entry(cnt + 1, j, len, pos));
+                s.cnt[cnt + 1] += len;
+              } else {
+                /* one entry per element: where it starts. Its strings are only counted now; the element is
+                   tokenised again when it is emitted. */
+                if (wbyte(w, f.p) != '{') return false;
+                tape_push(*s.t, tape_entry(TAPE_ELEM, j, cnt, f.p));
+                Tape nul;
+                nul.e = nullptr; nul.stride = 0; nul.cap = 0; nul.n = 0;
+                FSink es = s;
+                es.t = &nul;
+                FVals ev;
+                if (!fast_flat<FK<OBJ, I>::child, false>(w, f, es, ev, j) || nul.n > ELEM_STRINGS) return false;
+              }
+              j++;
+              fast_ws(w, f);
+              const uint32_t y = wbyte(w, f.p);
+              if (y == ',') { f.p++; fast_ws(w, f); continue; }
+              if (y == ']') { f.p++; break; }
+              return false;
+            }
+          }
+          s.cnt[cnt] = j;
+        }
+        v.present |= 1u << I;
+        return true;
+      }
+    }
+    return root_dispatch<OBJ, I + 1>(i, w, f, s, v, cv);
+  }
+}
+
+/* Members of a model root. f.p is after `{ ws*`, or at the value of property `pending` (>= 0) whose key
+ * was read already. Ends after the closing brace. */
+template <int OBJ>
+PJ_HD bool fast_root(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv, int pending) {
+  if (pending < 0 && wbyte(w, f.p) == '}') { f.p++; return true; }
+  for (;;) {
+    int i = pending;
+    pending = -1;
+    if (i < 0) { i = fast_key<OBJ>(w, f); if (i < 0) return false; }
+    if (!root_dispatch<OBJ>(i, w, f, s, v, cv)) return false;
+    fast_ws(w, f);
+    const uint32_t x = wbyte(w, f.p);
+    if (x == ',') { f.p++; fast_ws(w, f); continue; }
+    if (x == '}') { f.p++; return true; }
+    return false;
+  }
+}
+
+template <int SCHEMA> struct RootOf { static constexpr int obj = SCHEMA == PJ_SCHEMA_PET ? (int)OBJ_PET : (SCHEMA == PJ_SCHEMA_ORDER ? (int)OBJ_ORDER : (int)OBJ_USER); };
+
+/* One record at window offset `start`, ending before window offset `limit`. On success: model in
+ * *type_out, root values in v, the embedded object's in cv, counts in cnt[slot] (all NSLOT entries
+ * are reset), strings and list elements on the tape. */
+template <int SCHEMA>
+PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf_ws, uint32_t open_end, uint32_t* type_out,
+                       FVals& v, FVals& cv, uint32_t* cnt, Tape& t) {
+  FastState f;
+  f.p = start; f.limit = limit; f.lf_ws = lf_ws;
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = 0;
+  t.n = 0;
+  v.present = 0; cv.present = 0;
+  FSink s;
+  s.t = &t; s.cnt = cnt; s.cols = nullptr; s.base = nullptr; s.cur = nullptr;
+  fast_ws(w, f);
+  if (f.p >= limit || wbyte(w, f.p) != '{') return false;
+  f.p++;
+  fast_ws(w, f);
+  uint32_t type;
+  if constexpr (SCHEMA != PJ_SCHEMA_MIXED) {
+    constexpr int OBJ = RootOf<SCHEMA>::obj;
+    if (!fast_root<OBJ>(w, f, s, v, cv, -1)) return false;
+    if ((v.present & CObj<OBJ>::required) != (uint32_t)CObj<OBJ>::required) return false;
+    type = SCHEMA;
+  } else {
+    /* only the common `id` may precede the deciding key on this path */
+    bool have_id = false;
+    int64_t early_id = 0;
+    for (;;) {
+      if (wbyte(w, f.p) != '"') return false;
+      uint32_t len; uint64_t lo, hi;
+      if (!fast_short(w, f, &len, &lo, &hi) || !fast_colon(w, f)) return false;
+      const int kp = match_key<OBJ_PET>(len, lo, hi), ko = match_key<OBJ_ORDER>(len, lo, hi), ku = match_key<OBJ_USER>(len, lo, hi);
+      const int owners = (kp >= 0) + (ko >= 0) + (ku >= 0);
+      if (owners == 3) {
+        if (have_id || !fast_int(w, f, true, &early_id)) return false;
+        have_id = true;
+        fast_ws(w, f);
+        if (wbyte(w, f.p) != ',') return false;
+        f.p++;
+        fast_ws(w, f);
+        continue;
+      }
+      if (owners != 1) return false; /* unknown key, or `status` before the deciding key */
+      if (have_id) { v.v[0] = early_id; v.present = 1; }
+      if (kp >= 0) {
+        type = PJ_TYPE_PET;
+        if (!fast_root<OBJ_PET>(w, f, s, v, cv, kp)) return false;
+        if ((v.present & CObj<OBJ_PET>::required) != (uint32_t)CObj<OBJ_PET>::required) return false;
+      } else if (ko >= 0) {
+        type = PJ_TYPE_ORDER;
+        if (!fast_root<OBJ_ORDER>(w, f, s, v, cv, ko)) return false;
+      } else {
+        type = PJ_TYPE_USER;
+        if (!fast_root<OBJ_USER>(w, f, s, v, cv, ku)) return false;
+      }
+      break;
+    }
+  }
+  fast_ws(w, f);
+  if (f.p > limit) return false;
+  if (f.p < limit) { if (lf_ws || wbyte(w, f.p) != '\n') return false; }
+  else if (open_end) return false;
+  if (t.n > t.cap) return false;
+  if constexpr (SCHEMA == PJ_SCHEMA_MIXED) {
+    if (type == PJ_TYPE_PET) cnt[SLOT_ROWS_PET] = 1; else if (type == PJ_TYPE_ORDER) cnt[SLOT_ROWS_ORD] = 1; else cnt[SLOT_ROWS_USR] = 1;
+  }
+  *type_out = type;
+  return true;
+}
+
+/* ---- emission -------------------------------------------------------------------------------------- */
+/* Fixed-width values, string offsets and list offsets of one object at `row`. ELEM: the object is a
+ * list element whose string offsets were stored before it was tokenised (see emit_element). */
+template <int OBJ, bool ELEM, int I = 0>
+PJ_HD void store_vals(const DevCols* c, const FVals& v, uint64_t row, const uint32_t* base) {
+  if constexpr (I == 0) colp<uint8_t>(c, CObj<OBJ>::present_col)[row] = (uint8_t)v.present;
+  if constexpr (I < CObj<OBJ>::N) {
+    constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col, cnt = FK<OBJ, I>::cnt;
+    const bool pr = (v.present >> I) & 1;
+    if constexpr (kind == K_I64) colp<int64_t>(c, col)[row] = pr ? v.v[I] : 0;
+    else if constexpr (kind == K_I32) colp<int32_t>(c, col)[row] = pr ? (int32_t)v.v[I] : 0;
+    else if constexpr (kind == K_BOOL) colp<uint8_t>(c, col)[row] = pr ? (uint8_t)v.v[I] : 0;
+    else if constexpr (kind == K_ENUM) colp<uint8_t>(c, col)[row] = pr ? (uint8_t)v.v[I] : 255;
+    else if constexpr (kind == K_STR) { if constexpr (!ELEM) colp<uint32_t>(c, col)[row] = base[cnt]; }
+    else if constexpr (kind == K_LIST_STR || kind == K_LIST_OBJ) colp<uint32_t>(c, col)[row] = base[cnt];
+    store_vals<OBJ, ELEM, I + 1>(c, v, row, base);
+  }
+}
+/* offsets of the strings of a list element = the cursors as they stand before the element is emitted */
+template <int OBJ, int I = 0>
+PJ_HD void store_elem_str_offsets(const DevCols* c, uint64_t row, const uint32_t* base, const uint32_t* cur) {
+  if constexpr (I < CObj<OBJ>::N) {
+    if constexpr (FK<OBJ, I>::kind == K_STR) colp<uint32_t>(c, FK<OBJ, I>::col)[row] = base[FK<OBJ, I>::cnt] + cur[FK<OBJ, I>::cnt];
+    store_elem_str_offsets<OBJ, I + 1>(c, row, base, cur);
+  }
+}
+
+/* a string of the object embedded in the root (its properties are flat) */
+template <int CH, int I = 0>
+PJ_HD void replay_child(const Win& w, const DevCols* c, uint32_t slot, uint32_t len, uint32_t pos, const uint32_t* base, uint32_t* cur,
+                        bool* done) {
+  if constexpr (I < CObj<CH>::N) {
+    if constexpr (FK<CH, I>::kind == K_STR) {
+      constexpr uint32_t cnt = FK<CH, I>::cnt;
+      if (slot == cnt) { copy_win(colp<uint8_t>(c, FK<CH, I>::col + 1) + base[cnt] + cur[cnt], w, pos, len); cur[cnt] += len; *done = true; return; }
+    }
+    replay_child<CH, I + 1>(w, c, slot, len, pos, base, cur, done);
+  }
+}
+
+/* One tape entry of a record whose root is OBJ: finds the property it belongs to (an unrolled chain
+ * over the properties, constants all the way) and emits it. */
+template <int OBJ, int I = 0>
+PJ_HD void replay_entry(const Win& w, const DevCols* c, uint32_t slot, uint32_t j, uint32_t len, uint32_t pos, const uint32_t* base,
+                        uint32_t* cur) {
+  if constexpr (I < CObj<OBJ>::N) {
+    constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col, cnt = FK<OBJ, I>::cnt;
+    if constexpr (kind == K_STR) {
+      if (slot == cnt) { copy_win(colp<uint8_t>(c, col + 1) + base[cnt] + cur[cnt], w, pos, len); cur[cnt] += len; return; }
+    } else if constexpr (kind == K_LIST_STR) {
+      if (slot == cnt + 1) {
+        colp<uint32_t>(c, col + 1)[(uint64_t)base[cnt] + j] = base[cnt + 1] + cur[cnt + 1];
+        copy_win(colp<uint8_t>(c, col + 2) + base[cnt + 1] + cur[cnt + 1], w, pos, len);
+        cur[cnt + 1] += len;
+        return;
+      }
+    } else if constexpr (kind == K_OBJ) {
+      /* strings of the embedded object: its properties are flat */
+      constexpr int CH = FK<OBJ, I>::child;
+      bool done = false;
+      replay_child<CH>(w, c, slot, len, pos, base, cur, &done);
+      if (done) return;
+    } else if constexpr (kind == K_LIST_OBJ) {
+      if (slot == TAPE_ELEM && len == cnt) {
+        constexpr int E = FK<OBJ, I>::child;
+        const uint64_t erow = (uint64_t)base[cnt] + j;
+        store_elem_str_offsets<E>(c, erow, base, cur);
+        FastState f;
+        f.p = pos; f.limit = 0xFFFFFFFFu; f.lf_ws = 1;
+        FSink s;
+        s.t = nullptr; s.cnt = nullptr; s.cols = c; s.base = base; s.cur = cur;
+        FVals ev;
+        fast_flat<E, true>(w, f, s, ev, j);
+        store_vals<E, true>(c, ev, erow, base);
+        return;
+      }
+    }
+    replay_entry<OBJ, I + 1>(w, c, slot, j, len, pos, base, cur);
+  }
+}
+/* columns of the embedded object of OBJ (if it has one) at the root's row */
+template <int OBJ, int I = 0>
+PJ_HD void store_embedded(const DevCols* c, const FVals& v, const FVals& cv, uint64_t row, const uint32_t* base) {
+  if constexpr (I < CObj<OBJ>::N) {
+    if constexpr (FK<OBJ, I>::kind == K_OBJ) {
+      FVals z = cv;
+      if (!((v.present >> I) & 1)) z.present = 0;
+      store_vals<FK<OBJ, I>::child, false>(c, z, row, base);
+    }
+    store_embedded<OBJ, I + 1>(c, v, cv, row, base);
+  }
+}
+
+template <int OBJ>
+PJ_HD void emit_root(const Win& w, const DevCols* c, const FVals& v, const FVals& cv, const Tape& t, uint64_t row, const uint32_t* base) {
+  store_vals<OBJ, false>(c, v, row, base);
+  store_embedded<OBJ>(c, v, cv, row, base);
+  uint32_t cur[NSLOT];
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) cur[k] = 0;
+  for (uint32_t k = 0; k < t.n; ++k) {
+    const uint64_t e = t.e[(size_t)k * t.stride];
+    replay_entry<OBJ>(w, c, (uint32_t)(e & 0xFF), (uint32_t)(e >> 8) & 0xFFFF, (uint32_t)(e >> 24) & 0xFFFF, (uint32_t)(e >> 40), base, cur);
+  }
+}
+
+/* Replays a record accepted by fast_record<SCHEMA>(): every column of its row, then the tape.
+ * base[slot] = the record's start in every arena / child table. */
+template <int SCHEMA>
+PJ_HD void fast_emit(const Win& w, const DevCols* c, uint32_t type, const FVals& v, const FVals& cv, const Tape& t, const uint32_t* base,
+                     uint64_t rec_index) {
+  if constexpr (SCHEMA != PJ_SCHEMA_MIXED) emit_root<RootOf<SCHEMA>::obj>(w, c, v, cv, t, rec_index, base);
+  else {
+    if (type == PJ_TYPE_PET) emit_root<OBJ_PET>(w, c, v, cv, t, base[SLOT_ROWS_PET], base);
+    else if (type == PJ_TYPE_ORDER) emit_root<OBJ_ORDER>(w, c, v, cv, t, base[SLOT_ROWS_ORD], base);
+    else emit_root<OBJ_USER>(w, c, v, cv, t, base[SLOT_ROWS_USR], base);
+  }
+}
+
+}  // namespace pj
+#endif

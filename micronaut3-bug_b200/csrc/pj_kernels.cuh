@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include "pj_core.cuh"
+#include "pj_fast.cuh"
 #include "pj_index.cuh"
 #include "pj_write_core.cuh"
 
@@ -32,7 +33,11 @@ struct DevResult {
   unsigned long long out_bytes; /* writer: JSON bytes */
   unsigned long long doc_err_off;
   uint32_t doc_err_kind;
-  uint32_t ok; /* every output fits its buffer */
+  uint32_t ok;      /* every output fits its buffer */
+  uint32_t timeout; /* a bounded wait ran out */
+  uint32_t pad;
+  unsigned long long n_fast;  /* records decoded by the speculative pass alone */
+  unsigned long long phase_cycles[4]; /* tile kernel, summed over blocks: staging, tokenising, look-back, emit */
 };
 
 static constexpr int INDEX_THREADS = 256;
@@ -374,6 +379,300 @@ __global__ void __launch_bounds__(PARSE_THREADS) k_write_emit(const __grid_const
     WOut w; w.dst = a.out + at; w.n = 0;
     write_record<true>(c_schema, &a.cols, type, row, a.inclusion, w);
     a.out[at + w.n] = a.array ? (uint8_t)(at + w.n + 1 == total ? ']' : ',') : (uint8_t)'\n';
+  }
+}
+
+
+/* ================================================================================================
+ * Single-pass tile kernel
+ *
+ * One thread block takes TILE_THREADS consecutive records (a "tile"), stages their bytes in shared
+ * memory with coalesced 16-byte loads, lets every thread tokenise its record ONCE (speculative
+ * word-at-a-time pass of pj_fast.cuh, exact generic parser as fallback), scans the per-record counts
+ * inside the block, obtains the tile's start in every arena by a decoupled look-back over the tiles
+ * before it, and then emits every column. Input bytes are read from HBM once, every output byte is
+ * written once.
+ *
+ * Look-back protocol (per tile: flag, aggregate[NSLOT], inclusive[NSLOT]): a tile publishes its
+ * aggregate (flag 1) as soon as its records are sized and its inclusive prefix (flag 2) once it has
+ * found the nearest predecessor with flag 2 and added the aggregates in between. Tiles take their
+ * index from an atomic ticket, so every predecessor of a running tile is itself running or done and
+ * the waits cannot deadlock. Every wait is bounded: after PJ_SPIN_LIMIT_NS it raises res->timeout,
+ * which all other waits also watch, and the block finishes without emitting.
+ * ================================================================================================ */
+static constexpr int TILE_THREADS = 128;
+static constexpr unsigned long long PJ_SPIN_LIMIT_NS = 2000000000ull; /* 2 s */
+static constexpr uint32_t TILE_WIN_BYTES = 41 * 1024;  /* staged input bytes per tile */
+static constexpr uint32_t TILE_TAPE_CAP = 12;          /* tape entries per record before the generic parser takes over */
+static constexpr uint32_t TILE_SMEM_BYTES = ((TILE_WIN_BYTES + 64 + 15) & ~15u) + TILE_TAPE_CAP * TILE_THREADS * 8;
+
+struct TileState {
+  uint32_t flag; /* 0 nothing, 1 aggregate valid, 2 inclusive valid */
+  uint32_t agg[NSLOT];
+  uint32_t inc[NSLOT];
+  uint32_t pad;
+};
+static_assert(sizeof(TileState) == 128, "one tile state per 128-byte line");
+
+struct TileArgs {
+  const uint8_t* in;
+  uint64_t limit, goff, n_records;
+  uint32_t lf_ws, open_end, schema, slot_lo, slot_hi;
+  uint32_t tile_recs, ntiles, win_bytes, tape_cap;
+  const uint64_t* rec_end;  /* array framing: end of every extent, else null */
+  const uint8_t* rec_blank; /* array framing: extent without a value */
+  TileState* tiles;
+  uint32_t* ticket;
+  DevResult* res;
+  uint64_t slot_cap[NSLOT]; /* largest total per slot the caller's buffers can take */
+  FinalizePlan plan;
+  DevCols cols;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+/* Exclusive prefix of this tile over all earlier tiles, for slot = lane (lanes >= NSLOT idle). Warp 0 only.
+ * Returns false when a wait ran out. */
+__device__ __forceinline__ bool tile_lookback(const TileArgs& a, uint32_t tile, uint32_t lane, uint32_t* excl_out) {
+  uint32_t excl = 0;
+  int64_t j = (int64_t)tile - 1;
+  const unsigned long long t0 = global_ns();
+  while (j >= 0) {
+    /* lane L looks at tile j - L */
+    const int64_t mine = j - lane;
+    uint32_t f = 2;
+    uint32_t inc_mask, ready_mask, need;
+    for (;;) {
+      if (mine >= 0) f = ld_acquire_u32(&a.tiles[mine].flag);
+      inc_mask = __ballot_sync(0xFFFFFFFFu, f == 2);
+      ready_mask = __ballot_sync(0xFFFFFFFFu, f != 0);
+      const uint32_t first_inc = inc_mask ? (uint32_t)(__ffs((int)inc_mask) - 1) : 32u;
+      need = first_inc >= 31 ? 0xFFFFFFFFu : ((2u << first_inc) - 1u);
+      if ((ready_mask & need) == need) break;
+      uint32_t give_up = 0;
+      if (lane == 0) give_up = (global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)&a.res->timeout;
+      give_up = __shfl_sync(0xFFFFFFFFu, give_up, 0);
+      if (give_up) { if (lane == 0) atomicExch(&a.res->timeout, 1u); return false; }
+      __nanosleep(100);
+    }
+    __threadfence();
+    __syncwarp();
+    const uint32_t first_inc = inc_mask ? (uint32_t)(__ffs((int)inc_mask) - 1) : 32u;
+    const uint32_t steps = first_inc < 32 ? first_inc + 1 : 32;
+    if (lane < NSLOT) {
+      for (uint32_t L = 0; L < steps; ++L) {
+        const int64_t tj = j - L;
+        if (tj < 0) break; /* before the first tile: nothing to add (its lane reported "inclusive") */
+        const TileState* ts = &a.tiles[tj];
+        excl += __ldcg(L == first_inc ? &ts->inc[lane] : &ts->agg[lane]);
+      }
+    }
+    if (first_inc < 32) break;
+    j -= 32;
+  }
+  *excl_out = excl;
+  return true;
+}
+
+template <int SCHEMA> struct SlotRange {
+  static constexpr uint32_t lo = SCHEMA == PJ_SCHEMA_PET ? (uint32_t)SLOT_PET_CAT_NAME : (SCHEMA == PJ_SCHEMA_USER ? (uint32_t)SLOT_USR_STR0 : 0u);
+  static constexpr uint32_t hi = SCHEMA == PJ_SCHEMA_PET ? (uint32_t)SLOT_USR_STR0 : (SCHEMA == PJ_SCHEMA_ORDER ? 0u : (uint32_t)NSLOT);
+};
+
+template <int SCHEMA>
+__global__ void __launch_bounds__(TILE_THREADS) k_parse_tile(const __grid_constant__ TileArgs a) {
+  constexpr uint32_t LO = SlotRange<SCHEMA>::lo, HI = SlotRange<SCHEMA>::hi;
+  constexpr uint32_t NWARPS = TILE_THREADS / 32;
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ uint32_t sh_warp[NSLOT][NWARPS];
+  __shared__ uint32_t sh_tot[NSLOT], sh_base[NSLOT];
+  __shared__ uint32_t sh_tile, sh_ok;
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint8_t* win = smem;
+  uint64_t* tape = reinterpret_cast<uint64_t*>(smem + ((a.win_bytes + 64 + 15) & ~15u));
+
+  if (tid == 0) sh_tile = atomicAdd(a.ticket, 1u);
+  __syncthreads();
+  const uint32_t tile = sh_tile;
+  if (tile >= a.ntiles) return;
+  const uint64_t N = a.n_records;
+  const uint64_t r0 = (uint64_t)tile * a.tile_recs;
+  const uint64_t left = N > r0 ? N - r0 : 0;
+  const uint32_t nrec = left < a.tile_recs ? (uint32_t)left : a.tile_recs;
+  const uint64_t* rec_start = colp<uint64_t>(&a.cols, PJ_COL_REC_START);
+  const bool active = tid < nrec;
+  const uint64_t i = r0 + tid;
+  const uint64_t start = active ? rec_start[i] - a.goff : 0;
+  const uint64_t my_limit = (active && a.rec_end) ? a.rec_end[i] : a.limit;
+
+  const long long c0 = clock64();
+  /* ---- stage the tile's bytes ------------------------------------------------------------------ */
+  bool fits = false;
+  int64_t w0 = 0;
+  if (nrec) {
+    const uint64_t span_lo = rec_start[r0] - a.goff;
+    uint64_t span_hi;
+    if (a.rec_end) span_hi = a.rec_end[r0 + nrec - 1];
+    else span_hi = r0 + nrec < N ? rec_start[r0 + nrec] - a.goff : a.limit;
+    const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(a.in + span_lo) & 15u);
+    w0 = (int64_t)span_lo - mis;
+    const uint64_t copy_hi = a.limit < span_hi + 32 ? a.limit : span_hi + 32;
+    const uint64_t nbytes = (uint64_t)((int64_t)copy_hi - w0);
+    fits = nbytes + 64 <= a.win_bytes;
+    if (fits) {
+      const uint4* src = reinterpret_cast<const uint4*>(a.in + w0);
+      uint4* dst = reinterpret_cast<uint4*>(win);
+      const uint32_t n16 = (uint32_t)((nbytes + 15) >> 4);
+      for (uint32_t k = tid; k < n16; k += TILE_THREADS) dst[k] = __ldg(src + k);
+      __syncthreads();
+      if (tid < 32) win[nbytes + tid] = '\n';
+    }
+  }
+  __syncthreads();
+
+  const long long c1 = clock64();
+  /* ---- tokenise every record once ------------------------------------------------------------------ */
+  Win w;
+  w.s = win; w.w0 = w0;
+  Tape tp;
+  tp.e = tape + tid; tp.stride = TILE_THREADS; tp.cap = a.tape_cap; tp.n = 0;
+  uint32_t cnt[NSLOT], base[NSLOT];
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) { cnt[k] = 0; base[k] = 0; }
+  FVals v, cv;
+  uint32_t type = PJ_TYPE_NONE, err = 0, fast = 0;
+  if (active) {
+    const bool blank = a.rec_blank && a.rec_blank[i];
+    if (fits && !blank) {
+      const uint64_t rel = (uint64_t)((int64_t)my_limit - w0);
+      const uint32_t lim32 = rel > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)rel;
+      fast = fast_record<SCHEMA>(w, (uint32_t)((int64_t)start - w0), lim32, a.lf_ws, a.open_end, &type, v, cv, cnt, tp) ? 1u : 0u;
+    }
+    if (!fast) {
+      Rd r;
+      r.in = fits ? win - w0 : a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end; r.limit = my_limit;
+      PS s;
+      s.p = start; s.err = 0; s.err_pos = 0;
+      Out<false> so;
+      so.cols = &a.cols;
+      if (blank) { fail(s, PJ_E_SYNTAX, my_limit); type = PJ_TYPE_NONE; }
+      else type = parse_record<false>(c_schema, r, s, a.schema, so, i);
+      err = s.err;
+#pragma unroll
+      for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = (k >= LO && k < HI && !err) ? so.cnt[k] : 0u;
+      if (err) type = PJ_TYPE_NONE;
+      colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = err ? (uint32_t)(s.err_pos - start) : 0u;
+    } else colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = 0u;
+    colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i] = (uint8_t)err;
+    if (SCHEMA == PJ_SCHEMA_MIXED) colp<uint8_t>(&a.cols, PJ_COL_REC_TYPE)[i] = (uint8_t)type;
+  }
+  {
+    uint32_t packed = (err ? 1u : 0u) | (fast << 16);
+    for (int d = 16; d; d >>= 1) packed += __shfl_down_sync(0xFFFFFFFFu, packed, d);
+    if (lane == 0 && (packed & 0xFFFF)) atomicAdd(&a.res->n_errors, (unsigned long long)(packed & 0xFFFF));
+    if (lane == 0 && (packed >> 16)) atomicAdd(&a.res->n_fast, (unsigned long long)(packed >> 16));
+  }
+
+  /* ---- positions: scan inside the tile (two barriers for all counters), then look back ------------- */
+  if (tid < NSLOT) sh_tot[tid] = 0;
+#pragma unroll
+  for (uint32_t k = LO; k < HI; ++k) {
+    const uint32_t inc = warp_incl_scan(cnt[k]);
+    if (lane == 31) sh_warp[k][warp] = inc;
+    base[k] = inc - cnt[k];
+  }
+  __syncthreads();
+  const long long c2 = clock64();
+#pragma unroll
+  for (uint32_t k = LO; k < HI; ++k) {
+#pragma unroll
+    for (uint32_t q = 0; q < NWARPS; ++q) if (q < warp) base[k] += sh_warp[k][q];
+  }
+  if (warp == 0) {
+    TileState* me = &a.tiles[tile];
+    uint32_t mine = 0;
+    if (lane >= LO && lane < HI) {
+#pragma unroll
+      for (uint32_t q = 0; q < NWARPS; ++q) mine += sh_warp[lane][q];
+    }
+    if (lane < NSLOT) { sh_tot[lane] = mine; me->agg[lane] = mine; if (tile == 0) me->inc[lane] = mine; }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) st_release_u32(&me->flag, tile == 0 ? 2u : 1u);
+    uint32_t excl = 0;
+    const bool ok = tile_lookback(a, tile, lane, &excl);
+    if (tile != 0) {
+      if (lane < NSLOT) me->inc[lane] = excl + mine;
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) st_release_u32(&me->flag, 2u);
+    }
+    if (lane < NSLOT) sh_base[lane] = excl;
+    /* does the whole tile fit the caller's buffers? (totals only grow, so the last tile's verdict is the call's) */
+    const bool over = lane < NSLOT && (uint64_t)excl + mine > a.slot_cap[lane];
+    const uint32_t any_over = __ballot_sync(0xFFFFFFFFu, over);
+    if (lane == 0) {
+      sh_ok = ok && !any_over;
+      if (any_over) a.res->ok = 0;
+    }
+    if (tile == a.ntiles - 1 && lane < NSLOT) a.res->total[lane] = (unsigned long long)excl + mine;
+  }
+  __syncthreads();
+  const long long c3 = clock64();
+  if (!sh_ok) return;
+
+  /* ---- emit ---------------------------------------------------------------------------------------- */
+  if (active) {
+#pragma unroll
+    for (uint32_t k = LO; k < HI; ++k) base[k] += sh_base[k];
+    if (SCHEMA == PJ_SCHEMA_MIXED) {
+      const uint32_t row = type == PJ_TYPE_PET ? base[SLOT_ROWS_PET] : (type == PJ_TYPE_ORDER ? base[SLOT_ROWS_ORD] : base[SLOT_ROWS_USR]);
+      colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = type == PJ_TYPE_NONE ? 0xFFFFFFFFu : row;
+    }
+    if (fast) fast_emit<SCHEMA>(w, &a.cols, type, v, cv, tp, base, i);
+    else {
+      Out<true> o;
+      o.cols = &a.cols;
+#pragma unroll
+      for (uint32_t k = 0; k < NSLOT; ++k) { o.base[k] = base[k]; o.room[k] = cnt[k]; }
+      if (err) {
+        if (SCHEMA != PJ_SCHEMA_MIXED) store_absent<true>(c_schema, a.schema, o, i);
+      } else {
+        Rd r;
+        r.in = fits ? win - w0 : a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end; r.limit = my_limit;
+        PS s;
+        s.p = start; s.err = 0; s.err_pos = 0;
+        parse_record<true>(c_schema, r, s, a.schema, o, i);
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const long long c4 = clock64();
+    atomicAdd(&a.res->phase_cycles[0], (unsigned long long)(c1 - c0));
+    atomicAdd(&a.res->phase_cycles[1], (unsigned long long)(c2 - c1));
+    atomicAdd(&a.res->phase_cycles[2], (unsigned long long)(c3 - c2));
+    atomicAdd(&a.res->phase_cycles[3], (unsigned long long)(c4 - c3));
+  }
+  /* the last tile closes the offset columns */
+  if (tile == a.ntiles - 1 && tid < a.plan.n) {
+    const FinalizeItem it = a.plan.item[tid];
+    if (it.sentinel_slot != 0xFF) {
+      const uint64_t rows = it.rows_slot == 0xFF ? N : (uint64_t)sh_base[it.rows_slot] + sh_tot[it.rows_slot];
+      colp<uint32_t>(&a.cols, it.col)[rows] = sh_base[it.sentinel_slot] + sh_tot[it.sentinel_slot];
+    }
   }
 }
 

@@ -56,6 +56,10 @@ struct EnumDesc {
 struct Schema {
   ObjDesc obj[NOBJ];
   EnumDesc en[2]; /* 0: Pet.status, 1: Order.status */
+  /* per byte-counter slot: the arena column it fills, the item-counter slot that numbers the rows of
+   * its offset column (0xFF: one row per record) and whether it belongs to a list of strings */
+  uint8_t slot_data_col[NSLOT], slot_rows_slot[NSLOT], slot_is_list_str[NSLOT];
+  uint8_t pad[3];
 };
 
 /* Device addresses of the caller's columns plus capacities in elements. */
@@ -92,50 +96,96 @@ inline void mk_enum(EnumDesc* e, const char* a, const char* b, const char* c) {
   }
 }
 
-/* The built-in models. Property order is the specification's (it is also the output order). */
+/* ---- the built-in models as compile-time tables ------------------------------------------------
+ * The kernels are instantiated on these (every kind, column and slot is a constant in the generated
+ * code); build_schema() copies the same tables into the run-time Schema used by the generic parser,
+ * the writer and the host. Property order is the specification's (it is also the output order). */
+struct CF {
+  uint8_t kind, col, cnt, child, len;
+  uint64_t lo, hi;
+  const char* name;
+};
+constexpr int c_strlen(const char* s) { int n = 0; while (s[n]) ++n; return n; }
+constexpr uint64_t c_pack(const char* s, int from) {
+  uint64_t v = 0;
+  const int n = c_strlen(s);
+  for (int i = 0; i < 8 && from + i < n; ++i) v |= (uint64_t)(uint8_t)s[from + i] << (8 * i);
+  return v;
+}
+constexpr CF cf(const char* name, Kind kind, int col, int cnt = 0, int child = 0) {
+  return CF{(uint8_t)kind, (uint8_t)col, (uint8_t)cnt, (uint8_t)child, (uint8_t)c_strlen(name), c_pack(name, 0), c_pack(name, 8), name};
+}
+
+template <int OBJ> struct CObj;
+/* Pet — petstore.json:872-922, required name + photoUrls (:873-876) */
+template <> struct CObj<OBJ_PET> {
+  static constexpr int N = 6, present_col = PJ_COL_PET_PRESENT, required = (1 << 2) | (1 << 3), type = PJ_TYPE_PET;
+  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_PET_ID), cf("category", K_OBJ, 0, 0, OBJ_CATEGORY),
+                              cf("name", K_STR, PJ_COL_PET_NAME_OFF, SLOT_PET_NAME),
+                              cf("photoUrls", K_LIST_STR, PJ_COL_PET_PHOTO_OFF, SLOT_PET_PHOTO_CNT),
+                              cf("tags", K_LIST_OBJ, PJ_COL_PET_TAGS_OFF, SLOT_PET_TAG_CNT, OBJ_TAG),
+                              cf("status", K_ENUM, PJ_COL_PET_STATUS, 0, 0)};
+};
+/* Category — petstore.json:858-871 */
+template <> struct CObj<OBJ_CATEGORY> {
+  static constexpr int N = 2, present_col = PJ_COL_PET_CAT_PRESENT, required = 0, type = 0;
+  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_PET_CAT_ID), cf("name", K_STR, PJ_COL_PET_CAT_NAME_OFF, SLOT_PET_CAT_NAME)};
+};
+/* Tag — petstore.json:923-936 */
+template <> struct CObj<OBJ_TAG> {
+  static constexpr int N = 2, present_col = PJ_COL_PET_TAG_PRESENT, required = 0, type = 0;
+  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_PET_TAG_ID), cf("name", K_STR, PJ_COL_PET_TAG_NAME_OFF, SLOT_PET_TAG_NAME)};
+};
+/* Order — petstore.json:937-971 */
+template <> struct CObj<OBJ_ORDER> {
+  static constexpr int N = 6, present_col = PJ_COL_ORD_PRESENT, required = 0, type = PJ_TYPE_ORDER;
+  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_ORD_ID), cf("petId", K_I64, PJ_COL_ORD_PET_ID), cf("quantity", K_I32, PJ_COL_ORD_QUANTITY),
+                              cf("shipDate", K_DATETIME, PJ_COL_ORD_SHIP_EPOCH), cf("status", K_ENUM, PJ_COL_ORD_STATUS, 0, 1),
+                              cf("complete", K_BOOL, PJ_COL_ORD_COMPLETE)};
+};
+/* User — petstore.json:824-857 */
+template <> struct CObj<OBJ_USER> {
+  static constexpr int N = 8, present_col = PJ_COL_USR_PRESENT, required = 0, type = PJ_TYPE_USER;
+  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_USR_ID), cf("username", K_STR, PJ_COL_USR_USERNAME_OFF, SLOT_USR_STR0 + 0),
+                              cf("firstName", K_STR, PJ_COL_USR_FIRSTNAME_OFF, SLOT_USR_STR0 + 1),
+                              cf("lastName", K_STR, PJ_COL_USR_LASTNAME_OFF, SLOT_USR_STR0 + 2),
+                              cf("email", K_STR, PJ_COL_USR_EMAIL_OFF, SLOT_USR_STR0 + 3),
+                              cf("password", K_STR, PJ_COL_USR_PASSWORD_OFF, SLOT_USR_STR0 + 4),
+                              cf("phone", K_STR, PJ_COL_USR_PHONE_OFF, SLOT_USR_STR0 + 5), cf("userStatus", K_I32, PJ_COL_USR_STATUS)};
+};
+/* enum literals: 0 Pet.status (petstore.json:912-916), 1 Order.status (:958-962) */
+template <int E> struct CEnum;
+template <> struct CEnum<0> { static constexpr int N = 3; static constexpr CF lit[N] = {cf("available", K_ENUM, 0), cf("pending", K_ENUM, 0), cf("sold", K_ENUM, 0)}; };
+template <> struct CEnum<1> { static constexpr int N = 3; static constexpr CF lit[N] = {cf("placed", K_ENUM, 0), cf("approved", K_ENUM, 0), cf("delivered", K_ENUM, 0)}; };
+
+template <int OBJ>
+inline void copy_obj(Schema* s) {
+  ObjDesc& o = s->obj[OBJ];
+  o.nfields = (uint8_t)CObj<OBJ>::N; o.present_col = (uint8_t)CObj<OBJ>::present_col;
+  o.required_mask = (uint8_t)CObj<OBJ>::required; o.type = (uint8_t)CObj<OBJ>::type;
+  for (int i = 0; i < CObj<OBJ>::N; ++i) {
+    const CF c = CObj<OBJ>::f[i];
+    o.f[i] = mk_field(c.name, (Kind)c.kind, c.col, c.cnt, c.child);
+  }
+}
 inline void build_schema(Schema* s) {
   *s = Schema{};
-  /* Pet — petstore.json:872-922, required name + photoUrls (:873-876) */
-  ObjDesc& pet = s->obj[OBJ_PET];
-  pet.nfields = 6; pet.present_col = PJ_COL_PET_PRESENT; pet.required_mask = (1u << 2) | (1u << 3); pet.type = PJ_TYPE_PET;
-  pet.f[0] = mk_field("id", K_I64, PJ_COL_PET_ID);
-  pet.f[1] = mk_field("category", K_OBJ, 0, 0, OBJ_CATEGORY);
-  pet.f[2] = mk_field("name", K_STR, PJ_COL_PET_NAME_OFF, SLOT_PET_NAME);
-  pet.f[3] = mk_field("photoUrls", K_LIST_STR, PJ_COL_PET_PHOTO_OFF, SLOT_PET_PHOTO_CNT);
-  pet.f[4] = mk_field("tags", K_LIST_OBJ, PJ_COL_PET_TAGS_OFF, SLOT_PET_TAG_CNT, OBJ_TAG);
-  pet.f[5] = mk_field("status", K_ENUM, PJ_COL_PET_STATUS, 0, 0);
-  /* Category — petstore.json:858-871 */
-  ObjDesc& cat = s->obj[OBJ_CATEGORY];
-  cat.nfields = 2; cat.present_col = PJ_COL_PET_CAT_PRESENT;
-  cat.f[0] = mk_field("id", K_I64, PJ_COL_PET_CAT_ID);
-  cat.f[1] = mk_field("name", K_STR, PJ_COL_PET_CAT_NAME_OFF, SLOT_PET_CAT_NAME);
-  /* Tag — petstore.json:923-936 */
-  ObjDesc& tag = s->obj[OBJ_TAG];
-  tag.nfields = 2; tag.present_col = PJ_COL_PET_TAG_PRESENT;
-  tag.f[0] = mk_field("id", K_I64, PJ_COL_PET_TAG_ID);
-  tag.f[1] = mk_field("name", K_STR, PJ_COL_PET_TAG_NAME_OFF, SLOT_PET_TAG_NAME);
-  /* Order — petstore.json:937-971 */
-  ObjDesc& ord = s->obj[OBJ_ORDER];
-  ord.nfields = 6; ord.present_col = PJ_COL_ORD_PRESENT; ord.type = PJ_TYPE_ORDER;
-  ord.f[0] = mk_field("id", K_I64, PJ_COL_ORD_ID);
-  ord.f[1] = mk_field("petId", K_I64, PJ_COL_ORD_PET_ID);
-  ord.f[2] = mk_field("quantity", K_I32, PJ_COL_ORD_QUANTITY);
-  ord.f[3] = mk_field("shipDate", K_DATETIME, PJ_COL_ORD_SHIP_EPOCH);
-  ord.f[4] = mk_field("status", K_ENUM, PJ_COL_ORD_STATUS, 0, 1);
-  ord.f[5] = mk_field("complete", K_BOOL, PJ_COL_ORD_COMPLETE);
-  /* User — petstore.json:824-857 */
-  ObjDesc& usr = s->obj[OBJ_USER];
-  usr.nfields = 8; usr.present_col = PJ_COL_USR_PRESENT; usr.type = PJ_TYPE_USER;
-  usr.f[0] = mk_field("id", K_I64, PJ_COL_USR_ID);
-  usr.f[1] = mk_field("username", K_STR, PJ_COL_USR_USERNAME_OFF, SLOT_USR_STR0 + 0);
-  usr.f[2] = mk_field("firstName", K_STR, PJ_COL_USR_FIRSTNAME_OFF, SLOT_USR_STR0 + 1);
-  usr.f[3] = mk_field("lastName", K_STR, PJ_COL_USR_LASTNAME_OFF, SLOT_USR_STR0 + 2);
-  usr.f[4] = mk_field("email", K_STR, PJ_COL_USR_EMAIL_OFF, SLOT_USR_STR0 + 3);
-  usr.f[5] = mk_field("password", K_STR, PJ_COL_USR_PASSWORD_OFF, SLOT_USR_STR0 + 4);
-  usr.f[6] = mk_field("phone", K_STR, PJ_COL_USR_PHONE_OFF, SLOT_USR_STR0 + 5);
-  usr.f[7] = mk_field("userStatus", K_I32, PJ_COL_USR_STATUS);
-  mk_enum(&s->en[0], "available", "pending", "sold");     /* petstore.json:912-916 */
-  mk_enum(&s->en[1], "placed", "approved", "delivered");  /* petstore.json:958-962 */
+  copy_obj<OBJ_PET>(s); copy_obj<OBJ_CATEGORY>(s); copy_obj<OBJ_TAG>(s); copy_obj<OBJ_ORDER>(s); copy_obj<OBJ_USER>(s);
+  for (uint32_t k = 0; k < NSLOT; ++k) { s->slot_data_col[k] = 0; s->slot_rows_slot[k] = 0xFF; s->slot_is_list_str[k] = 0; }
+  for (uint32_t oi = 0; oi < NOBJ; ++oi) {
+    const ObjDesc& O = s->obj[oi];
+    for (int i = 0; i < (int)O.nfields; ++i) {
+      const FieldDesc& F = O.f[i];
+      if (F.kind == K_STR) s->slot_data_col[F.cnt] = (uint8_t)(F.col + 1);
+      else if (F.kind == K_LIST_STR) { s->slot_data_col[F.cnt + 1] = (uint8_t)(F.col + 2); s->slot_rows_slot[F.cnt + 1] = F.cnt; s->slot_is_list_str[F.cnt + 1] = 1; }
+      else if (F.kind == K_LIST_OBJ) {
+        const ObjDesc& E = s->obj[F.child];
+        for (int q = 0; q < (int)E.nfields; ++q) if (E.f[q].kind == K_STR) s->slot_rows_slot[E.f[q].cnt] = F.cnt;
+      }
+    }
+  }
+  mk_enum(&s->en[0], CEnum<0>::lit[0].name, CEnum<0>::lit[1].name, CEnum<0>::lit[2].name);
+  mk_enum(&s->en[1], CEnum<1>::lit[0].name, CEnum<1>::lit[1].name, CEnum<1>::lit[2].name);
 }
 
 /* Range of counter slots a schema uses. */

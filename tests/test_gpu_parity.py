@@ -230,7 +230,40 @@ def test_one_million_pets(native, oracle):
         c.parse(1, d_text, cols)
         assert same_result(want, cols) == ""
         st = c.stats()
-        assert st.kernel_launches >= 5 and st.algorithmic_bytes == text.size + cols.total_bytes()
+        assert st.kernel_launches >= 4 and st.algorithmic_bytes == text.size + cols.total_bytes()
+        assert st.fast_records == n
         d_out = torch.zeros(text.size + 16, dtype=torch.uint8, device="cuda")
         m = c.write(1, cols, d_out)
         assert m == text.size and torch.equal(d_out[:m], d_text)
+
+
+@pytest.mark.parametrize("schema", [1, 2, 3, 4])
+def test_staged_pipeline_gives_the_same_columns(native, oracle, schema):
+    """The multi-pass pipeline (PJ_OPT_STAGED_PIPELINE) and the single-pass tile kernel agree with the checker."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    text = pj.gen_text(schema, 41, 0, 5000, abi.PJ_GEN_ESCAPES | abi.PJ_GEN_MALFORMED | abi.PJ_GEN_SPARSE | abi.PJ_GEN_WHITESPACE)
+    want = oracle.parse(schema, text)
+    with native.Context(device=0, flags=abi.PJ_OPT_STAGED_PIPELINE) as c:
+        assert same_result(want, gpu_parse_device(c, schema, text)) == ""
+        assert c.stats().kernel_launches >= 7
+
+
+def test_long_records_fall_back_to_unstaged_reads(ctx, oracle):
+    """Records longer than the staging window are parsed straight from global memory."""
+    big = b'{"name":"n","photoUrls":[' + b",".join(b'"' + b"u" * 50 + b'"' for _ in range(3000)) + b'],"tags":[' + \
+          b",".join(b'{"id":%d,"name":"t%d"}' % (k, k) for k in range(500)) + b"]}"
+    small = bytes(pj.gen_text(1, 8, 0, 300, 0))
+    body = as_u8(small + big + b"\n" + small + big[:-5] + b"\n" + small)
+    want = oracle.parse(1, body)
+    assert want.n_errors == 1
+    assert same_result(want, gpu_parse_device(ctx, 1, body)) == ""
+
+
+def test_many_tiny_records(ctx, oracle):
+    """Far more records than bytes per tile would suggest: empty objects and one-byte garbage lines."""
+    body = as_u8(b"{}\n" * 70000 + b"x\n" * 30000 + b'{"id":1}\n' * 50000)
+    for schema in (2, 3, 4):
+        assert same_result(oracle.parse(schema, body), gpu_parse_device(ctx, schema, body)) == ""
