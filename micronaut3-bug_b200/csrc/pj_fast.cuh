@@ -499,6 +499,10 @@ PJ_HD void store_vals(const DevCols* c, const FVals& v, uint64_t row, const uint
     else if constexpr (kind == K_BOOL) colp<uint8_t>(c, col)[row] = pr ? (uint8_t)v.v[I] : 0;
     else if constexpr (kind == K_ENUM) colp<uint8_t>(c, col)[row] = pr ? (uint8_t)v.v[I] : 255;
     else if constexpr (kind == K_STR) { if constexpr (!ELEM) colp<uint32_t>(c, col)[row] = base[cnt]; }
+    else if constexpr (kind == K_DATETIME) {
+      /* never decoded on this path, so always absent here */
+      colp<int64_t>(c, col)[row] = 0; colp<int32_t>(c, col + 1)[row] = 0; colp<int32_t>(c, col + 2)[row] = 0;
+    }
     else if constexpr (kind == K_LIST_STR || kind == K_LIST_OBJ) colp<uint32_t>(c, col)[row] = base[cnt];
     store_vals<OBJ, ELEM, I + 1>(c, v, row, base);
   }
