@@ -351,7 +351,8 @@ def main():
                                     "stage_ms_per_step": {"record_index": stage_ms[0] / args.steps, "setup": stage_ms[1] / args.steps, "tile_kernel": stage_ms[2] / args.steps}}},
         "gpu_launches": launches,
         "tile_kernel": {"records_per_block": int(last_stats.tile_records), "blocks": int(last_stats.tiles), "fast_records": int(last_stats.fast_records),
-                        "phase_cycles_per_block": [int(x) // max(int(last_stats.tiles), 1) for x in last_stats.phase_cycles]},
+                        "phase_cycles_per_block": [int(x) // max(int(last_stats.tiles), 1) for x in last_stats.phase_cycles],
+                        "lookback_polls": int(last_stats.lookback_polls), "lookback_rounds": int(last_stats.lookback_rounds)},
         "clocks": clocks,
         "e2e": e2e,
     }

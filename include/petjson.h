@@ -273,6 +273,8 @@ typedef struct pj_call_stats {
   uint64_t fast_records;    /* parse: records decoded by the speculative word-at-a-time pass alone */
   uint64_t phase_cycles[4]; /* parse: SM cycles summed over the blocks of the tile kernel: staging,
                                tokenising, look-back wait, emission                              */
+  uint64_t lookback_polls;  /* parse: times a block found the block before it not yet sized        */
+  uint64_t lookback_rounds; /* parse: 32-block look-back rounds, summed over blocks                 */
   uint32_t tile_records;    /* parse: records per block of the tile kernel                       */
   uint32_t tiles;           /* parse: blocks of the tile kernel                                   */
 } pj_call_stats;

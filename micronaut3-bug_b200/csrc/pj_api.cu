@@ -348,6 +348,7 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   const DevResult& r = *c->h_res;
   c->stats.fast_records = r.n_fast;
   for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] = r.phase_cycles[k];
+  c->stats.lookback_polls = r.lookback_polls; c->stats.lookback_rounds = r.lookback_rounds;
   if (r.timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_parse: a bounded device-side wait ran out");
   const uint64_t N = r.n_records;
   out->schema = schema;

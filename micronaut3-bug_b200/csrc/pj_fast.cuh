@@ -90,23 +90,24 @@ PJ_HD uint32_t swar_parse_k(uint64_t w, uint32_t k) {
 }
 
 /* ---- tape ---------------------------------------------------------------------------------------
- * One 64-bit entry per string of the record itself and per element of a list of objects, in reading order:
- *   bits  0..7   slot: byte-counter slot of a string, or TAPE_ELEM for a list element
- *   bits  8..23  j: element index inside its list
- *   bits 24..39  len: string length in bytes / for an element: the list's item-counter slot
- *   bits 40..63  pos: start of the string / of the element, as a window offset                     */
-enum { TAPE_ELEM = 0xFE, ELEM_STRINGS = 4 /* strings a list element may hold on the fast path */ };
+ * 32-bit words in reading order, kept in shared memory until the record's output positions are known:
+ *   string          bits 0..3 byte-counter slot, bits 4..15 length (< 4096), bits 16..31 window offset
+ *   list element    bits 0..3 = TAPE_ELEM, bits 4..11 presence bits, bits 12..15 the list's item-counter slot;
+ *                   followed by two words (low, high) for every non-string property of the element, in
+ *                   property order, and then by the element's strings as ordinary string words          */
+enum { TAPE_ELEM = 15, TAPE_MAX_STR = 4095 };
+static_assert(NSLOT <= 15, "slot numbers share four bits with the element marker");
 struct Tape {
-  uint64_t* e; /* entry k of this thread is e[k * stride] */
+  uint32_t* e; /* word k of this thread is e[k * stride] */
   uint32_t stride, cap, n;
 };
-PJ_HD void tape_push(Tape& t, uint64_t v) {
+PJ_HD void tape_push(Tape& t, uint32_t v) {
   if (t.n < t.cap) t.e[(size_t)t.n * t.stride] = v;
   t.n++; /* n > cap afterwards means overflow */
 }
-PJ_HD uint64_t tape_entry(uint32_t slot, uint32_t j, uint32_t len, uint32_t pos) {
-  return (uint64_t)slot | ((uint64_t)j << 8) | ((uint64_t)len << 24) | ((uint64_t)pos << 40);
-}
+PJ_HD void tape_set(Tape& t, uint32_t k, uint32_t v) { if (k < t.cap) t.e[(size_t)k * t.stride] = v; }
+PJ_HD uint32_t tape_get(const Tape& t, uint32_t k) { return t.e[(size_t)k * t.stride]; }
+PJ_HD uint32_t tape_str(uint32_t slot, uint32_t len, uint32_t pos) { return slot | (len << 4) | (pos << 16); }
 
 /* tokeniser position: window offsets */
 struct FastState {
@@ -114,11 +115,17 @@ struct FastState {
   uint32_t lf_ws;
 };
 
-PJ_HD void fast_ws(const Win& w, FastState& f) {
+PJ_HD void fast_ws_slow(const Win& w, FastState& f) {
   for (;;) {
     const uint32_t x = wbyte(w, f.p);
     if ((x == ' ' || x == '\t' || x == '\r' || (f.lf_ws && x == '\n')) && f.p < f.limit) f.p++; else break;
   }
+}
+/* skips whitespace and returns the byte at the new position; one compare when there is none */
+PJ_HD uint32_t fast_ws(const Win& w, FastState& f) {
+  uint32_t x = wbyte(w, f.p);
+  if (x <= ' ') { fast_ws_slow(w, f); x = wbyte(w, f.p); }
+  return x;
 }
 
 /* A plain string at f.p (opening quote): *pos = offset of the first content byte, *len = bytes. */
@@ -132,7 +139,7 @@ PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len)
   }
   if (q >= f.limit || wbyte(w, q) != '"') return false;
   const uint32_t n = q - (f.p + 1);
-  if (n > 0xFFFF) return false;
+  if (n > TAPE_MAX_STR || f.p + 1 > 0xFFFFu) return false;
   *pos = f.p + 1; *len = n;
   f.p = q + 1;
   return true;
@@ -170,14 +177,16 @@ PJ_HD bool fast_int(const Win& w, FastState& f, bool is64, int64_t* out) {
   for (;;) {
     const uint64_t x = wpeek8(w, p);
     const uint64_t m = swar_nondigit(x);
-    const uint32_t k = m ? ctz64(m) >> 3 : 8;
+    if (!m) { mag = mag * 100000000u + swar_parse8(x); nd += 8; p += 8; if (nd > 19) return false; continue; }
+    const uint32_t k = ctz64(m) >> 3;
     if (k) {
-      const uint32_t scale = k == 8 ? 100000000u : (k == 1 ? 10u : k == 2 ? 100u : k == 3 ? 1000u : k == 4 ? 10000u : k == 5 ? 100000u : k == 6 ? 1000000u : 10000000u);
+      uint32_t scale = (k & 1) ? 10u : 1u;
+      if (k & 2) scale *= 100u;
+      if (k & 4) scale *= 10000u;
       mag = mag * scale + swar_parse_k(x, k);
     }
     nd += k; p += k;
-    if (k < 8) break;
-    if (nd > 19) return false;
+    break;
   }
   if (nd == 0 || nd > 19 || (first == '0' && nd > 1)) return false;
   const uint32_t t = wbyte(w, p);
@@ -191,17 +200,48 @@ PJ_HD bool fast_int(const Win& w, FastState& f, bool is64, int64_t* out) {
 }
 
 /* ---- compile-time view of one property ------------------------------------------------------------ */
+constexpr uint64_t key_pattern_word(uint64_t lo, uint64_t hi, uint32_t len, uint32_t word) {
+  /* bytes of `"name":` number 8*word .. 8*word+7, little endian; 0 past the end */
+  uint64_t v = 0;
+  for (uint32_t k = 0; k < 8; ++k) {
+    const uint32_t b = 8 * word + k;
+    uint64_t c = 0;
+    if (b == 0 || b == len + 1) c = '"';
+    else if (b == len + 2) c = ':';
+    else if (b <= len) { const uint32_t q = b - 1; c = q < 8 ? (lo >> (8 * q)) & 0xFF : (hi >> (8 * (q - 8))) & 0xFF; }
+    v |= c << (8 * k);
+  }
+  return v;
+}
+constexpr uint64_t low_bytes_mask(uint32_t n) { return n >= 8 ? ~0ull : ((1ull << (8 * n)) - 1); }
+
 template <int OBJ, int I>
 struct FK {
   static constexpr uint32_t kind = CObj<OBJ>::f[I].kind, col = CObj<OBJ>::f[I].col, cnt = CObj<OBJ>::f[I].cnt,
                             child = CObj<OBJ>::f[I].child, len = CObj<OBJ>::f[I].len;
   static constexpr uint64_t lo = CObj<OBJ>::f[I].lo, hi = CObj<OBJ>::f[I].hi;
+  /* the compact spelling `"name":` as one or two 8-byte words */
+  static constexpr uint32_t pat_len = len + 3;
+  static_assert(pat_len <= 16, "property names of up to 13 bytes");
+  static constexpr uint64_t pat0 = key_pattern_word(lo, hi, len, 0), pat1 = key_pattern_word(lo, hi, len, 1);
+  static constexpr uint64_t mask0 = low_bytes_mask(pat_len), mask1 = low_bytes_mask(pat_len > 8 ? pat_len - 8 : 0);
 };
 template <int E, int I>
 struct EK {
   static constexpr uint32_t len = CEnum<E>::lit[I].len;
   static constexpr uint64_t lo = CEnum<E>::lit[I].lo, hi = CEnum<E>::lit[I].hi;
 };
+/* Is the compact spelling of key I at f.p? If so, move past its colon. */
+template <int OBJ, int I>
+PJ_HD bool at_key(const Win& w, FastState& f) {
+  const uint64_t a = wpeek8(w, f.p);
+  if ((a & FK<OBJ, I>::mask0) != FK<OBJ, I>::pat0) return false;
+  if constexpr (FK<OBJ, I>::pat_len > 8) {
+    if ((wpeek8(w, f.p + 8) & FK<OBJ, I>::mask1) != FK<OBJ, I>::pat1) return false;
+  }
+  f.p += FK<OBJ, I>::pat_len;
+  return true;
+}
 /* index of the property / literal with this packed name, -1 if none (an unrolled compare chain) */
 template <int OBJ, int I = 0>
 PJ_HD int match_key(uint32_t len, uint64_t lo, uint64_t hi) {
@@ -219,12 +259,6 @@ PJ_HD int match_enum(uint32_t len, uint64_t lo, uint64_t hi) {
     return match_enum<E, I + 1>(len, lo, hi);
   }
 }
-/* the object embedded in OBJ (its single K_OBJ property), or OBJ_CATEGORY as a placeholder */
-template <int OBJ>
-constexpr int embedded_child() {
-  for (int i = 0; i < CObj<OBJ>::N; ++i) if (CObj<OBJ>::f[i].kind == K_OBJ) return CObj<OBJ>::f[i].child;
-  return OBJ_CATEGORY;
-}
 
 /* values of one object; only ever indexed with constants, so it lives in registers */
 struct FVals {
@@ -232,14 +266,11 @@ struct FVals {
   uint32_t present;
 };
 
-/* Where strings go: while tokenising, onto the tape (and into the counters); while emitting a list
- * element, straight into the arena. Arrays are indexed by constant slot numbers only. */
+/* Where strings go: while tokenising, onto the tape (and into the counters). Arrays are indexed by
+ * constant slot numbers only. */
 struct FSink {
   Tape* t;
-  uint32_t* cnt;         /* [NSLOT] bytes / items counted so far */
-  const DevCols* cols;   /* emit only */
-  const uint32_t* base;  /* emit only: [NSLOT] start of this record in every arena */
-  uint32_t* cur;         /* emit only: [NSLOT] bytes already emitted */
+  uint32_t* cnt; /* [NSLOT] bytes / items counted so far */
 };
 
 /* n bytes from window offset pos to dst (global memory): bytes up to 4-byte alignment of dst, then words */
@@ -249,10 +280,10 @@ PJ_HD void copy_win(uint8_t* dst, const Win& w, uint32_t pos, uint32_t n) {
   while (n) { *dst++ = (uint8_t)wbyte(w, pos++); n--; }
 }
 
-/* Value of scalar property I of OBJ at f.p (kinds I64, I32, BOOL, STR, ENUM); j = element index of the
- * enclosing list element (0 otherwise). DATETIME and null are left to the generic parser. */
-template <int OBJ, int I, bool EMIT>
-PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v, uint32_t j) {
+/* Value of scalar property I of OBJ at f.p (kinds I64, I32, BOOL, STR, ENUM). DATETIME and null are
+ * left to the generic parser. */
+template <int OBJ, int I>
+PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v) {
   constexpr uint32_t kind = FK<OBJ, I>::kind, slot = FK<OBJ, I>::cnt;
   if (v.present & (1u << I)) return false; /* repeated key */
   if constexpr (kind == K_I64 || kind == K_I32) {
@@ -268,13 +299,8 @@ PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v, uint32_t 
     if (wbyte(w, f.p) != '"') return false;
     uint32_t pos, len;
     if (!fast_string(w, f, &pos, &len)) return false;
-    if constexpr (EMIT) {
-      copy_win(colp<uint8_t>(s.cols, FK<OBJ, I>::col + 1) + s.base[slot] + s.cur[slot], w, pos, len);
-      s.cur[slot] += len;
-    } else {
-      tape_push(*s.t, tape_entry(slot, j, len, pos));
-      s.cnt[slot] += len;
-    }
+    tape_push(*s.t, tape_str(slot, len, pos));
+    s.cnt[slot] += len;
   } else if constexpr (kind == K_ENUM) {
     if (wbyte(w, f.p) != '"') return false;
     uint32_t len; uint64_t lo, hi;
@@ -289,8 +315,7 @@ PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v, uint32_t 
 
 /* `ws* : ws*` */
 PJ_HD bool fast_colon(const Win& w, FastState& f) {
-  fast_ws(w, f);
-  if (wbyte(w, f.p) != ':') return false;
+  if (fast_ws(w, f) != ':') return false;
   f.p++;
   fast_ws(w, f);
   return true;
@@ -305,111 +330,157 @@ PJ_HD int fast_key(const Win& w, FastState& f) {
   if (i < 0 || !fast_colon(w, f)) return -1;
   return i;
 }
+/* After a value: `ws* , ws*` (returns 1, positioned at the next key), `ws* }` (returns 2, past the brace), else 0. */
+PJ_HD int fast_member_end(const Win& w, FastState& f) {
+  const uint32_t x = fast_ws(w, f);
+  if (x == ',') { f.p++; fast_ws(w, f); return 1; }
+  if (x == '}') { f.p++; return 2; }
+  return 0;
+}
 
-template <int OBJ, bool EMIT, int I = 0>
-PJ_HD bool flat_dispatch(int i, const Win& w, FastState& f, FSink& s, FVals& v, uint32_t j) {
+/* ---- flat objects (Category, Tag): scalar properties only ---------------------------------------- */
+template <int OBJ, int I>
+PJ_HD bool flat_value(const Win& w, FastState& f, FSink& s, FVals& v) {
+  if constexpr (FK<OBJ, I>::kind <= K_ENUM) return fast_scalar<OBJ, I>(w, f, s, v);
+  else return false;
+}
+template <int OBJ, int I = 0>
+PJ_HD bool flat_dispatch(int i, const Win& w, FastState& f, FSink& s, FVals& v) {
   if constexpr (I >= CObj<OBJ>::N) return false;
   else {
-    if (i == I) {
-      if constexpr (FK<OBJ, I>::kind <= K_ENUM) return fast_scalar<OBJ, I, EMIT>(w, f, s, v, j);
-      else return false;
-    }
-    return flat_dispatch<OBJ, EMIT, I + 1>(i, w, f, s, v, j);
+    if (i == I) return flat_value<OBJ, I>(w, f, s, v);
+    return flat_dispatch<OBJ, I + 1>(i, w, f, s, v);
   }
 }
-/* Flat object (Category, Tag) at f.p == '{'. */
-template <int OBJ, bool EMIT>
-PJ_HD bool fast_flat(const Win& w, FastState& f, FSink& s, FVals& v, uint32_t j) {
+/* One pass over the properties in model order: every key spelled compactly and in order is matched with
+ * one or two word compares. state: 1 = at a key, 2 = object closed, 0 = refuse. */
+template <int OBJ, int I = 0>
+PJ_HD int flat_inorder(const Win& w, FastState& f, FSink& s, FVals& v, int state) {
+  if constexpr (I >= CObj<OBJ>::N) return state;
+  else {
+    if (state == 1 && at_key<OBJ, I>(w, f)) {
+      fast_ws(w, f);
+      if (!flat_value<OBJ, I>(w, f, s, v)) return 0;
+      state = fast_member_end(w, f);
+    }
+    return flat_inorder<OBJ, I + 1>(w, f, s, v, state);
+  }
+}
+/* Flat object at f.p == '{'. */
+template <int OBJ>
+PJ_HD bool fast_flat(const Win& w, FastState& f, FSink& s, FVals& v) {
   v.present = 0;
   f.p++;
-  fast_ws(w, f);
-  if (wbyte(w, f.p) == '}') { f.p++; return true; }
-  for (;;) {
+  if (fast_ws(w, f) == '}') { f.p++; return true; }
+  int state = flat_inorder<OBJ>(w, f, s, v, 1);
+  while (state == 1) { /* keys out of order or spelled with blanks */
     const int i = fast_key<OBJ>(w, f);
-    if (i < 0) return false;
-    if (!flat_dispatch<OBJ, EMIT>(i, w, f, s, v, j)) return false;
-    fast_ws(w, f);
-    const uint32_t x = wbyte(w, f.p);
-    if (x == ',') { f.p++; fast_ws(w, f); continue; }
-    if (x == '}') { f.p++; return true; }
-    return false;
+    if (i < 0 || !flat_dispatch<OBJ>(i, w, f, s, v)) return false;
+    state = fast_member_end(w, f);
+  }
+  return state == 2;
+}
+
+/* ---- model roots ------------------------------------------------------------------------------------ */
+template <int OBJ, int I = 0>
+constexpr uint32_t scalar_words() { /* tape words for the non-string properties of a list element */
+  if constexpr (I >= CObj<OBJ>::N) return 0;
+  else return (CObj<OBJ>::f[I].kind != K_STR ? 2u : 0u) + scalar_words<OBJ, I + 1>();
+}
+template <int OBJ, int I = 0>
+PJ_HD void tape_put_scalars(Tape& t, uint32_t at, const FVals& v) {
+  if constexpr (I < CObj<OBJ>::N) {
+    if constexpr (FK<OBJ, I>::kind != K_STR) {
+      tape_set(t, at, (uint32_t)(uint64_t)v.v[I]);
+      tape_set(t, at + 1, (uint32_t)((uint64_t)v.v[I] >> 32));
+      tape_put_scalars<OBJ, I + 1>(t, at + 2, v);
+    } else tape_put_scalars<OBJ, I + 1>(t, at, v);
   }
 }
 
-/* Property I of a model root at f.p: scalars as above; an embedded object into cv; lists entry by entry. */
+/* Property I of a model root at f.p: scalars as above; an embedded object into cv; lists item by item. */
+template <int OBJ, int I>
+PJ_HD bool root_value(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv) {
+  constexpr uint32_t kind = FK<OBJ, I>::kind, cnt = FK<OBJ, I>::cnt;
+  if constexpr (kind <= K_ENUM) return fast_scalar<OBJ, I>(w, f, s, v);
+  else if constexpr (kind == K_DATETIME) return false;
+  else {
+    if (v.present & (1u << I)) return false;
+    if constexpr (kind == K_OBJ) {
+      if (wbyte(w, f.p) != '{' || !fast_flat<FK<OBJ, I>::child>(w, f, s, cv)) return false;
+    } else {
+      if (wbyte(w, f.p) != '[') return false;
+      f.p++;
+      uint32_t j = 0;
+      if (fast_ws(w, f) == ']') f.p++;
+      else {
+        for (;;) {
+          if constexpr (kind == K_LIST_STR) {
+            if (wbyte(w, f.p) != '"') return false;
+            uint32_t pos, len;
+            if (!fast_string(w, f, &pos, &len)) return false;
+            tape_push(*s.t, tape_str(cnt + 1, len, pos));
+            s.cnt[cnt + 1] += len;
+          } else {
+            /* header word, room for the scalars, then the element's strings as they are met */
+            constexpr int E = FK<OBJ, I>::child;
+            if (wbyte(w, f.p) != '{') return false;
+            const uint32_t at = s.t->n;
+            for (uint32_t k = 0; k < 1 + scalar_words<E>(); ++k) tape_push(*s.t, 0);
+            FVals ev;
+            if (!fast_flat<E>(w, f, s, ev)) return false;
+            tape_set(*s.t, at, (uint32_t)TAPE_ELEM | (ev.present << 4) | (cnt << 12));
+            tape_put_scalars<E>(*s.t, at + 1, ev);
+          }
+          j++;
+          const uint32_t y = fast_ws(w, f);
+          if (y == ',') { f.p++; fast_ws(w, f); continue; }
+          if (y == ']') { f.p++; break; }
+          return false;
+        }
+      }
+      s.cnt[cnt] = j;
+    }
+    v.present |= 1u << I;
+    return true;
+  }
+}
 template <int OBJ, int I = 0>
 PJ_HD bool root_dispatch(int i, const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv) {
   if constexpr (I >= CObj<OBJ>::N) return false;
   else {
-    if (i == I) {
-      constexpr uint32_t kind = FK<OBJ, I>::kind, cnt = FK<OBJ, I>::cnt;
-      if constexpr (kind <= K_ENUM) return fast_scalar<OBJ, I, false>(w, f, s, v, 0);
-      else if constexpr (kind == K_DATETIME) return false;
-      else {
-        if (v.present & (1u << I)) return false;
-        if constexpr (kind == K_OBJ) {
-          if (wbyte(w, f.p) != '{' || !fast_flat<FK<OBJ, I>::child, false>(w, f, s, cv, 0)) return false;
-        } else {
-          if (wbyte(w, f.p) != '[') return false;
-          f.p++;
-          fast_ws(w, f);
-          uint32_t j = 0;
-          if (wbyte(w, f.p) == ']') f.p++;
-          else {
-            for (;;) {
-              if (j >= 0xFFFF) return false;
-              if constexpr (kind == K_LIST_STR) {
-                if (wbyte(w, f.p) != '"') return false;
-                uint32_t pos, len;
-                if (!fast_string(w, f, &pos, &len)) return false;
-                tape_push(*s.t, tape_entry(cnt + 1, j, len, pos));
-                s.cnt[cnt + 1] += len;
-              } else {
-                /* one entry per element: where it starts. Its strings are only counted now; the element is
-                   tokenised again when it is emitted. */
-                if (wbyte(w, f.p) != '{') return false;
-                tape_push(*s.t, tape_entry(TAPE_ELEM, j, cnt, f.p));
-                Tape nul;
-                nul.e = nullptr; nul.stride = 0; nul.cap = 0; nul.n = 0;
-                FSink es = s;
-                es.t = &nul;
-                FVals ev;
-                if (!fast_flat<FK<OBJ, I>::child, false>(w, f, es, ev, j) || nul.n > ELEM_STRINGS) return false;
-              }
-              j++;
-              fast_ws(w, f);
-              const uint32_t y = wbyte(w, f.p);
-              if (y == ',') { f.p++; fast_ws(w, f); continue; }
-              if (y == ']') { f.p++; break; }
-              return false;
-            }
-          }
-          s.cnt[cnt] = j;
-        }
-        v.present |= 1u << I;
-        return true;
-      }
-    }
+    if (i == I) return root_value<OBJ, I>(w, f, s, v, cv);
     return root_dispatch<OBJ, I + 1>(i, w, f, s, v, cv);
   }
 }
-
+template <int OBJ, int I = 0>
+PJ_HD int root_inorder(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv, int state) {
+  if constexpr (I >= CObj<OBJ>::N) return state;
+  else {
+    if (state == 1 && at_key<OBJ, I>(w, f)) {
+      fast_ws(w, f);
+      if (!root_value<OBJ, I>(w, f, s, v, cv)) return 0;
+      state = fast_member_end(w, f);
+    }
+    return root_inorder<OBJ, I + 1>(w, f, s, v, cv, state);
+  }
+}
 /* Members of a model root. f.p is after `{ ws*`, or at the value of property `pending` (>= 0) whose key
  * was read already. Ends after the closing brace. */
 template <int OBJ>
 PJ_HD bool fast_root(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv, int pending) {
-  if (pending < 0 && wbyte(w, f.p) == '}') { f.p++; return true; }
-  for (;;) {
-    int i = pending;
-    pending = -1;
-    if (i < 0) { i = fast_key<OBJ>(w, f); if (i < 0) return false; }
-    if (!root_dispatch<OBJ>(i, w, f, s, v, cv)) return false;
-    fast_ws(w, f);
-    const uint32_t x = wbyte(w, f.p);
-    if (x == ',') { f.p++; fast_ws(w, f); continue; }
-    if (x == '}') { f.p++; return true; }
-    return false;
+  int state = 1;
+  if (pending >= 0) {
+    if (!root_dispatch<OBJ>(pending, w, f, s, v, cv)) return false;
+    state = fast_member_end(w, f);
+  } else if (wbyte(w, f.p) == '}') { f.p++; return true; }
+  state = root_inorder<OBJ>(w, f, s, v, cv, state);
+  while (state == 1) { /* keys out of order or spelled with blanks */
+    const int i = fast_key<OBJ>(w, f);
+    if (i < 0 || !root_dispatch<OBJ>(i, w, f, s, v, cv)) return false;
+    state = fast_member_end(w, f);
   }
+  return state == 2;
 }
 
 template <int SCHEMA> struct RootOf { static constexpr int obj = SCHEMA == PJ_SCHEMA_PET ? (int)OBJ_PET : (SCHEMA == PJ_SCHEMA_ORDER ? (int)OBJ_ORDER : (int)OBJ_USER); };
@@ -427,9 +498,8 @@ PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf
   t.n = 0;
   v.present = 0; cv.present = 0;
   FSink s;
-  s.t = &t; s.cnt = cnt; s.cols = nullptr; s.base = nullptr; s.cur = nullptr;
-  fast_ws(w, f);
-  if (f.p >= limit || wbyte(w, f.p) != '{') return false;
+  s.t = &t; s.cnt = cnt;
+  if (fast_ws(w, f) != '{' || f.p >= limit) return false;
   f.p++;
   fast_ws(w, f);
   uint32_t type;
@@ -451,10 +521,7 @@ PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf
       if (owners == 3) {
         if (have_id || !fast_int(w, f, true, &early_id)) return false;
         have_id = true;
-        fast_ws(w, f);
-        if (wbyte(w, f.p) != ',') return false;
-        f.p++;
-        fast_ws(w, f);
+        if (fast_member_end(w, f) != 1) return false;
         continue;
       }
       if (owners != 1) return false; /* unknown key, or `status` before the deciding key */
@@ -473,9 +540,9 @@ PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf
       break;
     }
   }
-  fast_ws(w, f);
+  const uint32_t x = fast_ws(w, f);
   if (f.p > limit) return false;
-  if (f.p < limit) { if (lf_ws || wbyte(w, f.p) != '\n') return false; }
+  if (f.p < limit) { if (lf_ws || x != '\n') return false; }
   else if (open_end) return false;
   if (t.n > t.cap) return false;
   if constexpr (SCHEMA == PJ_SCHEMA_MIXED) {
@@ -487,7 +554,7 @@ PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf
 
 /* ---- emission -------------------------------------------------------------------------------------- */
 /* Fixed-width values, string offsets and list offsets of one object at `row`. ELEM: the object is a
- * list element whose string offsets were stored before it was tokenised (see emit_element). */
+ * list element, whose string offsets are stored by store_elem_str_offsets. */
 template <int OBJ, bool ELEM, int I = 0>
 PJ_HD void store_vals(const DevCols* c, const FVals& v, uint64_t row, const uint32_t* base) {
   if constexpr (I == 0) colp<uint8_t>(c, CObj<OBJ>::present_col)[row] = (uint8_t)v.present;
@@ -507,7 +574,7 @@ PJ_HD void store_vals(const DevCols* c, const FVals& v, uint64_t row, const uint
     store_vals<OBJ, ELEM, I + 1>(c, v, row, base);
   }
 }
-/* offsets of the strings of a list element = the cursors as they stand before the element is emitted */
+/* offsets of the strings of a list element = the cursors as they stand before its strings are copied */
 template <int OBJ, int I = 0>
 PJ_HD void store_elem_str_offsets(const DevCols* c, uint64_t row, const uint32_t* base, const uint32_t* cur) {
   if constexpr (I < CObj<OBJ>::N) {
@@ -515,60 +582,66 @@ PJ_HD void store_elem_str_offsets(const DevCols* c, uint64_t row, const uint32_t
     store_elem_str_offsets<OBJ, I + 1>(c, row, base, cur);
   }
 }
-
-/* a string of the object embedded in the root (its properties are flat) */
+template <int OBJ, int I = 0>
+PJ_HD void tape_get_scalars(const Tape& t, uint32_t at, FVals& v) {
+  if constexpr (I < CObj<OBJ>::N) {
+    if constexpr (FK<OBJ, I>::kind != K_STR) {
+      v.v[I] = (int64_t)((uint64_t)tape_get(t, at) | ((uint64_t)tape_get(t, at + 1) << 32));
+      tape_get_scalars<OBJ, I + 1>(t, at + 2, v);
+    } else tape_get_scalars<OBJ, I + 1>(t, at, v);
+  }
+}
+/* a string word that belongs to a flat object CH (embedded object or list element): copy it to its arena */
 template <int CH, int I = 0>
-PJ_HD void replay_child(const Win& w, const DevCols* c, uint32_t slot, uint32_t len, uint32_t pos, const uint32_t* base, uint32_t* cur,
-                        bool* done) {
-  if constexpr (I < CObj<CH>::N) {
+PJ_HD bool replay_flat_string(const Win& w, const DevCols* c, uint32_t slot, uint32_t len, uint32_t pos, const uint32_t* base, uint32_t* cur) {
+  if constexpr (I >= CObj<CH>::N) return false;
+  else {
     if constexpr (FK<CH, I>::kind == K_STR) {
       constexpr uint32_t cnt = FK<CH, I>::cnt;
-      if (slot == cnt) { copy_win(colp<uint8_t>(c, FK<CH, I>::col + 1) + base[cnt] + cur[cnt], w, pos, len); cur[cnt] += len; *done = true; return; }
+      if (slot == cnt) { copy_win(colp<uint8_t>(c, FK<CH, I>::col + 1) + base[cnt] + cur[cnt], w, pos, len); cur[cnt] += len; return true; }
     }
-    replay_child<CH, I + 1>(w, c, slot, len, pos, base, cur, done);
+    return replay_flat_string<CH, I + 1>(w, c, slot, len, pos, base, cur);
   }
 }
 
-/* One tape entry of a record whose root is OBJ: finds the property it belongs to (an unrolled chain
- * over the properties, constants all the way) and emits it. */
+/* One tape word of a record whose root is OBJ (k = its index; returns the index of the next word): finds
+ * the property it belongs to by an unrolled chain over the properties and emits it. cur[] holds, per slot,
+ * the bytes (byte slots) or items (item slots) emitted so far. */
 template <int OBJ, int I = 0>
-PJ_HD void replay_entry(const Win& w, const DevCols* c, uint32_t slot, uint32_t j, uint32_t len, uint32_t pos, const uint32_t* base,
-                        uint32_t* cur) {
-  if constexpr (I < CObj<OBJ>::N) {
+PJ_HD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32_t k, uint32_t word, const uint32_t* base, uint32_t* cur) {
+  if constexpr (I >= CObj<OBJ>::N) return k + 1;
+  else {
     constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col, cnt = FK<OBJ, I>::cnt;
+    const uint32_t slot = word & 15u, len = (word >> 4) & 0xFFFu, pos = word >> 16;
     if constexpr (kind == K_STR) {
-      if (slot == cnt) { copy_win(colp<uint8_t>(c, col + 1) + base[cnt] + cur[cnt], w, pos, len); cur[cnt] += len; return; }
+      if (slot == cnt) { copy_win(colp<uint8_t>(c, col + 1) + base[cnt] + cur[cnt], w, pos, len); cur[cnt] += len; return k + 1; }
     } else if constexpr (kind == K_LIST_STR) {
       if (slot == cnt + 1) {
-        colp<uint32_t>(c, col + 1)[(uint64_t)base[cnt] + j] = base[cnt + 1] + cur[cnt + 1];
+        colp<uint32_t>(c, col + 1)[(uint64_t)base[cnt] + cur[cnt]] = base[cnt + 1] + cur[cnt + 1];
         copy_win(colp<uint8_t>(c, col + 2) + base[cnt + 1] + cur[cnt + 1], w, pos, len);
-        cur[cnt + 1] += len;
-        return;
+        cur[cnt + 1] += len; cur[cnt] += 1;
+        return k + 1;
       }
     } else if constexpr (kind == K_OBJ) {
-      /* strings of the embedded object: its properties are flat */
-      constexpr int CH = FK<OBJ, I>::child;
-      bool done = false;
-      replay_child<CH>(w, c, slot, len, pos, base, cur, &done);
-      if (done) return;
+      if (replay_flat_string<FK<OBJ, I>::child>(w, c, slot, len, pos, base, cur)) return k + 1;
     } else if constexpr (kind == K_LIST_OBJ) {
-      if (slot == TAPE_ELEM && len == cnt) {
-        constexpr int E = FK<OBJ, I>::child;
-        const uint64_t erow = (uint64_t)base[cnt] + j;
+      constexpr int E = FK<OBJ, I>::child;
+      if (slot == TAPE_ELEM && (word >> 12 & 15u) == cnt) {
+        const uint64_t erow = (uint64_t)base[cnt] + cur[cnt];
+        cur[cnt] += 1;
         store_elem_str_offsets<E>(c, erow, base, cur);
-        FastState f;
-        f.p = pos; f.limit = 0xFFFFFFFFu; f.lf_ws = 1;
-        FSink s;
-        s.t = nullptr; s.cnt = nullptr; s.cols = c; s.base = base; s.cur = cur;
         FVals ev;
-        fast_flat<E, true>(w, f, s, ev, j);
+        ev.present = (word >> 4) & 0xFFu;
+        tape_get_scalars<E>(t, k + 1, ev);
         store_vals<E, true>(c, ev, erow, base);
-        return;
+        return k + 1 + scalar_words<E>();
       }
+      if (slot != TAPE_ELEM && replay_flat_string<E>(w, c, slot, len, pos, base, cur)) return k + 1;
     }
-    replay_entry<OBJ, I + 1>(w, c, slot, j, len, pos, base, cur);
+    return replay_word<OBJ, I + 1>(w, c, t, k, word, base, cur);
   }
 }
+
 /* columns of the embedded object of OBJ (if it has one) at the root's row */
 template <int OBJ, int I = 0>
 PJ_HD void store_embedded(const DevCols* c, const FVals& v, const FVals& cv, uint64_t row, const uint32_t* base) {
@@ -589,10 +662,7 @@ PJ_HD void emit_root(const Win& w, const DevCols* c, const FVals& v, const FVals
   uint32_t cur[NSLOT];
 #pragma unroll
   for (uint32_t k = 0; k < NSLOT; ++k) cur[k] = 0;
-  for (uint32_t k = 0; k < t.n; ++k) {
-    const uint64_t e = t.e[(size_t)k * t.stride];
-    replay_entry<OBJ>(w, c, (uint32_t)(e & 0xFF), (uint32_t)(e >> 8) & 0xFFFF, (uint32_t)(e >> 24) & 0xFFFF, (uint32_t)(e >> 40), base, cur);
-  }
+  for (uint32_t k = 0; k < t.n;) k = replay_word<OBJ>(w, c, t, k, tape_get(t, k), base, cur);
 }
 
 /* Replays a record accepted by fast_record<SCHEMA>(): every column of its row, then the tape.

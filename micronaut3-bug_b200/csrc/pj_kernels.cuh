@@ -38,6 +38,7 @@ struct DevResult {
   uint32_t pad;
   unsigned long long n_fast;  /* records decoded by the speculative pass alone */
   unsigned long long phase_cycles[4]; /* tile kernel, summed over blocks: staging, tokenising, look-back, emit */
+  unsigned long long lookback_polls, lookback_rounds;
 };
 
 static constexpr int INDEX_THREADS = 256;
@@ -402,9 +403,9 @@ __global__ void __launch_bounds__(PARSE_THREADS) k_write_emit(const __grid_const
  * ================================================================================================ */
 static constexpr int TILE_THREADS = 128;
 static constexpr unsigned long long PJ_SPIN_LIMIT_NS = 2000000000ull; /* 2 s */
-static constexpr uint32_t TILE_WIN_BYTES = 41 * 1024;  /* staged input bytes per tile */
-static constexpr uint32_t TILE_TAPE_CAP = 12;          /* tape entries per record before the generic parser takes over */
-static constexpr uint32_t TILE_SMEM_BYTES = ((TILE_WIN_BYTES + 64 + 15) & ~15u) + TILE_TAPE_CAP * TILE_THREADS * 8;
+static constexpr uint32_t TILE_WIN_BYTES = 44 * 1024;  /* staged input bytes per tile */
+static constexpr uint32_t TILE_TAPE_CAP = 20;          /* 32-bit tape words per record before the generic parser takes over */
+static constexpr uint32_t TILE_SMEM_BYTES = ((TILE_WIN_BYTES + 64 + 15) & ~15u) + TILE_TAPE_CAP * TILE_THREADS * 4;
 
 struct TileState {
   uint32_t flag; /* 0 nothing, 1 aggregate valid, 2 inclusive valid */
@@ -449,7 +450,24 @@ __device__ __forceinline__ bool tile_lookback(const TileArgs& a, uint32_t tile, 
   uint32_t excl = 0;
   int64_t j = (int64_t)tile - 1;
   const unsigned long long t0 = global_ns();
+  /* first wait, with one lane, until the tile just before has sized its records: by then the tiles before it
+     usually have too, and the wide look below succeeds at once */
+  if (j >= 0) {
+    uint32_t give_up = 0;
+    if (lane == 0) {
+      unsigned polls = 0;
+      while (ld_acquire_u32(&a.tiles[j].flag) == 0) {
+        ++polls;
+        if ((global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)&a.res->timeout) { give_up = 1; break; }
+        __nanosleep(200);
+      }
+      if (polls) atomicAdd(&a.res->lookback_polls, (unsigned long long)polls);
+    }
+    give_up = __shfl_sync(0xFFFFFFFFu, give_up, 0);
+    if (give_up) { if (lane == 0) atomicExch(&a.res->timeout, 1u); return false; }
+  }
   while (j >= 0) {
+    if (lane == 0) atomicAdd(&a.res->lookback_rounds, 1ull);
     /* lane L looks at tile j - L */
     const int64_t mine = j - lane;
     uint32_t f = 2;
@@ -492,7 +510,7 @@ template <int SCHEMA> struct SlotRange {
 };
 
 template <int SCHEMA>
-__global__ void __launch_bounds__(TILE_THREADS) k_parse_tile(const __grid_constant__ TileArgs a) {
+__global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_constant__ TileArgs a) {
   constexpr uint32_t LO = SlotRange<SCHEMA>::lo, HI = SlotRange<SCHEMA>::hi;
   constexpr uint32_t NWARPS = TILE_THREADS / 32;
   extern __shared__ __align__(16) uint8_t smem[];
@@ -501,7 +519,7 @@ __global__ void __launch_bounds__(TILE_THREADS) k_parse_tile(const __grid_consta
   __shared__ uint32_t sh_tile, sh_ok;
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* win = smem;
-  uint64_t* tape = reinterpret_cast<uint64_t*>(smem + ((a.win_bytes + 64 + 15) & ~15u));
+  uint32_t* tape = reinterpret_cast<uint32_t*>(smem + ((a.win_bytes + 64 + 15) & ~15u));
 
   if (tid == 0) sh_tile = atomicAdd(a.ticket, 1u);
   __syncthreads();
