@@ -309,7 +309,8 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
     ta.ntiles = (uint32_t)ntiles;
     c->stats.tile_records = tile_recs; c->stats.tiles = (uint32_t)ntiles;
     ta.rec_end = nullptr; ta.rec_blank = nullptr;
-    { pj_status st = ensure(c, &c->tiles, ntiles * sizeof(TileState) + 256); if (st) return st; }
+    const uint64_t nstates = ntiles; /* one look-back state per block */
+    { pj_status st = ensure(c, &c->tiles, nstates * sizeof(TileState) + 256); if (st) return st; }
     ta.ticket = (uint32_t*)c->tiles.p;
     ta.tiles = (TileState*)((uint8_t*)c->tiles.p + 128);
     ta.res = c->d_res;
@@ -323,7 +324,7 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
     }
     ta.plan = fa.plan;
     ta.cols = dcols;
-    PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, ntiles * sizeof(TileState) + 128, c->stream));
+    PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, nstates * sizeof(TileState) + 128, c->stream));
     const uint32_t one = 1;
     PJ_CUDA(c, cudaMemcpyAsync(&c->d_res->ok, &one, sizeof one, cudaMemcpyHostToDevice, c->stream));
     stage.next(); /* stage 1: set-up */

@@ -394,9 +394,9 @@ __global__ void __launch_bounds__(PARSE_THREADS) k_write_emit(const __grid_const
  * before it, and then emits every column. Input bytes are read from HBM once, every output byte is
  * written once.
  *
- * Look-back protocol (per tile: flag, aggregate[NSLOT], inclusive[NSLOT]): a tile publishes its
- * aggregate (flag 1) as soon as its records are sized and its inclusive prefix (flag 2) once it has
- * found the nearest predecessor with flag 2 and added the aggregates in between. Tiles take their
+ * Look-back protocol (per tile: aggregate[NSLOT], inclusive[NSLOT], each word with its own valid bit): a
+ * tile publishes its aggregate as soon as its records are sized and its inclusive prefix once it has
+ * found the nearest predecessor whose inclusive prefix is published and added the aggregates in between. Tiles take their
  * index from an atomic ticket, so every predecessor of a running tile is itself running or done and
  * the waits cannot deadlock. Every wait is bounded: after PJ_SPIN_LIMIT_NS it raises res->timeout,
  * which all other waits also watch, and the block finishes without emitting.
@@ -407,13 +407,16 @@ static constexpr uint32_t TILE_WIN_BYTES = 44 * 1024;  /* staged input bytes per
 static constexpr uint32_t TILE_TAPE_CAP = 20;          /* 32-bit tape words per record before the generic parser takes over */
 static constexpr uint32_t TILE_SMEM_BYTES = ((TILE_WIN_BYTES + 64 + 15) & ~15u) + TILE_TAPE_CAP * TILE_THREADS * 4;
 
+/* Look-back state of one tile. Every word carries its own "valid" bit (bit 63) next to a 32-bit value and
+ * is written once with a single 64-bit store, so a reader needs no fence and gets status and value in the
+ * same round trip: agg = the tile's own totals, inc = totals of all tiles up to and including it. */
 struct TileState {
-  uint32_t flag; /* 0 nothing, 1 aggregate valid, 2 inclusive valid */
-  uint32_t agg[NSLOT];
-  uint32_t inc[NSLOT];
-  uint32_t pad;
+  unsigned long long agg[NSLOT];
+  unsigned long long inc[NSLOT];
+  unsigned long long pad[2];
 };
-static_assert(sizeof(TileState) == 128, "one tile state per 128-byte line");
+static_assert(sizeof(TileState) == 256, "two 128-byte lines per tile state");
+static constexpr unsigned long long TS_VALID = 1ull << 63;
 
 struct TileArgs {
   const uint8_t* in;
@@ -430,13 +433,13 @@ struct TileArgs {
   DevCols cols;
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
@@ -444,63 +447,56 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 
-/* Exclusive prefix of this tile over all earlier tiles, for slot = lane (lanes >= NSLOT idle). Warp 0 only.
- * Returns false when a wait ran out. */
-__device__ __forceinline__ bool tile_lookback(const TileArgs& a, uint32_t tile, uint32_t lane, uint32_t* excl_out) {
-  uint32_t excl = 0;
+/* Exclusive prefix of tile `tile` over all earlier tiles for the slots LO..HI-1, into excl[] (every lane
+ * gets all of them). Warp 0 only, all 32 lanes. Each round looks at the 32 tiles before position j with one
+ * memory round trip: lane L loads every agg and inc word of tile j - L, the warp finds the nearest tile whose
+ * inclusive totals are published, and a shuffle reduction adds its inclusive totals to the aggregates of
+ * the tiles after it. Returns false when the bounded wait ran out. */
+template <uint32_t LO, uint32_t HI>
+__device__ __forceinline__ bool tile_lookback(const TileArgs& a, uint32_t tile, uint32_t lane, uint32_t* excl) {
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) excl[k] = 0;
   int64_t j = (int64_t)tile - 1;
   const unsigned long long t0 = global_ns();
-  /* first wait, with one lane, until the tile just before has sized its records: by then the tiles before it
-     usually have too, and the wide look below succeeds at once */
-  if (j >= 0) {
-    uint32_t give_up = 0;
-    if (lane == 0) {
-      unsigned polls = 0;
-      while (ld_acquire_u32(&a.tiles[j].flag) == 0) {
-        ++polls;
-        if ((global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)&a.res->timeout) { give_up = 1; break; }
-        __nanosleep(200);
-      }
-      if (polls) atomicAdd(&a.res->lookback_polls, (unsigned long long)polls);
-    }
-    give_up = __shfl_sync(0xFFFFFFFFu, give_up, 0);
-    if (give_up) { if (lane == 0) atomicExch(&a.res->timeout, 1u); return false; }
-  }
+  unsigned polls = 0, rounds = 0;
   while (j >= 0) {
-    if (lane == 0) atomicAdd(&a.res->lookback_rounds, 1ull);
-    /* lane L looks at tile j - L */
-    const int64_t mine = j - lane;
-    uint32_t f = 2;
-    uint32_t inc_mask, ready_mask, need;
+    const int64_t mine = j - lane; /* lane L looks at tile j - L; tiles before the first count as "inclusive, zero" */
+    uint32_t va[NSLOT], vi[NSLOT];
+    uint32_t first_inc;
     for (;;) {
-      if (mine >= 0) f = ld_acquire_u32(&a.tiles[mine].flag);
-      inc_mask = __ballot_sync(0xFFFFFFFFu, f == 2);
-      ready_mask = __ballot_sync(0xFFFFFFFFu, f != 0);
-      const uint32_t first_inc = inc_mask ? (uint32_t)(__ffs((int)inc_mask) - 1) : 32u;
-      need = first_inc >= 31 ? 0xFFFFFFFFu : ((2u << first_inc) - 1u);
+      bool has_inc = true, has_agg = true;
+#pragma unroll
+      for (uint32_t k = LO; k < HI; ++k) {
+        unsigned long long wa = TS_VALID, wi = TS_VALID;
+        if (mine >= 0) { wi = ld_relaxed_u64(&a.tiles[mine].inc[k]); wa = ld_relaxed_u64(&a.tiles[mine].agg[k]); }
+        has_inc = has_inc && (wi & TS_VALID);
+        has_agg = has_agg && (wa & TS_VALID);
+        va[k] = (uint32_t)wa; vi[k] = (uint32_t)wi;
+      }
+      const uint32_t inc_mask = __ballot_sync(0xFFFFFFFFu, has_inc);
+      const uint32_t ready_mask = __ballot_sync(0xFFFFFFFFu, has_inc || has_agg);
+      first_inc = inc_mask ? (uint32_t)(__ffs((int)inc_mask) - 1) : 32u;
+      const uint32_t need = first_inc >= 31 ? 0xFFFFFFFFu : ((2u << first_inc) - 1u);
       if ((ready_mask & need) == need) break;
+      ++polls;
       uint32_t give_up = 0;
       if (lane == 0) give_up = (global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)&a.res->timeout;
       give_up = __shfl_sync(0xFFFFFFFFu, give_up, 0);
       if (give_up) { if (lane == 0) atomicExch(&a.res->timeout, 1u); return false; }
       __nanosleep(100);
     }
-    __threadfence();
-    __syncwarp();
-    const uint32_t first_inc = inc_mask ? (uint32_t)(__ffs((int)inc_mask) - 1) : 32u;
-    const uint32_t steps = first_inc < 32 ? first_inc + 1 : 32;
-    if (lane < NSLOT) {
-      for (uint32_t L = 0; L < steps; ++L) {
-        const int64_t tj = j - L;
-        if (tj < 0) break; /* before the first tile: nothing to add (its lane reported "inclusive") */
-        const TileState* ts = &a.tiles[tj];
-        excl += __ldcg(L == first_inc ? &ts->inc[lane] : &ts->agg[lane]);
-      }
+    ++rounds;
+#pragma unroll
+    for (uint32_t k = LO; k < HI; ++k) {
+      uint32_t c = lane < first_inc ? va[k] : (lane == first_inc ? vi[k] : 0u);
+#pragma unroll
+      for (int d = 16; d; d >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, d);
+      excl[k] += c;
     }
     if (first_inc < 32) break;
     j -= 32;
   }
-  *excl_out = excl;
+  if (lane == 0) { atomicAdd(&a.res->lookback_polls, (unsigned long long)polls); atomicAdd(&a.res->lookback_rounds, (unsigned long long)rounds); }
   return true;
 }
 
@@ -625,18 +621,17 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
 #pragma unroll
       for (uint32_t q = 0; q < NWARPS; ++q) mine += sh_warp[lane][q];
     }
-    if (lane < NSLOT) { sh_tot[lane] = mine; me->agg[lane] = mine; if (tile == 0) me->inc[lane] = mine; }
-    __threadfence();
-    __syncwarp();
-    if (lane == 0) st_release_u32(&me->flag, tile == 0 ? 2u : 1u);
-    uint32_t excl = 0;
-    const bool ok = tile_lookback(a, tile, lane, &excl);
-    if (tile != 0) {
-      if (lane < NSLOT) me->inc[lane] = excl + mine;
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) st_release_u32(&me->flag, 2u);
+    if (lane < NSLOT) {
+      sh_tot[lane] = mine;
+      st_relaxed_u64(&me->agg[lane], TS_VALID | mine);
+      if (tile == 0) st_relaxed_u64(&me->inc[lane], TS_VALID | mine);
     }
+    uint32_t excl_all[NSLOT];
+    const bool ok = tile_lookback<LO, HI>(a, tile, lane, excl_all);
+    uint32_t excl = 0;
+#pragma unroll
+    for (uint32_t k = LO; k < HI; ++k) if (lane == k) excl = excl_all[k];
+    if (tile != 0 && ok && lane < NSLOT) st_relaxed_u64(&me->inc[lane], TS_VALID | (unsigned long long)(excl + mine));
     if (lane < NSLOT) sh_base[lane] = excl;
     /* does the whole tile fit the caller's buffers? (totals only grow, so the last tile's verdict is the call's) */
     const bool over = lane < NSLOT && (uint64_t)excl + mine > a.slot_cap[lane];
