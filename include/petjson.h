@@ -332,6 +332,29 @@ pj_status pj_parse_shard(pj_ctx* ctx, uint32_t schema, const uint8_t* in, uint64
 pj_status pj_index_records(pj_ctx* ctx, uint32_t framing, const uint8_t* in, uint64_t len,
                            uint32_t kind, uint64_t* rec_start, uint64_t cap, uint64_t* n);
 
+/* Record index of an NDJSON buffer for callers that must not allocate. It has no counterpart in the
+ * reference; it exists for hosts that run this library where device memory cannot be obtained or
+ * released: inside a region whose memory is owned and budgeted by someone else (an embedding runtime's
+ * pool allocator, a serving process that froze its heap after start-up), or on a latency-critical thread
+ * where the implicit synchronisation of an allocation is not acceptable. pj_index_records grows a
+ * per-context scratch buffer on demand; this variant does the same work with its scratch (one 32-bit
+ * count per 16 KiB of input) in a fixed array that is part of the loaded library image, at most
+ * PJ_STATIC_INDEX_MAX_BYTES of input per call (PJ_ERR_TOO_LARGE beyond that).
+ *   - `in`, `rec_start` (room for `cap` offsets) and `n_device` (one uint64) are DEVICE memory of the
+ *     device that is current for the calling thread; nothing is copied to the host.
+ *   - The kernels are enqueued on `stream` (a cudaStream_t, NULL = the default stream) and the call
+ *     returns without waiting: read *n_device and rec_start after synchronising that stream. If more than
+ *     `cap` records are found, *n_device still holds the true count and only the first `cap` are stored.
+ *   - It calls no allocating routine. Its first call on each device looks up the device address of the
+ *     fixed array (a driver query, not an allocation); make that first call before any stream capture.
+ *   - Every GPU that loads the library holds the array (about 256 KiB) until the process exits. All calls
+ *     on a device share it: two calls whose kernels can overlap on the GPU (different streams) race and
+ *     give undefined offsets; calls on one stream are ordered and safe. Nothing in it needs clearing
+ *     between calls: every word a call reads, that call has written first. */
+#define PJ_STATIC_INDEX_MAX_BYTES (1ull << 30)
+pj_status pj_index_records_static(const uint8_t* in, uint64_t len, uint64_t* rec_start, uint64_t cap,
+                                  uint64_t* n_device, void* stream);
+
 /* Replaces ObjectMapper#writeValueAsBytes / the response body encoder (MyEntityController.java:48-51)
  * for a whole table: serialises rows [0, cols->n_rows[type]) of the model table(s) of `schema`
  * (for PJ_SCHEMA_MIXED: records in PJ_COL_REC_TYPE / PJ_COL_REC_ROW order, PJ_TYPE_NONE skipped).

@@ -55,6 +55,7 @@ def lib() -> C.CDLL:
         L.pj_parse.argtypes = [C.c_void_p, u32, u32, C.c_void_p, u64, u32, C.POINTER(abi.pj_columns)]
         L.pj_parse_shard.argtypes = [C.c_void_p, u32, C.c_void_p, u64, u64, i32, i32, u64, u32, C.POINTER(abi.pj_columns)]
         L.pj_index_records.argtypes = [C.c_void_p, u32, C.c_void_p, u64, u32, C.c_void_p, u64, C.POINTER(u64)]
+        L.pj_index_records_static.argtypes = [C.c_void_p, u64, C.c_void_p, u64, C.c_void_p, C.c_void_p]
         L.pj_write.argtypes = [C.c_void_p, u32, u32, C.POINTER(abi.pj_columns), C.c_void_p, u64, u32, C.POINTER(u64)]
         L.pj_gen_text.argtypes = [u32, u64, u64, u64, u32, C.c_void_p, u64, C.POINTER(u64)]
         L.pj_gen_columns.argtypes = [u32, u64, u64, u64, u32, C.POINTER(abi.pj_columns)]
@@ -252,3 +253,13 @@ class Context:
         st = lib().pj_write(self._h, schema, framing, C.byref(cols.raw), p, cap, kind, C.byref(ln))
         self._check(st, "pj_write", (abi.PJ_ERR_CAPACITY,) if allow_capacity else ())
         return int(ln.value)
+
+
+def index_records_static(buf, rec_start, n_out, stream: int | None = None) -> None:
+    """pj_index_records_static: the allocation-free record index. `buf` (uint8), `rec_start` (8-byte elements)
+    and `n_out` (one 8-byte element) are CUDA tensors on the current device; the work is only enqueued on
+    `stream` (a raw cudaStream_t value, default stream when None), so synchronise before reading."""
+    assert buf.is_cuda and rec_start.is_cuda and n_out.is_cuda and buf.is_contiguous()
+    st = lib().pj_index_records_static(buf.data_ptr(), buf.numel(), rec_start.data_ptr(), rec_start.numel(), n_out.data_ptr(), stream)
+    if st != abi.PJ_OK:
+        raise PetJsonError(st, "pj_index_records_static", (lib().pj_last_error(None) or b"").decode())

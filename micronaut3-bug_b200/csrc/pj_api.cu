@@ -572,6 +572,51 @@ pj_status pj_index_records(pj_ctx* c, uint32_t framing, const uint8_t* in, uint6
   return *n > cap ? set_err(c, PJ_ERR_CAPACITY, "pj_index_records: %llu records, room for %llu", (unsigned long long)*n, (unsigned long long)cap) : PJ_OK;
 }
 
+/* ---- the allocation-free record index -------------------------------------------------------------
+ * Scratch of pj_index_records_static: one count per 16 KiB tile of the largest accepted input, plus the
+ * closing entry the scan writes. It lives in the library image; in host code its name only stands for
+ * the symbol, so the device address is looked up once per device (static_scratch_for). */
+static constexpr uint64_t STATIC_INDEX_TILES = (PJ_STATIC_INDEX_MAX_BYTES + 15 + INDEX_TILE) / INDEX_TILE;
+static __device__ __align__(256) uint32_t g_static_index_scratch[STATIC_INDEX_TILES + 1];
+
+static uint32_t* static_scratch_for(int device, cudaError_t* err) {
+  static uint32_t* addr[64] = {};
+  *err = cudaSuccess;
+  if (device < 0 || device >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+  uint32_t* p = __atomic_load_n(&addr[device], __ATOMIC_ACQUIRE);
+  if (!p) {
+    /* the calling thread's current device is `device`: the address is that device's copy of the array */
+    *err = cudaGetSymbolAddress((void**)&p, g_static_index_scratch);
+    if (*err != cudaSuccess) return nullptr;
+    __atomic_store_n(&addr[device], p, __ATOMIC_RELEASE);
+  }
+  return p;
+}
+
+pj_status pj_index_records_static(const uint8_t* in, uint64_t len, uint64_t* rec_start, uint64_t cap, uint64_t* n_device,
+                                  void* stream) {
+  if ((!in && len) || !n_device || (!rec_start && cap)) return set_err(nullptr, PJ_ERR_ARG, "pj_index_records_static: bad argument");
+  if (len > PJ_STATIC_INDEX_MAX_BYTES)
+    return set_err(nullptr, PJ_ERR_TOO_LARGE, "pj_index_records_static: %llu input bytes, the fixed scratch serves at most %llu",
+                   (unsigned long long)len, (unsigned long long)PJ_STATIC_INDEX_MAX_BYTES);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return set_err(nullptr, PJ_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  uint32_t* tile = static_scratch_for(device, &e);
+  if (!tile) return set_err(nullptr, PJ_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+  const uint64_t ntiles = (len + 15 + INDEX_TILE) / INDEX_TILE; /* <= STATIC_INDEX_TILES by the size check */
+  cudaStream_t st = (cudaStream_t)stream;
+  IndexArgs ia;
+  ia.in = in; ia.len = len; ia.limit = len; ia.is_first = 1; ia.is_last = 1;
+  ia.tile = tile; ia.rec_start = rec_start; ia.cap = cap; ia.goff = 0;
+  k_nd_index<false><<<(unsigned)ntiles, INDEX_THREADS, 0, st>>>(ia);
+  k_scan_single<uint32_t><<<1, 1024, 0, st>>>(tile, ntiles, (unsigned long long*)n_device);
+  k_nd_index<true><<<(unsigned)ntiles, INDEX_THREADS, 0, st>>>(ia);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_err(nullptr, PJ_ERR_CUDA, "pj_index_records_static launch: %s", cudaGetErrorString(e));
+  return PJ_OK;
+}
+
 pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_columns* cols, uint8_t* out, uint64_t cap,
                    uint32_t out_kind, uint64_t* out_len) {
   if (!c) return PJ_ERR_ARG;
