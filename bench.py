@@ -203,6 +203,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # NCCL's version banner must not land on stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     R = args.records
     PET = abi.PJ_SCHEMA_PET
@@ -226,7 +227,7 @@ def main():
 
     def step_device():
         if sharded:
-            return sharded.parse(d_text, nbytes, cols)
+            return sharded.parse(d_text, nbytes, cols, wait=False)
         ctx.parse(PET, d_text[:nbytes], cols)
         return None
 
@@ -244,6 +245,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     dev_ms = 0.0
     stitch_ms = 0.0
+    pending = []
     e0.record(stream)
     for _ in range(args.steps):
         info = step_device()
@@ -252,12 +254,13 @@ def main():
         dev_ms += st.device_ms
         stage_ms += np.array(list(st.stage_ms))
         if info:
-            stitch_ms += info["stitch_ms"]
+            pending.append(info)
     e1.record(stream)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     ms = e0.elapsed_time(e1)
+    stitch_ms = sum(p.result()["stitch_ms"] for p in pending)
     clocks = sampler.stop() if rank == 0 else None
     n_rec = cols.n_records
     last_stats = ctx.stats()
@@ -266,6 +269,10 @@ def main():
         t = torch.tensor([ms, dev_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, dev_ms = float(t[0]), float(t[1])
+        kms = torch.zeros(world, device=dev, dtype=torch.float64)
+        kms[rank] = stage_ms[2] / args.steps
+        dist.all_reduce(kms)
+        per_rank_kernel_ms = kms.tolist()
         cnt = torch.tensor([n_rec, launches], device=dev, dtype=torch.int64)
         dist.all_reduce(cnt)
         total_rec, launches = int(cnt[0]), int(cnt[1])
@@ -358,6 +365,7 @@ def main():
     }
     if sharded:
         line["stitch_ms_per_step"] = stitch_ms / args.steps
+        line["tile_kernel_ms_per_rank"] = per_rank_kernel_ms
     if w_ms:
         wa = w_alg / (w_dev_ms / wsteps * 1e-3) / 1e9
         line["reserialise"] = {"records_per_s": R * wsteps / (w_ms * 1e-3), "gb_per_s_out": nbytes * wsteps / (w_ms * 1e-3) / 1e9, "ms_per_step": w_ms / wsteps,

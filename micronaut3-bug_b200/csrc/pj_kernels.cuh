@@ -533,8 +533,10 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
 
   const long long c0 = clock64();
   /* ---- stage the tile's bytes ------------------------------------------------------------------ */
-  bool fits = false;
+  /* As much of the tile's span as the window holds; a record is read from the window when all of its bytes
+     are in it (for the last record of the input that means: the window reaches the end of the input). */
   int64_t w0 = 0;
+  uint64_t win_hi = 0; /* input offset of the first byte that is not staged */
   if (nrec) {
     const uint64_t span_lo = rec_start[r0] - a.goff;
     uint64_t span_hi;
@@ -542,19 +544,25 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
     else span_hi = r0 + nrec < N ? rec_start[r0 + nrec] - a.goff : a.limit;
     const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(a.in + span_lo) & 15u);
     w0 = (int64_t)span_lo - mis;
-    const uint64_t copy_hi = a.limit < span_hi + 32 ? a.limit : span_hi + 32;
-    const uint64_t nbytes = (uint64_t)((int64_t)copy_hi - w0);
-    fits = nbytes + 64 <= a.win_bytes;
-    if (fits) {
-      const uint4* src = reinterpret_cast<const uint4*>(a.in + w0);
-      uint4* dst = reinterpret_cast<uint4*>(win);
-      const uint32_t n16 = (uint32_t)((nbytes + 15) >> 4);
-      for (uint32_t k = tid; k < n16; k += TILE_THREADS) dst[k] = __ldg(src + k);
-      __syncthreads();
-      if (tid < 32) win[nbytes + tid] = '\n';
-    }
+    const uint64_t need_hi = a.limit < span_hi + 32 ? a.limit : span_hi + 32;
+    const uint64_t cap_hi = (uint64_t)(w0 + (int64_t)a.win_bytes - 64);
+    win_hi = need_hi < cap_hi ? need_hi : cap_hi;
+    const uint64_t nbytes = (uint64_t)((int64_t)win_hi - w0);
+    const uint4* src = reinterpret_cast<const uint4*>(a.in + w0);
+    uint4* dst = reinterpret_cast<uint4*>(win);
+    const uint32_t n16 = (uint32_t)((nbytes + 15) >> 4);
+    for (uint32_t k = tid; k < n16; k += TILE_THREADS) dst[k] = __ldg(src + k);
+    __syncthreads();
+    if (tid < 32) win[nbytes + tid] = '\n';
   }
   __syncthreads();
+  uint64_t my_end = !active ? 0 : (a.rec_end ? a.rec_end[i] : (i + 1 < N ? rec_start[i + 1] - a.goff : a.limit));
+  if (active && !a.rec_end && i + 1 == N && my_end > win_hi && start < win_hi) {
+    /* the last record of a shard with slack: it ends at its LF, which may well be staged */
+    for (uint32_t q = (uint32_t)((int64_t)start - w0), qe = (uint32_t)((int64_t)win_hi - w0); q < qe; ++q)
+      if (win[q] == '\n') { my_end = (uint64_t)(w0 + (int64_t)q) + 1; break; }
+  }
+  const bool fits = active && my_end <= win_hi;
 
   const long long c1 = clock64();
   /* ---- tokenise every record once ------------------------------------------------------------------ */

@@ -34,25 +34,37 @@ class ShardedParser:
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
+        self._plan = None
 
-    def parse(self, buf: torch.Tensor, nbytes: int, out) -> dict:
+    def plan(self, nbytes: int, device) -> dict:
+        """Exchanges the shard sizes (one small all-gather) and derives what every later parse of shards of
+        these sizes needs: global byte offset, how much of the next shard to fetch, whether the stream ends in
+        this shard's view. Cached while `nbytes` stays the same, so steady-state steps skip it."""
+        if self._plan is not None and self._plan["nbytes"] == nbytes:
+            return self._plan
+        r, w = self.rank, self.world
+        sizes_h = self._all_gather(torch.tensor([nbytes], dtype=torch.int64, device=device)).view(-1).tolist()
+        self._plan = {"nbytes": nbytes, "sizes": sizes_h, "goff": int(sum(sizes_h[:r])),
+                      "recv_n": min(self.slack, sizes_h[r + 1]) if r + 1 < w else 0,
+                      "send_n": min(self.slack, nbytes) if r > 0 else 0,
+                      "is_last": r == w - 1 or (r + 1 == w - 1 and sizes_h[r + 1] <= self.slack)}
+        return self._plan
+
+    def parse(self, buf: torch.Tensor, nbytes: int, out, wait: bool = True):
         """`buf` holds this rank's `nbytes` bytes followed by at least `slack` writable bytes.
-        Fills `out` with this shard's columns (offsets local to the shard) and returns the stitch:
-        global byte offset, global first record / row / arena positions, totals, and the time spent
-        on the exchange."""
+        Fills `out` with this shard's columns (offsets local to the shard). With wait=True returns the stitch
+        (global byte offset, global first record / row / arena positions, totals, time spent on the exchange);
+        with wait=False the counter all-gather is only enqueued and the returned object's .result() gives the
+        stitch later, so consecutive steps do not stop for it."""
         g, r, w = self.group, self.rank, self.world
         on_gpu = buf.is_cuda
         t0 = time.perf_counter()
+        plan = self.plan(nbytes, buf.device)
+        recv_n, send_n = plan["recv_n"], plan["send_n"]
         if on_gpu:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
-        # 1. shard sizes -> global byte offsets and how much of the next shard each rank may read
-        sizes_h = self._all_gather(torch.tensor([nbytes], dtype=torch.int64, device=buf.device)).view(-1).tolist()
-        goff = int(sum(sizes_h[:r]))
-        recv_n = min(self.slack, sizes_h[r + 1]) if r + 1 < w else 0
-        send_n = min(self.slack, nbytes) if r > 0 else 0
-        is_last = r == w - 1 or (r + 1 == w - 1 and sizes_h[r + 1] <= self.slack)
-        # 2. the head of the next shard becomes this shard's slack
+        # the head of the next shard becomes this shard's slack
         ops = []
         if send_n:
             ops.append(dist.P2POp(dist.isend, buf[:send_n], self._peer(r - 1), group=g))
@@ -60,16 +72,13 @@ class ShardedParser:
             ops.append(dist.P2POp(dist.irecv, buf[nbytes:nbytes + recv_n], self._peer(r + 1), group=g))
         if ops:
             for req in dist.batch_isend_irecv(ops):
-                req.wait()
+                req.wait()  # on GPUs: orders the current stream after the transfer, does not block the host
         if on_gpu:
             ev1.record()
-            torch.cuda.current_stream().synchronize()
-            exchange_ms = ev0.elapsed_time(ev1)
-        else:
-            exchange_ms = 1e3 * (time.perf_counter() - t0)
-        # 3. the local parse
-        self.engine.parse_shard(self.schema, buf, nbytes, recv_n, r == 0, is_last, goff, out)
-        # 4. counters -> global bases
+        exchange_host_ms = 1e3 * (time.perf_counter() - t0)
+        # the local parse
+        self.engine.parse_shard(self.schema, buf, nbytes, recv_n, r == 0, plan["is_last"], plan["goff"], out)
+        # counters -> global bases
         t1 = time.perf_counter()
         c = torch.zeros(N_COUNTERS, dtype=torch.int64)
         c[0], c[1] = out.n_records, out.n_errors
@@ -78,20 +87,17 @@ class ShardedParser:
         c[5] = nbytes
         for col in abi.schema_columns(self.schema):
             c[6 + col.id] = out.count(col.id)
-        allc = self._all_gather(c.to(buf.device)).numpy()
-        gather_ms = 1e3 * (time.perf_counter() - t1)
-        before = allc[:r].sum(axis=0)
-        total = allc.sum(axis=0)
-        # an _OFF column of a shard has rows + 1 entries; globally the closing entries collapse
-        bases, totals = {}, {}
-        for col in abi.schema_columns(self.schema):
-            closing = 1 if col.shape.endswith("+1") else 0
-            bases[col.name] = int(before[6 + col.id] - closing * r)
-            totals[col.name] = int(total[6 + col.id] - closing * (w - 1))
-        return {"global_offset": goff, "first_record": int(before[0]), "total_records": int(total[0]), "total_errors": int(total[1]),
-                "first_row": {t: int(before[1 + t]) for t in (1, 2, 3)}, "total_rows": {t: int(total[1 + t]) for t in (1, 2, 3)},
-                "column_base": bases, "column_total": totals, "slack_used": recv_n, "is_last": is_last,
-                "stitch_ms": exchange_ms + gather_ms, "exchange_ms": exchange_ms, "gather_ms": gather_ms}
+        c = c.to(buf.device)
+        if on_gpu:
+            gathered = torch.empty(w * N_COUNTERS, dtype=torch.int64, device=buf.device)
+            dist.all_gather_into_tensor(gathered, c, group=g)
+        else:
+            parts = [torch.empty_like(c) for _ in range(w)]
+            dist.all_gather(parts, c, group=g)
+            gathered = torch.stack(parts)
+        gather_host_ms = 1e3 * (time.perf_counter() - t1)
+        pending = _Pending(self, plan, gathered, (ev0, ev1) if on_gpu else None, exchange_host_ms, gather_host_ms)
+        return pending.result() if wait else pending
 
     def _all_gather(self, t: torch.Tensor) -> torch.Tensor:
         """[world, len(t)] on the host."""
@@ -105,6 +111,31 @@ class ShardedParser:
 
     def _peer(self, group_rank: int) -> int:
         return dist.get_global_rank(self.group, group_rank) if self.group is not None else group_rank
+
+
+class _Pending:
+    """The stitch of one ShardedParser.parse call whose counter all-gather may still be in flight."""
+
+    def __init__(self, sp: ShardedParser, plan: dict, gathered: torch.Tensor, events, exchange_host_ms: float, gather_host_ms: float):
+        self.sp, self.plan, self.gathered, self.events = sp, plan, gathered, events
+        self.exchange_host_ms, self.gather_host_ms = exchange_host_ms, gather_host_ms
+
+    def result(self) -> dict:
+        sp, r, w = self.sp, self.sp.rank, self.sp.world
+        allc = self.gathered.view(w, N_COUNTERS).cpu().numpy()  # synchronises with the all-gather
+        exchange_ms = self.events[0].elapsed_time(self.events[1]) if self.events else self.exchange_host_ms
+        before = allc[:r].sum(axis=0)
+        total = allc.sum(axis=0)
+        # an _OFF column of a shard has rows + 1 entries; globally the closing entries collapse
+        bases, totals = {}, {}
+        for col in abi.schema_columns(sp.schema):
+            closing = 1 if col.shape.endswith("+1") else 0
+            bases[col.name] = int(before[6 + col.id] - closing * r)
+            totals[col.name] = int(total[6 + col.id] - closing * (w - 1))
+        return {"global_offset": self.plan["goff"], "first_record": int(before[0]), "total_records": int(total[0]), "total_errors": int(total[1]),
+                "first_row": {t: int(before[1 + t]) for t in (1, 2, 3)}, "total_rows": {t: int(total[1 + t]) for t in (1, 2, 3)},
+                "column_base": bases, "column_total": totals, "slack_used": self.plan["recv_n"], "is_last": self.plan["is_last"],
+                "stitch_ms": exchange_ms + self.gather_host_ms, "exchange_ms": exchange_ms, "gather_ms": self.gather_host_ms}
 
 
 def split_even(total_bytes: int, world: int) -> list[tuple[int, int]]:
