@@ -182,6 +182,7 @@ def main():
     ap.add_argument("--records", type=int, default=1_000_000, help="records per GPU and step")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="pet", choices=["pet", "mixed"], help="pet: 1M Pet records (the headline configuration); mixed: Pet/Order/User 50/30/20 with 1%% malformed")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -206,10 +207,15 @@ def main():
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # NCCL's version banner must not land on stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     R = args.records
-    PET = abi.PJ_SCHEMA_PET
+    mixed_wl = args.workload == "mixed"
+    PET = abi.PJ_SCHEMA_MIXED if mixed_wl else abi.PJ_SCHEMA_PET  # the schema of the timed workload
+    gen_flags = abi.PJ_GEN_MALFORMED if mixed_wl else 0
+    if mixed_wl:
+        args.no_e2e = True
+        args.no_cpu_baseline = True
 
     # ---- workload: this rank's byte range of the stream = its R records ------------------------------
-    text_np = pj.gen_text(PET, SEED, rank * R, R, 0)
+    text_np = pj.gen_text(PET, SEED, rank * R, R, gen_flags)
     nbytes = int(text_np.size)
     h_text = torch.empty(nbytes + SLACK, dtype=torch.uint8).pin_memory()
     h_text[:nbytes].copy_(torch.from_numpy(text_np))
@@ -279,13 +285,13 @@ def main():
     else:
         total_rec = n_rec
     if not sharded:
-        assert n_rec == R and cols.n_errors == 0, (n_rec, cols.n_errors)
+        assert n_rec == R and (mixed_wl or cols.n_errors == 0), (n_rec, cols.n_errors)
 
     # ---- the reverse direction on the parsed columns ------------------------------------------------------
     d_out = torch.empty(nbytes + 64, dtype=torch.uint8, device=dev)
     w_ms, w_dev_ms, w_launch, w_alg, w_len = 0.0, 0.0, 0, 0, 0
     wsteps = max(3, args.steps // 2)
-    if not sharded:
+    if not sharded and not mixed_wl:
         for _ in range(3):
             ctx.write(PET, cols, d_out)
         torch.cuda.synchronize()
@@ -346,7 +352,7 @@ def main():
         "vs_baseline": None,
         "dtype": "u8",
         "data": "synthetic",
-        "config": {"workload": "1M Pet records as NDJSON, one record per line (BASELINE configs[1])", "records_per_gpu": R, "seed": SEED,
+        "config": {"workload": "Pet/Order/User 50/30/20 with 1% malformed records as NDJSON (BASELINE configs[2] distributions)" if mixed_wl else "1M Pet records as NDJSON, one record per line (BASELINE configs[1])", "records_per_gpu": R, "seed": SEED,
                    "input_bytes_per_gpu": nbytes, "l2": "input (292 MB at 1M records) and columns are larger than the 126 MB L2; no flush between steps",
                    "sharding": "one byte range per GPU, 64 KiB slack from the next rank, counters all-gathered" if world > 1 else "single GPU"},
         "gb_per_s": total_rec * args.steps / (ms * 1e-3) * nbytes / R / 1e9,

@@ -13,6 +13,7 @@
 
 #include "petjson.h"
 #include "pj_kernels.cuh"
+#include "pj_array_kernels.cuh"
 
 using namespace pj;
 
@@ -175,7 +176,9 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   if (!out || (!in && len + slack) || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED || in_kind > PJ_MEM_DEVICE ||
       out->mem_kind > PJ_MEM_DEVICE)
     return set_err(c, PJ_ERR_ARG, "pj_parse: bad argument");
-  if (framing != PJ_FRAMING_NDJSON) return set_err(c, PJ_ERR_ARG, "pj_parse: framing %u is not available", framing);
+  if (framing > PJ_FRAMING_ARRAY) return set_err(c, PJ_ERR_ARG, "pj_parse: unknown framing %u", framing);
+  const bool array = framing == PJ_FRAMING_ARRAY;
+  if (array && (slack || !is_first || !is_last)) return set_err(c, PJ_ERR_ARG, "pj_parse: array framing cannot be sharded");
   const uint64_t limit = len + slack;
   if (limit >= (1ull << 32)) return set_err(c, PJ_ERR_TOO_LARGE, "pj_parse: %llu input bytes do not fit 32-bit offsets", (unsigned long long)limit);
   DeviceGuard guard(c->device);
@@ -219,8 +222,9 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   for (int i = 0; i < nneed; ++i) fa.cap_elems[need[i]] = out->col[need[i]].bytes / col_info(need[i])->elem;
   for (int i = 0; i < nrc; ++i) if (fa.cap_elems[rcols[i]] < cap_records) cap_records = fa.cap_elems[rcols[i]];
   if (cap_records > (1ull << 32)) cap_records = 1ull << 32;
-  /* no more records than candidate line starts */
-  if (cap_records > limit / 2 + 2) cap_records = limit / 2 + 2;
+  /* no more records than candidate line starts (NDJSON: a record needs a byte and an LF) or separators (array) */
+  if (!array && cap_records > limit / 2 + 2) cap_records = limit / 2 + 2;
+  if (array && cap_records > limit + 2) cap_records = limit + 2;
   fa.cap_records = cap_records;
   fa.res = c->d_res;
   fa.cols = dcols;
@@ -233,9 +237,19 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   const uint64_t stride = align_up(cap_records + 1, 4);
   const uint32_t nchunks = (uint32_t)((cap_records + 1 + SCAN_CHUNK - 1) / SCAN_CHUNK);
   size_t off_tile = 0;
-  size_t off_cnt = align_up(off_tile + (ntiles + 1) * 4, 256);
+  size_t off_cnt = align_up(off_tile + ((ntiles > (len >> 14) + 2 ? ntiles : (len >> 14) + 2) + 1) * 4, 256);
   size_t off_part = align_up(off_cnt + (c->staged ? (size_t)nslots * stride * 4 : 0), 256);
-  size_t total_scratch = off_part + (c->staged ? (size_t)nslots * nchunks * 4 : 0) + 256;
+  size_t off_arr = align_up(off_part + (c->staged ? (size_t)nslots * nchunks * 4 : 0), 256);
+  const uint64_t nwords = (len + 63) >> 6;
+  const uint64_t atiles = nwords ? (nwords + ARR_THREADS - 1) / ARR_THREADS : 1;
+  size_t off_fn = off_arr, off_tin = 0, off_sep = 0, off_rend = 0, off_rblank = 0, total_scratch = off_arr + 256;
+  if (array) {
+    off_tin = align_up(off_fn + atiles * sizeof(ArrFn), 256);
+    off_sep = align_up(off_tin + atiles * sizeof(ArrState), 256);
+    off_rend = align_up(off_sep + (nwords + 1) * 8, 256);
+    off_rblank = align_up(off_rend + cap_records * 8, 256);
+    total_scratch = off_rblank + cap_records + 256;
+  }
   { pj_status st = ensure(c, &c->scratch, total_scratch); if (st) return st; }
   uint32_t* d_tile = (uint32_t*)((uint8_t*)c->scratch.p + off_tile);
   uint32_t* d_cnt = (uint32_t*)((uint8_t*)c->scratch.p + off_cnt);
@@ -245,13 +259,36 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   Stage stage(c);
 
   /* stage 0: record index */
-  IndexArgs ia;
-  ia.in = d_in; ia.len = len; ia.limit = limit; ia.is_first = is_first; ia.is_last = is_last;
-  ia.tile = d_tile; ia.rec_start = (uint64_t*)dcols.ptr[PJ_COL_REC_START]; ia.cap = cap_records; ia.goff = goff;
-  k_nd_index<false><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
-  k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles, &c->d_res->n_records);
-  k_nd_index<true><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
-  count_launch(c, 0, 3);
+  uint64_t* d_rec_end = nullptr;
+  uint8_t* d_rec_blank = nullptr;
+  if (!array) {
+    IndexArgs ia;
+    ia.in = d_in; ia.len = len; ia.limit = limit; ia.is_first = is_first; ia.is_last = is_last;
+    ia.tile = d_tile; ia.rec_start = (uint64_t*)dcols.ptr[PJ_COL_REC_START]; ia.cap = cap_records; ia.goff = goff;
+    k_nd_index<false><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
+    k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles, &c->d_res->n_records);
+    k_nd_index<true><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
+    count_launch(c, 0, 3);
+  } else {
+    d_rec_end = (uint64_t*)((uint8_t*)c->scratch.p + off_rend);
+    d_rec_blank = (uint8_t*)c->scratch.p + off_rblank;
+    ArrArgs aa;
+    aa.in = d_in; aa.len = len; aa.nwords = nwords;
+    aa.tile_fn = (ArrFn*)((uint8_t*)c->scratch.p + off_fn); aa.tile_in = (ArrState*)((uint8_t*)c->scratch.p + off_tin);
+    aa.sep = (uint64_t*)((uint8_t*)c->scratch.p + off_sep); aa.tile_cnt = d_tile;
+    aa.rec_start = (uint64_t*)dcols.ptr[PJ_COL_REC_START]; aa.rec_end = d_rec_end; aa.rec_blank = d_rec_blank;
+    aa.cap = cap_records; aa.goff = goff; aa.ntiles = (uint32_t)atiles; aa.res = c->d_res;
+    /* the two running minima start at "none" */
+    PJ_CUDA(c, cudaMemsetAsync(&c->d_res->doc_err_off, 0xFF, sizeof(unsigned long long), c->stream));
+    PJ_CUDA(c, cudaMemsetAsync(&c->d_res->first_opener, 0xFF, sizeof(unsigned long long), c->stream));
+    k_arr_summary<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+    k_arr_scan_tiles<<<1, 32, 0, c->stream>>>(aa);
+    k_arr_mark<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+    k_arr_records<false><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+    k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, atiles, &c->d_res->n_records);
+    k_arr_records<true><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+    count_launch(c, 0, 6);
+  }
   PJ_CUDA(c, cudaGetLastError());
   stage.next();
 
@@ -260,9 +297,9 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
     /* stage 1: size pass */
     ParseArgs pa;
     pa.in = d_in; pa.limit = limit; pa.goff = goff; pa.cap_records = cap_records;
-    pa.lf_ws = 0; pa.open_end = is_last ? 0u : 1u; pa.schema = schema; pa.slot_lo = slot_lo; pa.slot_hi = slot_hi;
+    pa.lf_ws = array ? 1u : 0u; pa.open_end = is_last ? 0u : 1u; pa.schema = schema; pa.slot_lo = slot_lo; pa.slot_hi = slot_hi;
     pa.cnt = d_cnt - (size_t)slot_lo * stride; /* indexed by absolute slot */
-    pa.stride = stride; pa.rec_end = nullptr; pa.rec_blank = nullptr; pa.res = c->d_res; pa.cols = dcols;
+    pa.stride = stride; pa.rec_end = d_rec_end; pa.rec_blank = d_rec_blank; pa.res = c->d_res; pa.cols = dcols;
     const int pgrid = persistent_grid(c, cap_records, PARSE_THREADS);
     k_parse_size<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
     count_launch(c, 1);
@@ -298,7 +335,7 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
     TileArgs ta;
     memset(&ta, 0, sizeof ta);
     ta.in = d_in; ta.limit = limit; ta.goff = goff; ta.n_records = N0;
-    ta.lf_ws = 0; ta.open_end = is_last ? 0u : 1u; ta.schema = schema; ta.slot_lo = slot_lo; ta.slot_hi = slot_hi;
+    ta.lf_ws = array ? 1u : 0u; ta.open_end = is_last ? 0u : 1u; ta.schema = schema; ta.slot_lo = slot_lo; ta.slot_hi = slot_hi;
     ta.win_bytes = TILE_WIN_BYTES; ta.tape_cap = TILE_TAPE_CAP;
     /* as many records per tile as fit the staging window on average */
     const uint64_t avg = N0 ? limit / N0 + 1 : 1;
@@ -308,7 +345,7 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
     const uint64_t ntiles = N0 ? (N0 + tile_recs - 1) / tile_recs : 1;
     ta.ntiles = (uint32_t)ntiles;
     c->stats.tile_records = tile_recs; c->stats.tiles = (uint32_t)ntiles;
-    ta.rec_end = nullptr; ta.rec_blank = nullptr;
+    ta.rec_end = d_rec_end; ta.rec_blank = d_rec_blank;
     const uint64_t nstates = ntiles; /* one look-back state per block */
     { pj_status st = ensure(c, &c->tiles, nstates * sizeof(TileState) + 256); if (st) return st; }
     ta.ticket = (uint32_t*)c->tiles.p;
@@ -356,6 +393,10 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   out->n_records = N;
   out->n_errors = r.n_errors;
   out->doc_err_kind = 0; out->doc_err_off = 0;
+  if (array) {
+    if (r.doc_err_off != ~0ull) { out->doc_err_kind = PJ_E_SYNTAX; out->doc_err_off = r.doc_err_off; }
+    else if (r.first_opener == ~0ull || r.arr_final_s || r.arr_final_d != 0) { out->doc_err_kind = PJ_E_EOF; out->doc_err_off = len; }
+  }
   for (int t = 0; t < 4; ++t) out->n_rows[t] = 0;
   if (schema == PJ_SCHEMA_MIXED) { out->n_rows[1] = r.total[SLOT_ROWS_PET]; out->n_rows[2] = r.total[SLOT_ROWS_ORD]; out->n_rows[3] = r.total[SLOT_ROWS_USR]; }
   else out->n_rows[schema] = N;

@@ -38,7 +38,7 @@ def gpu_parse_device(ctx, schema, buf, framing=NDJSON, misalign=0):
     return out
 
 
-@pytest.mark.parametrize("case", [c for c in CASES if c[2] == "ndjson"], ids=[c[0] for c in CASES if c[2] == "ndjson"])
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
 def test_known_answers_on_gpu(ctx, case):
     check_case(lambda sch, buf, fr: gpu_parse_host(ctx, sch, buf, fr), *case)
 
@@ -267,3 +267,62 @@ def test_many_tiny_records(ctx, oracle):
     body = as_u8(b"{}\n" * 70000 + b"x\n" * 30000 + b'{"id":1}\n' * 50000)
     for schema in (2, 3, 4):
         assert same_result(oracle.parse(schema, body), gpu_parse_device(ctx, schema, body)) == ""
+
+
+# ---- array framing -----------------------------------------------------------------------------------
+ARRAY_FLAG_SETS = [abi.PJ_GEN_ARRAY, abi.PJ_GEN_ARRAY | abi.PJ_GEN_WHITESPACE | abi.PJ_GEN_ESCAPES,
+                   abi.PJ_GEN_ARRAY | abi.PJ_GEN_WHITESPACE | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_MALFORMED | abi.PJ_GEN_SPARSE]
+
+
+def same_doc(a, b) -> bool:
+    return (int(a.raw.doc_err_kind), int(a.raw.doc_err_off)) == (int(b.raw.doc_err_kind), int(b.raw.doc_err_off))
+
+
+@pytest.mark.parametrize("schema", [1, 2, 3, 4])
+@pytest.mark.parametrize("flags", ARRAY_FLAG_SETS)
+def test_array_framing_generated(ctx, oracle, schema, flags):
+    """The first benchmark configuration's shape (a JSON array of records) at 1 000 and 20 000 records."""
+    for n in (1000, 20000):
+        text = pj.gen_text(schema, 0x5EED, 0, n, flags)
+        want = oracle.parse(schema, text, ARRAY)
+        got = gpu_parse_device(ctx, schema, text, ARRAY)
+        assert same_result(want, got) == "" and same_doc(want, got)
+        assert same_result(want, gpu_parse_host(ctx, schema, text, ARRAY)) == ""
+    assert same_result(want, pj.gen_columns(schema, 0x5EED, 0, 20000, flags, text.size)) == ""
+
+
+def test_array_framing_mutated(ctx, oracle):
+    rng = random.Random(99)
+    special = [b'"', b"\\", b"\\\\", b'\\"', b"[", b"]", b"{", b"}", b",", b" ", b"\n", b"\\" * 63, b"\\" * 64, b"\\" * 65, b'"a,b]"', b"[]", b"x"]
+    for rnd in range(40):
+        body = bytearray(pj.gen_text(rng.choice([1, 4]), 200 + rnd, 0, rng.choice([1, 40, 400]), abi.PJ_GEN_ARRAY | rng.choice([0, abi.PJ_GEN_ESCAPES, abi.PJ_GEN_WHITESPACE])))
+        for _ in range(rng.randrange(0, 6)):
+            pos = rng.randrange(len(body) + 1)
+            body[pos:pos] = rng.choice(special)
+        if rnd % 5 == 0:
+            body = body[: rng.randrange(len(body))]
+        buf = as_u8(bytes(body))
+        want = oracle.parse(1, buf, ARRAY)
+        got = gpu_parse_device(ctx, 1, buf, ARRAY, misalign=rnd % 3)
+        assert same_result(want, got) == "" and same_doc(want, got), rnd
+
+
+@pytest.mark.parametrize("run", [1, 62, 63, 64, 65, 127, 128, 16383, 16384, 16385])
+def test_array_backslash_runs_across_word_and_tile_edges(ctx, oracle, run):
+    """Escape parity, in-string state and depth must carry across 64-byte words and 16 KiB tiles."""
+    for lead in (0, 1, 17):
+        body = b"[" + b" " * lead + b'{"name":"' + b"\\" * run + b'","photoUrls":["[,]{}"]},{"name":"b","photoUrls":[]}]'
+        buf = as_u8(body)
+        want = oracle.parse(1, buf, ARRAY)
+        got = gpu_parse_device(ctx, 1, buf, ARRAY)
+        assert same_result(want, got) == "" and same_doc(want, got)
+
+
+def test_array_framing_with_the_staged_pipeline(native, oracle):
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    text = pj.gen_text(4, 5, 0, 3000, abi.PJ_GEN_ARRAY | abi.PJ_GEN_WHITESPACE | abi.PJ_GEN_MALFORMED)
+    with native.Context(device=0, flags=abi.PJ_OPT_STAGED_PIPELINE) as c:
+        assert same_result(oracle.parse(4, text, ARRAY), gpu_parse_device(c, 4, text, ARRAY)) == ""
