@@ -4,7 +4,7 @@
  *
  * fast_record<>() reads a record 8 bytes at a time from a window staged in shared memory and accepts
  * it only when it is "plain": valid, every key known and met once, no null, no escape, printable
- * ASCII strings, no date-time. Such a record never needs the byte-at-a-time machinery of
+ * ASCII strings. Such a record never needs the byte-at-a-time machinery of
  * pj_core.cuh, so its values, counts and the place of every string are known after ONE pass; they
  * are kept (values in registers, strings as 8-byte tape entries in shared memory) until the record's
  * output positions are known, and then replayed by fast_emit<>(). Anything else makes fast_record<>()
@@ -113,7 +113,19 @@ PJ_HD uint32_t tape_str(uint32_t slot, uint32_t len, uint32_t pos) { return slot
 struct FastState {
   uint32_t p, limit; /* limit: window offset of the first byte that is not the record's */
   uint32_t lf_ws;
+  uint32_t err, err_pos; /* a validation failure found on this path (kind, window offset); 0 = none */
 };
+
+/* Records a failure that the generic parser would report in exactly the same way. Every function below
+ * returns false both for "refused" (err stays 0: the generic parser decides) and for "failed" (err set);
+ * callers pass false upwards without trying anything else, so the first failure in reading order stands. */
+PJ_HD bool fast_fail(FastState& f, uint32_t kind, uint32_t pos) { f.err = kind; f.err_pos = pos; return false; }
+/* The byte x at f.p cannot start a value of the expected type. When it starts a value of another type
+ * that is PJ_E_TYPE at f.p; null, the end of the record and stray bytes are left to the generic parser. */
+PJ_HD bool fast_wrong_type(FastState& f, uint32_t x) {
+  if (f.p < f.limit && (x == '"' || x == '-' || x - '0' <= 9u || x == '{' || x == '[' || x == 't' || x == 'f')) return fast_fail(f, PJ_E_TYPE, f.p);
+  return false;
+}
 
 PJ_HD void fast_ws_slow(const Win& w, FastState& f) {
   for (;;) {
@@ -128,7 +140,8 @@ PJ_HD uint32_t fast_ws(const Win& w, FastState& f) {
   return x;
 }
 
-/* A plain string at f.p (opening quote): *pos = offset of the first content byte, *len = bytes. */
+/* A plain string at f.p (opening quote): *pos = offset of the first content byte, *len = bytes.
+ * Only for VALUES: it reports the failure a value string has when the record ends inside it. */
 PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len) {
   uint32_t q = f.p + 1;
   for (;;) {
@@ -137,7 +150,12 @@ PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len)
     q += 8;
     if (q > f.limit) return false;
   }
-  if (q >= f.limit || wbyte(w, q) != '"') return false;
+  if (q >= f.limit) return false;
+  if (wbyte(w, q) != '"') {
+    /* a line feed inside a string of an LF-delimited record: the record's bytes end here */
+    if (wbyte(w, q) == '\n' && !f.lf_ws) return fast_fail(f, PJ_E_EOF, q);
+    return false;
+  }
   const uint32_t n = q - (f.p + 1);
   if (n > TAPE_MAX_STR || f.p + 1 > 0xFFFFu) return false;
   *pos = f.p + 1; *len = n;
@@ -197,6 +215,63 @@ PJ_HD bool fast_int(const Win& w, FastState& f, bool is64, int64_t* out) {
   *out = neg ? (int64_t)(0 - mag) : (int64_t)mag;
   f.p = p;
   return p <= f.limit;
+}
+
+/* RFC 3339 date-time in the n bytes at window offset pos (plain ASCII, no escapes), decoded exactly as
+ * parse_datetime() of pj_core.cuh decodes it; false for anything that function would reject. The fixed
+ * part `YYYY-MM-DDThh:mm:ss` is checked as two 8-byte words and one 4-byte word. */
+PJ_HD bool fast_datetime(const Win& w, uint32_t pos, uint32_t n, int64_t* epoch, int32_t* nanos, int32_t* off) {
+  if (n < 20 || n > 35) return false;
+  const uint64_t a = wpeek8(w, pos), b = wpeek8(w, pos + 8);
+  const uint32_t c = wpeek4(w, pos + 16);
+  /* separators: a = YYYY-MM-  b = DDThh:mm  c = :ss? */
+  if ((a & 0xFF0000FF00000000ull) != 0x2D00002D00000000ull) return false;
+  if ((b & 0x0000FF0000FF0000ull) != 0x00003A0000540000ull) return false;
+  if ((c & 0xFFu) != ':') return false;
+  const uint64_t da = (a & ~0xFF0000FF00000000ull) | 0x3000003000000000ull;
+  const uint64_t db = (b & ~0x0000FF0000FF0000ull) | 0x0000300000300000ull;
+  const uint64_t dc = ((uint64_t)(c >> 8) & 0xFFFFull) | 0x3030303030300000ull;
+  if (swar_nondigit(da) | swar_nondigit(db) | swar_nondigit(dc)) return false;
+#define PJ_DG(word, k) ((uint32_t)((word) >> (8 * (k))) & 0xFu)
+  const uint32_t year = PJ_DG(a, 0) * 1000 + PJ_DG(a, 1) * 100 + PJ_DG(a, 2) * 10 + PJ_DG(a, 3);
+  const uint32_t mon = PJ_DG(a, 5) * 10 + PJ_DG(a, 6), day = PJ_DG(b, 0) * 10 + PJ_DG(b, 1);
+  const uint32_t hh = PJ_DG(b, 3) * 10 + PJ_DG(b, 4), mi = PJ_DG(b, 6) * 10 + PJ_DG(b, 7), ss = PJ_DG(c, 1) * 10 + PJ_DG(c, 2);
+#undef PJ_DG
+  if (mon < 1 || mon > 12 || day < 1) return false;
+  uint32_t dim = (mon == 2) ? 28u : ((mon == 4 || mon == 6 || mon == 9 || mon == 11) ? 30u : 31u);
+  if (mon == 2 && (year % 4 == 0 && (year % 100 != 0 || year % 400 == 0))) dim = 29;
+  if (day > dim || hh > 23 || mi > 59 || ss > 59) return false;
+  uint32_t i = 19, ns = 0;
+  uint32_t x = c >> 24;
+  if (x == '.') {
+    uint32_t kd = 0;
+    ++i;
+    for (;;) {
+      x = i < n ? wbyte(w, pos + i) : 0u;
+      if (x - '0' > 9u) break;
+      if (kd >= 9) return false;
+      ns = ns * 10 + (x - '0'); ++kd; ++i;
+    }
+    if (kd == 0) return false;
+    for (; kd < 9; ++kd) ns *= 10;
+  }
+  if (i >= n) return false;
+  int32_t o = 0;
+  if (x == 'Z') { if (i + 1 != n) return false; }
+  else if (x == '+' || x == '-') {
+    if (i + 6 != n) return false;
+    const uint64_t z = wpeek8(w, pos + i + 1); /* hh:mm */
+    if (((z >> 16) & 0xFFu) != ':') return false;
+    const uint64_t dz = ((z & 0xFFFF00FFFFull) | 0x3030300000300000ull);
+    if (swar_nondigit(dz)) return false;
+    const uint32_t oh = ((uint32_t)z & 0xFu) * 10 + ((uint32_t)(z >> 8) & 0xFu), om = ((uint32_t)(z >> 24) & 0xFu) * 10 + ((uint32_t)(z >> 32) & 0xFu);
+    if (oh > 23 || om > 59) return false;
+    o = (int32_t)(oh * 3600 + om * 60);
+    if (x == '-') o = -o;
+  } else return false;
+  *epoch = days_from_civil((int64_t)year, mon, day) * 86400 + (int64_t)hh * 3600 + (int64_t)(mi * 60 + ss) - o;
+  *nanos = (int32_t)ns; *off = o;
+  return true;
 }
 
 /* ---- compile-time view of one property ------------------------------------------------------------ */
@@ -263,6 +338,7 @@ PJ_HD int match_enum(uint32_t len, uint64_t lo, uint64_t hi) {
 /* values of one object; only ever indexed with constants, so it lives in registers */
 struct FVals {
   int64_t v[8];
+  int64_t aux; /* date-time: nanos << 32 | (uint32) offset */
   uint32_t present;
 };
 
@@ -280,34 +356,51 @@ PJ_HD void copy_win(uint8_t* dst, const Win& w, uint32_t pos, uint32_t n) {
   while (n) { *dst++ = (uint8_t)wbyte(w, pos++); n--; }
 }
 
-/* Value of scalar property I of OBJ at f.p (kinds I64, I32, BOOL, STR, ENUM). DATETIME and null are
- * left to the generic parser. */
+/* Value of scalar property I of OBJ at f.p (kinds I64, I32, BOOL, STR, ENUM, DATETIME). null is left to
+ * the generic parser. */
 template <int OBJ, int I>
 PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v) {
   constexpr uint32_t kind = FK<OBJ, I>::kind, slot = FK<OBJ, I>::cnt;
   if (v.present & (1u << I)) return false; /* repeated key */
+  const uint32_t x = wbyte(w, f.p);
   if constexpr (kind == K_I64 || kind == K_I32) {
     int64_t val;
+    if (!(x == '-' || x - '0' <= 9u)) return fast_wrong_type(f, x);
     if (!fast_int(w, f, kind == K_I64, &val)) return false;
     v.v[I] = val;
   } else if constexpr (kind == K_BOOL) {
     const uint64_t k = wpeek8(w, f.p);
     if ((k & 0xFFFFFFFFull) == 0x65757274ull) { v.v[I] = 1; f.p += 4; }
     else if ((k & 0xFFFFFFFFFFull) == 0x65736C6166ull) { v.v[I] = 0; f.p += 5; }
+    else if (x != 't' && x != 'f') return fast_wrong_type(f, x);
     else return false;
   } else if constexpr (kind == K_STR) {
-    if (wbyte(w, f.p) != '"') return false;
+    if (x != '"') return fast_wrong_type(f, x);
     uint32_t pos, len;
     if (!fast_string(w, f, &pos, &len)) return false;
     tape_push(*s.t, tape_str(slot, len, pos));
     s.cnt[slot] += len;
   } else if constexpr (kind == K_ENUM) {
-    if (wbyte(w, f.p) != '"') return false;
+    if (x != '"') return fast_wrong_type(f, x);
+    const uint32_t q = f.p;
     uint32_t len; uint64_t lo, hi;
-    if (!fast_short(w, f, &len, &lo, &hi)) return false;
+    if (!fast_short(w, f, &len, &lo, &hi)) {
+      /* not a short plain string; a long plain one is a well-formed string that is no literal */
+      uint32_t pos;
+      if (fast_string(w, f, &pos, &len)) return fast_fail(f, PJ_E_ENUM, q);
+      return false;
+    }
     const int e = match_enum<FK<OBJ, I>::child>(len, lo, hi);
-    if (e < 0) return false;
+    if (e < 0) return fast_fail(f, PJ_E_ENUM, q);
     v.v[I] = e;
+  } else if constexpr (kind == K_DATETIME) {
+    if (x != '"') return fast_wrong_type(f, x);
+    const uint32_t q = f.p;
+    uint32_t pos, len;
+    if (!fast_string(w, f, &pos, &len)) return false;
+    int64_t ep; int32_t ns, of;
+    if (!fast_datetime(w, pos, len, &ep, &ns, &of)) return fast_fail(f, PJ_E_DATETIME, q);
+    v.v[I] = ep; v.aux = (int64_t)(((uint64_t)(uint32_t)ns << 32) | (uint32_t)of);
   } else return false;
   v.present |= 1u << I;
   return true;
@@ -402,21 +495,21 @@ PJ_HD void tape_put_scalars(Tape& t, uint32_t at, const FVals& v) {
 template <int OBJ, int I>
 PJ_HD bool root_value(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv) {
   constexpr uint32_t kind = FK<OBJ, I>::kind, cnt = FK<OBJ, I>::cnt;
-  if constexpr (kind <= K_ENUM) return fast_scalar<OBJ, I>(w, f, s, v);
-  else if constexpr (kind == K_DATETIME) return false;
+  if constexpr (kind <= K_ENUM || kind == K_DATETIME) return fast_scalar<OBJ, I>(w, f, s, v);
   else {
     if (v.present & (1u << I)) return false;
     if constexpr (kind == K_OBJ) {
-      if (wbyte(w, f.p) != '{' || !fast_flat<FK<OBJ, I>::child>(w, f, s, cv)) return false;
+      if (wbyte(w, f.p) != '{') return fast_wrong_type(f, wbyte(w, f.p));
+      if (!fast_flat<FK<OBJ, I>::child>(w, f, s, cv)) return false;
     } else {
-      if (wbyte(w, f.p) != '[') return false;
+      if (wbyte(w, f.p) != '[') return fast_wrong_type(f, wbyte(w, f.p));
       f.p++;
       uint32_t j = 0;
       if (fast_ws(w, f) == ']') f.p++;
       else {
         for (;;) {
           if constexpr (kind == K_LIST_STR) {
-            if (wbyte(w, f.p) != '"') return false;
+            if (wbyte(w, f.p) != '"') return fast_wrong_type(f, wbyte(w, f.p));
             uint32_t pos, len;
             if (!fast_string(w, f, &pos, &len)) return false;
             tape_push(*s.t, tape_str(cnt + 1, len, pos));
@@ -424,7 +517,7 @@ PJ_HD bool root_value(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv)
           } else {
             /* header word, room for the scalars, then the element's strings as they are met */
             constexpr int E = FK<OBJ, I>::child;
-            if (wbyte(w, f.p) != '{') return false;
+            if (wbyte(w, f.p) != '{') return fast_wrong_type(f, wbyte(w, f.p));
             const uint32_t at = s.t->n;
             for (uint32_t k = 0; k < 1 + scalar_words<E>(); ++k) tape_push(*s.t, 0);
             FVals ev;
@@ -485,14 +578,29 @@ PJ_HD bool fast_root(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv, 
 
 template <int SCHEMA> struct RootOf { static constexpr int obj = SCHEMA == PJ_SCHEMA_PET ? (int)OBJ_PET : (SCHEMA == PJ_SCHEMA_ORDER ? (int)OBJ_ORDER : (int)OBJ_USER); };
 
-/* One record at window offset `start`, ending before window offset `limit`. On success: model in
- * *type_out, root values in v, the embedded object's in cv, counts in cnt[slot] (all NSLOT entries
- * are reset), strings and list elements on the tape. */
+enum { FAST_REFUSED = 0, FAST_ACCEPTED = 1, FAST_FAILED = 2 };
 template <int SCHEMA>
-PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf_ws, uint32_t open_end, uint32_t* type_out,
-                       FVals& v, FVals& cv, uint32_t* cnt, Tape& t) {
+PJ_HD bool fast_record_body(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, uint32_t* cnt, Tape& t);
+
+/* One record at window offset `start`, ending before window offset `limit`.
+ * FAST_ACCEPTED: model in *type_out, root values in v, the embedded object's in cv, counts in cnt[slot]
+ *                (all NSLOT entries are reset), strings and list elements on the tape.
+ * FAST_FAILED:   the record fails validation with *err_kind at window offset *err_pos, exactly as the
+ *                generic parser reports it.
+ * FAST_REFUSED:  the generic parser has to look at the record. */
+template <int SCHEMA>
+PJ_HD uint32_t fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf_ws, uint32_t open_end, uint32_t* type_out,
+                           FVals& v, FVals& cv, uint32_t* cnt, Tape& t, uint32_t* err_kind, uint32_t* err_pos) {
   FastState f;
-  f.p = start; f.limit = limit; f.lf_ws = lf_ws;
+  f.p = start; f.limit = limit; f.lf_ws = lf_ws; f.err = 0; f.err_pos = 0;
+  if (fast_record_body<SCHEMA>(w, f, open_end, type_out, v, cv, cnt, t)) return FAST_ACCEPTED;
+  if (!f.err) return FAST_REFUSED;
+  *err_kind = f.err; *err_pos = f.err_pos;
+  return FAST_FAILED;
+}
+template <int SCHEMA>
+PJ_HD bool fast_record_body(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, uint32_t* cnt, Tape& t) {
+  const uint32_t limit = f.limit, lf_ws = f.lf_ws;
 #pragma unroll
   for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = 0;
   t.n = 0;
@@ -506,7 +614,7 @@ PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf
   if constexpr (SCHEMA != PJ_SCHEMA_MIXED) {
     constexpr int OBJ = RootOf<SCHEMA>::obj;
     if (!fast_root<OBJ>(w, f, s, v, cv, -1)) return false;
-    if ((v.present & CObj<OBJ>::required) != (uint32_t)CObj<OBJ>::required) return false;
+    if ((v.present & CObj<OBJ>::required) != (uint32_t)CObj<OBJ>::required) return fast_fail(f, PJ_E_REQUIRED, f.p - 1);
     type = SCHEMA;
   } else {
     /* only the common `id` may precede the deciding key on this path */
@@ -519,7 +627,10 @@ PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf
       const int kp = match_key<OBJ_PET>(len, lo, hi), ko = match_key<OBJ_ORDER>(len, lo, hi), ku = match_key<OBJ_USER>(len, lo, hi);
       const int owners = (kp >= 0) + (ko >= 0) + (ku >= 0);
       if (owners == 3) {
-        if (have_id || !fast_int(w, f, true, &early_id)) return false;
+        if (have_id) return false;
+        const uint32_t x = wbyte(w, f.p);
+        if (!(x == '-' || x - '0' <= 9u)) return fast_wrong_type(f, x);
+        if (!fast_int(w, f, true, &early_id)) return false;
         have_id = true;
         if (fast_member_end(w, f) != 1) return false;
         continue;
@@ -529,7 +640,7 @@ PJ_HD bool fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_t lf
       if (kp >= 0) {
         type = PJ_TYPE_PET;
         if (!fast_root<OBJ_PET>(w, f, s, v, cv, kp)) return false;
-        if ((v.present & CObj<OBJ_PET>::required) != (uint32_t)CObj<OBJ_PET>::required) return false;
+        if ((v.present & CObj<OBJ_PET>::required) != (uint32_t)CObj<OBJ_PET>::required) return fast_fail(f, PJ_E_REQUIRED, f.p - 1);
       } else if (ko >= 0) {
         type = PJ_TYPE_ORDER;
         if (!fast_root<OBJ_ORDER>(w, f, s, v, cv, ko)) return false;
@@ -567,8 +678,9 @@ PJ_HD void store_vals(const DevCols* c, const FVals& v, uint64_t row, const uint
     else if constexpr (kind == K_ENUM) colp<uint8_t>(c, col)[row] = pr ? (uint8_t)v.v[I] : 255;
     else if constexpr (kind == K_STR) { if constexpr (!ELEM) colp<uint32_t>(c, col)[row] = base[cnt]; }
     else if constexpr (kind == K_DATETIME) {
-      /* never decoded on this path, so always absent here */
-      colp<int64_t>(c, col)[row] = 0; colp<int32_t>(c, col + 1)[row] = 0; colp<int32_t>(c, col + 2)[row] = 0;
+      colp<int64_t>(c, col)[row] = pr ? v.v[I] : 0;
+      colp<int32_t>(c, col + 1)[row] = pr ? (int32_t)((uint64_t)v.aux >> 32) : 0;
+      colp<int32_t>(c, col + 2)[row] = pr ? (int32_t)(uint32_t)v.aux : 0;
     }
     else if constexpr (kind == K_LIST_STR || kind == K_LIST_OBJ) colp<uint32_t>(c, col)[row] = base[cnt];
     store_vals<OBJ, ELEM, I + 1>(c, v, row, base);

@@ -577,15 +577,25 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
 #pragma unroll
   for (uint32_t k = 0; k < NSLOT; ++k) { cnt[k] = 0; base[k] = 0; }
   FVals v, cv;
-  uint32_t type = PJ_TYPE_NONE, err = 0, fast = 0;
+  uint32_t type = PJ_TYPE_NONE, err = 0, fast = 0, verdict = FAST_REFUSED;
   if (active) {
     const bool blank = a.rec_blank && a.rec_blank[i];
     if (fits && !blank) {
       const uint64_t rel = (uint64_t)((int64_t)my_limit - w0);
       const uint32_t lim32 = rel > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)rel;
-      fast = fast_record<SCHEMA>(w, (uint32_t)((int64_t)start - w0), lim32, a.lf_ws, a.open_end, &type, v, cv, cnt, tp) ? 1u : 0u;
+      const uint32_t start32 = (uint32_t)((int64_t)start - w0);
+      uint32_t fpos = 0;
+      verdict = fast_record<SCHEMA>(w, start32, lim32, a.lf_ws, a.open_end, &type, v, cv, cnt, tp, &err, &fpos);
+      fast = verdict == FAST_ACCEPTED;
+      if (verdict == FAST_FAILED) {
+        /* a validation failure found by the word-at-a-time path: no row values, no bytes anywhere */
+        type = PJ_TYPE_NONE;
+#pragma unroll
+        for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = 0;
+        colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = fpos - start32;
+      }
     }
-    if (!fast) {
+    if (verdict == FAST_REFUSED) {
       Rd r;
       r.in = fits ? win - w0 : a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end; r.limit = my_limit;
       PS s;
@@ -599,7 +609,7 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
       for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = (k >= LO && k < HI && !err) ? so.cnt[k] : 0u;
       if (err) type = PJ_TYPE_NONE;
       colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = err ? (uint32_t)(s.err_pos - start) : 0u;
-    } else colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = 0u;
+    } else if (fast) colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = 0u;
     colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i] = (uint8_t)err;
     if (SCHEMA == PJ_SCHEMA_MIXED) colp<uint8_t>(&a.cols, PJ_COL_REC_TYPE)[i] = (uint8_t)type;
   }
