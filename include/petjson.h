@@ -250,7 +250,11 @@ typedef struct pj_options {
   int32_t inclusion;         /* PJ_INCLUDE_* for pj_write                                       */
   void* stream;              /* a cudaStream_t to run on, or NULL for a stream the context owns */
   uint32_t flags;            /* PJ_OPT_* bits                                                   */
-  uint32_t reserved;
+  uint32_t host_piece_bytes; /* pj_parse with host input and host columns (NDJSON): the input is cut after
+                                line feeds into pieces of about this many bytes (at most 16), and the copy of
+                                one piece to the device, the kernels of the previous one and the copy of the
+                                columns of the one before run at the same time. 0 = 64 MiB; 0xFFFFFFFF = never
+                                cut. The result does not depend on it.                            */
 } pj_options;
 
 typedef struct pj_ctx pj_ctx;
@@ -258,7 +262,7 @@ typedef struct pj_ctx pj_ctx;
 /* Kernel accounting of the most recent pj_parse* / pj_write / pj_index_records call on a context. */
 typedef struct pj_call_stats {
   uint32_t kernel_launches; /* kernels of this library launched by the call                    */
-  uint32_t reserved;
+  uint32_t pieces;          /* pj_parse: pieces the input was parsed in (see pj_options.host_piece_bytes) */
   float device_ms;          /* CUDA-event time from first launch to last, on the call's stream  */
   float main_kernel_ms;     /* CUDA-event time of the dominant kernel(s) of the call            */
   float stage_ms[8];        /* CUDA-event time per stage. parse: [0] record index, [1] set-up between

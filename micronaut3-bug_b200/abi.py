@@ -120,11 +120,11 @@ class pj_columns(C.Structure):
 
 class pj_options(C.Structure):
     _fields_ = [("device", C.c_int32), ("inclusion", C.c_int32), ("stream", C.c_void_p),
-                ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+                ("flags", C.c_uint32), ("host_piece_bytes", C.c_uint32)]
 
 
 class pj_call_stats(C.Structure):
-    _fields_ = [("kernel_launches", C.c_uint32), ("reserved", C.c_uint32), ("device_ms", C.c_float),
+    _fields_ = [("kernel_launches", C.c_uint32), ("pieces", C.c_uint32), ("device_ms", C.c_float),
                 ("main_kernel_ms", C.c_float), ("stage_ms", C.c_float * 8), ("stage_launches", C.c_uint32 * 8),
                 ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
                 ("algorithmic_bytes", C.c_uint64), ("fast_records", C.c_uint64), ("phase_cycles", C.c_uint64 * 4),

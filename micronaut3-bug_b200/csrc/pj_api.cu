@@ -87,6 +87,10 @@ struct pj_ctx {
   DevResult* d_res = nullptr;
   DevResult* h_res = nullptr; /* pinned */
   cudaEvent_t ev[10] = {};
+  /* host buffers parsed in pieces: copy streams and one "piece is on the device" event per piece */
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  cudaEvent_t ev_in[16] = {};
+  uint32_t piece_bytes = 0;
   Schema schema;
   pj_call_stats stats = {};
   char err[256] = "";
@@ -137,13 +141,24 @@ struct Stage {
 };
 inline void count_launch(pj_ctx* c, int stage, uint32_t n = 1) { c->stats.kernel_launches += n; c->stats.stage_launches[stage] += n; }
 
+/* adds the stage times of the launches just finished to the call's statistics (a call may run several passes) */
 void collect_times(pj_ctx* c, int stages) {
   for (int i = 0; i < stages && i < 8; ++i) {
     float ms = 0.f;
-    if (cudaEventElapsedTime(&ms, c->ev[i], c->ev[i + 1]) == cudaSuccess) c->stats.stage_ms[i] = ms;
+    if (cudaEventElapsedTime(&ms, c->ev[i], c->ev[i + 1]) == cudaSuccess) c->stats.stage_ms[i] += ms;
   }
   float ms = 0.f;
-  if (cudaEventElapsedTime(&ms, c->ev[0], c->ev[stages]) == cudaSuccess) c->stats.device_ms = ms;
+  if (cudaEventElapsedTime(&ms, c->ev[0], c->ev[stages]) == cudaSuccess) c->stats.device_ms += ms;
+}
+
+enum { MAX_PIECES = 16 };
+static constexpr uint64_t DEFAULT_PIECE_BYTES = 64ull << 20;
+pj_status ensure_pipe_streams(pj_ctx* c) {
+  if (c->s_in) return PJ_OK;
+  PJ_CUDA(c, cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking));
+  PJ_CUDA(c, cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking));
+  for (auto& ev : c->ev_in) PJ_CUDA(c, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  return PJ_OK;
 }
 
 pj_status run_scan_u32(pj_ctx* c, uint32_t* data, uint64_t stride, uint32_t nslots, uint32_t slot_lo, uint64_t n_cap,
@@ -196,15 +211,53 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   for (int i = 0; i < nneed; ++i)
     if (!out->col[need[i]].ptr) return set_err(c, PJ_ERR_ARG, "pj_parse: column %s has no buffer", col_info(need[i])->name);
 
+  /* Pieces. Host buffers of an LF-delimited stream are parsed in pieces cut after line feeds, so that the
+     copy of piece p+1 to the device, the kernels of piece p and the copy of piece p-1's columns back run at
+     the same time on three streams. A piece is a complete input of its own (it starts at a line start and
+     ends with a line feed); what ties the pieces together is where each one starts in the columns: its first
+     row (pointers of the row-indexed columns are advanced) and its first byte / item in every arena and
+     child table (TileArgs.slot_base). */
+  const bool host_in = in_kind == PJ_MEM_HOST, host_out = out->mem_kind == PJ_MEM_HOST;
+  uint64_t cut[MAX_PIECES + 1];
+  int np = 1;
+  cut[0] = 0; cut[1] = len;
+  if (host_in && host_out && !array && !c->staged && slack == 0 && is_first && is_last && c->piece_bytes != 0xFFFFFFFFu) {
+    const uint64_t piece = c->piece_bytes ? c->piece_bytes : DEFAULT_PIECE_BYTES;
+    uint64_t want = len / piece;
+    if (want > MAX_PIECES) want = MAX_PIECES;
+    np = 0;
+    for (uint64_t k = 1; k < want; ++k) {
+      const uint64_t target = len / want * k;
+      if (target <= cut[np]) continue;
+      const void* q = memrchr(in + cut[np], '\n', target - cut[np]);
+      if (!q) continue;
+      cut[np + 1] = (uint64_t)((const uint8_t*)q - in) + 1;
+      ++np;
+    }
+    cut[++np] = len;
+  }
+  const bool pipe = np > 1;
+  if (pipe) { pj_status st = ensure_pipe_streams(c); if (st) return st; }
+  cudaStream_t s_in = pipe ? c->s_in : c->stream, s_out = pipe ? c->s_out : c->stream;
+  /* whatever goes wrong from here on, no copy may still be running when the call returns */
+  struct Drain {
+    pj_ctx* c; bool pipe;
+    ~Drain() { if (pipe) { cudaStreamSynchronize(c->s_in); cudaStreamSynchronize(c->stream); cudaStreamSynchronize(c->s_out); } }
+  } drain{c, pipe};
+
   /* stage host memory */
-  const bool host_out = out->mem_kind == PJ_MEM_HOST;
   const uint8_t* d_in = in;
-  if (in_kind == PJ_MEM_HOST && limit) {
+  if (host_in && limit) {
     pj_status st = ensure(c, &c->in_stage, limit + 64);
     if (st) return st;
-    PJ_CUDA(c, cudaMemcpyAsync(c->in_stage.p, in, limit, cudaMemcpyHostToDevice, c->stream));
-    c->stats.h2d_bytes += limit;
     d_in = (const uint8_t*)c->in_stage.p;
+    if (pipe) { PJ_CUDA(c, cudaEventRecord(c->ev_in[0], c->stream)); PJ_CUDA(c, cudaStreamWaitEvent(s_in, c->ev_in[0], 0)); }
+    for (int p = 0; p < np; ++p) {
+      const uint64_t nb = cut[p + 1] - cut[p] + (p == np - 1 ? slack : 0);
+      if (nb) PJ_CUDA(c, cudaMemcpyAsync((uint8_t*)c->in_stage.p + cut[p], in + cut[p], nb, cudaMemcpyHostToDevice, s_in));
+      if (pipe) PJ_CUDA(c, cudaEventRecord(c->ev_in[p], s_in));
+      c->stats.h2d_bytes += nb;
+    }
   }
   DevCols dcols;
   memset(&dcols, 0, sizeof dcols);
@@ -218,26 +271,24 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   } else {
     for (int i = 0; i < nneed; ++i) dcols.ptr[need[i]] = out->col[need[i]].ptr;
   }
-  uint64_t cap_records = ~0ull;
+  uint64_t cap_all = ~0ull;
   for (int i = 0; i < nneed; ++i) fa.cap_elems[need[i]] = out->col[need[i]].bytes / col_info(need[i])->elem;
-  for (int i = 0; i < nrc; ++i) if (fa.cap_elems[rcols[i]] < cap_records) cap_records = fa.cap_elems[rcols[i]];
-  if (cap_records > (1ull << 32)) cap_records = 1ull << 32;
+  for (int i = 0; i < nrc; ++i) if (fa.cap_elems[rcols[i]] < cap_all) cap_all = fa.cap_elems[rcols[i]];
+  if (cap_all > (1ull << 32)) cap_all = 1ull << 32;
   /* no more records than candidate line starts (NDJSON: a record needs a byte and an LF) or separators (array) */
-  if (!array && cap_records > limit / 2 + 2) cap_records = limit / 2 + 2;
-  if (array && cap_records > limit + 2) cap_records = limit + 2;
-  fa.cap_records = cap_records;
+  if (!array && cap_all > limit / 2 + 2) cap_all = limit / 2 + 2;
+  if (array && cap_all > limit + 2) cap_all = limit + 2;
   fa.res = c->d_res;
-  fa.cols = dcols;
 
-  /* scratch */
+  /* scratch, sized for the whole input (no piece needs more) */
   uint32_t slot_lo, slot_hi;
   slot_range(schema, &slot_lo, &slot_hi);
   const uint32_t nslots = slot_hi - slot_lo;
-  const uint64_t ntiles = (len + 15 + INDEX_TILE) / INDEX_TILE; /* covers the worst misalignment of `in` */
-  const uint64_t stride = align_up(cap_records + 1, 4);
-  const uint32_t nchunks = (uint32_t)((cap_records + 1 + SCAN_CHUNK - 1) / SCAN_CHUNK);
+  const uint64_t max_index_tiles = (len + 15 + INDEX_TILE) / INDEX_TILE; /* covers the worst misalignment of `in` */
+  const uint64_t stride = align_up(cap_all + 1, 4);
+  const uint32_t nchunks = (uint32_t)((cap_all + 1 + SCAN_CHUNK - 1) / SCAN_CHUNK);
   size_t off_tile = 0;
-  size_t off_cnt = align_up(off_tile + ((ntiles > (len >> 14) + 2 ? ntiles : (len >> 14) + 2) + 1) * 4, 256);
+  size_t off_cnt = align_up(off_tile + ((max_index_tiles > (len >> 14) + 2 ? max_index_tiles : (len >> 14) + 2) + 1) * 4, 256);
   size_t off_part = align_up(off_cnt + (c->staged ? (size_t)nslots * stride * 4 : 0), 256);
   size_t off_arr = align_up(off_part + (c->staged ? (size_t)nslots * nchunks * 4 : 0), 256);
   const uint64_t nwords = (len + 63) >> 6;
@@ -247,178 +298,224 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
     off_tin = align_up(off_fn + atiles * sizeof(ArrFn), 256);
     off_sep = align_up(off_tin + atiles * sizeof(ArrState), 256);
     off_rend = align_up(off_sep + (nwords + 1) * 8, 256);
-    off_rblank = align_up(off_rend + cap_records * 8, 256);
-    total_scratch = off_rblank + cap_records + 256;
+    off_rblank = align_up(off_rend + cap_all * 8, 256);
+    total_scratch = off_rblank + cap_all + 256;
   }
   { pj_status st = ensure(c, &c->scratch, total_scratch); if (st) return st; }
   uint32_t* d_tile = (uint32_t*)((uint8_t*)c->scratch.p + off_tile);
   uint32_t* d_cnt = (uint32_t*)((uint8_t*)c->scratch.p + off_cnt);
   uint32_t* d_part = (uint32_t*)((uint8_t*)c->scratch.p + off_part);
 
-  PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream));
-  Stage stage(c);
-
-  /* stage 0: record index */
-  uint64_t* d_rec_end = nullptr;
-  uint8_t* d_rec_blank = nullptr;
-  if (!array) {
-    IndexArgs ia;
-    ia.in = d_in; ia.len = len; ia.limit = limit; ia.is_first = is_first; ia.is_last = is_last;
-    ia.tile = d_tile; ia.rec_start = (uint64_t*)dcols.ptr[PJ_COL_REC_START]; ia.cap = cap_records; ia.goff = goff;
-    k_nd_index<false><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
-    k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles, &c->d_res->n_records);
-    k_nd_index<true><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
-    count_launch(c, 0, 3);
-  } else {
-    d_rec_end = (uint64_t*)((uint8_t*)c->scratch.p + off_rend);
-    d_rec_blank = (uint8_t*)c->scratch.p + off_rblank;
-    ArrArgs aa;
-    aa.in = d_in; aa.len = len; aa.nwords = nwords;
-    aa.tile_fn = (ArrFn*)((uint8_t*)c->scratch.p + off_fn); aa.tile_in = (ArrState*)((uint8_t*)c->scratch.p + off_tin);
-    aa.sep = (uint64_t*)((uint8_t*)c->scratch.p + off_sep); aa.tile_cnt = d_tile;
-    aa.rec_start = (uint64_t*)dcols.ptr[PJ_COL_REC_START]; aa.rec_end = d_rec_end; aa.rec_blank = d_rec_blank;
-    aa.cap = cap_records; aa.goff = goff; aa.ntiles = (uint32_t)atiles; aa.res = c->d_res;
-    /* the two running minima start at "none" */
-    PJ_CUDA(c, cudaMemsetAsync(&c->d_res->doc_err_off, 0xFF, sizeof(unsigned long long), c->stream));
-    PJ_CUDA(c, cudaMemsetAsync(&c->d_res->first_opener, 0xFF, sizeof(unsigned long long), c->stream));
-    k_arr_summary<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
-    k_arr_scan_tiles<<<1, 32, 0, c->stream>>>(aa);
-    k_arr_mark<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
-    k_arr_records<false><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
-    k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, atiles, &c->d_res->n_records);
-    k_arr_records<true><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
-    count_launch(c, 0, 6);
-  }
-  PJ_CUDA(c, cudaGetLastError());
-  stage.next();
-
+  /* what the pieces parsed so far have produced */
+  uint64_t rows_done = 0, n_errors = 0, n_fast = 0;
+  uint64_t total[NSLOT];
+  for (uint32_t k = 0; k < NSLOT; ++k) total[k] = 0;
+  DevResult last{};
   int n_stages = 5;
-  if (c->staged) {
-    /* stage 1: size pass */
-    ParseArgs pa;
-    pa.in = d_in; pa.limit = limit; pa.goff = goff; pa.cap_records = cap_records;
-    pa.lf_ws = array ? 1u : 0u; pa.open_end = is_last ? 0u : 1u; pa.schema = schema; pa.slot_lo = slot_lo; pa.slot_hi = slot_hi;
-    pa.cnt = d_cnt - (size_t)slot_lo * stride; /* indexed by absolute slot */
-    pa.stride = stride; pa.rec_end = d_rec_end; pa.rec_blank = d_rec_blank; pa.res = c->d_res; pa.cols = dcols;
-    const int pgrid = persistent_grid(c, cap_records, PARSE_THREADS);
-    k_parse_size<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
-    count_launch(c, 1);
-    PJ_CUDA(c, cudaGetLastError());
-    stage.next();
+  /* A call that does not fit the caller's buffers still reports what it needs: once the records do not fit
+     (count_only) the remaining pieces are only indexed; once an arena or child table does not fit (over) they are
+     still sized, but nothing more is emitted or copied back. */
+  bool count_only = false, over = false;
 
-    /* stage 2: where every record starts in every arena */
-    { pj_status st = run_scan_u32(c, d_cnt, stride, nslots, slot_lo, cap_records, d_part, nchunks, 2); if (st) return st; }
-    k_check<<<1, 32, 0, c->stream>>>(fa);
-    count_launch(c, 2);
-    stage.next();
-
-    /* stage 3: emit pass */
-    k_parse_emit<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
-    count_launch(c, 3);
-    PJ_CUDA(c, cudaGetLastError());
-    stage.next();
-
-    /* stage 4: closing offsets */
-    k_finalize<<<1, 64, 0, c->stream>>>(fa);
-    count_launch(c, 4);
-    stage.next();
-  } else {
-    /* the tile kernel needs the record count to size its grid */
-    PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
-    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
-    const uint64_t N0 = c->h_res->n_records;
-    if (N0 > cap_records) {
-      out->schema = schema; out->n_records = N0; out->n_errors = 0;
-      for (int i = 0; i < nrc; ++i) out->col[rcols[i]].count = N0;
-      return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records, per-record buffers hold %llu", (unsigned long long)N0, (unsigned long long)cap_records);
-    }
-    TileArgs ta;
-    memset(&ta, 0, sizeof ta);
-    ta.in = d_in; ta.limit = limit; ta.goff = goff; ta.n_records = N0;
-    ta.lf_ws = array ? 1u : 0u; ta.open_end = is_last ? 0u : 1u; ta.schema = schema; ta.slot_lo = slot_lo; ta.slot_hi = slot_hi;
-    ta.win_bytes = TILE_WIN_BYTES; ta.tape_cap = TILE_TAPE_CAP;
-    /* as many records per tile as fit the staging window on average */
-    const uint64_t avg = N0 ? limit / N0 + 1 : 1;
-    uint32_t tile_recs = TILE_THREADS;
-    while (tile_recs > 4 && (uint64_t)tile_recs * avg + 3584 > TILE_WIN_BYTES) tile_recs >>= 1;
-    ta.tile_recs = tile_recs;
-    const uint64_t ntiles = N0 ? (N0 + tile_recs - 1) / tile_recs : 1;
-    ta.ntiles = (uint32_t)ntiles;
-    c->stats.tile_records = tile_recs; c->stats.tiles = (uint32_t)ntiles;
-    ta.rec_end = d_rec_end; ta.rec_blank = d_rec_blank;
-    const uint64_t nstates = ntiles; /* one look-back state per block */
-    { pj_status st = ensure(c, &c->tiles, nstates * sizeof(TileState) + 256); if (st) return st; }
-    ta.ticket = (uint32_t*)c->tiles.p;
-    ta.tiles = (TileState*)((uint8_t*)c->tiles.p + 128);
-    ta.res = c->d_res;
-    for (uint32_t k = 0; k < NSLOT; ++k) ta.slot_cap[k] = ~0ull;
+  for (int p = 0; p < np; ++p) {
+    const uint64_t poff = cut[p], plen = cut[p + 1] - cut[p], plimit = plen + (p == np - 1 ? slack : 0);
+    const uint8_t* pin = d_in ? d_in + poff : d_in;
+    const uint64_t pgoff = goff + poff;
+    const uint64_t cap_records = count_only ? 0 : cap_all - rows_done;
+    /* this piece's view of the columns: row-indexed ones start at its first row */
+    DevCols pcols = dcols;
+    for (int i = 0; i < nrc; ++i) pcols.ptr[rcols[i]] = (uint8_t*)dcols.ptr[rcols[i]] + rows_done * col_info(rcols[i])->elem;
     for (uint32_t k = 0; k < fa.plan.n; ++k) {
       const FinalizeItem& it = fa.plan.item[k];
-      if (it.rows_slot == 0xFF) continue;
-      uint64_t room = fa.cap_elems[it.col];
-      if (it.sentinel_slot != 0xFF) room = room ? room - 1 : 0;
-      if (room < ta.slot_cap[it.rows_slot]) ta.slot_cap[it.rows_slot] = room;
+      if (it.rows_slot == 0xFF) pcols.ptr[it.col] = (uint8_t*)dcols.ptr[it.col] + rows_done * col_info(it.col)->elem;
     }
-    ta.plan = fa.plan;
-    ta.cols = dcols;
-    PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, nstates * sizeof(TileState) + 128, c->stream));
-    const uint32_t one = 1;
-    PJ_CUDA(c, cudaMemcpyAsync(&c->d_res->ok, &one, sizeof one, cudaMemcpyHostToDevice, c->stream));
-    stage.next(); /* stage 1: set-up */
-    switch (schema) {
-      case PJ_SCHEMA_PET: k_parse_tile<PJ_SCHEMA_PET><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
-      case PJ_SCHEMA_ORDER: k_parse_tile<PJ_SCHEMA_ORDER><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
-      case PJ_SCHEMA_USER: k_parse_tile<PJ_SCHEMA_USER><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
-      default: k_parse_tile<PJ_SCHEMA_MIXED><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+    fa.cap_records = cap_records;
+    fa.cols = pcols;
+    if (pipe) PJ_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_in[p], 0));
+
+    PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream));
+    Stage stage(c);
+
+    /* stage 0: record index */
+    const uint64_t ntiles_index = (plen + 15 + INDEX_TILE) / INDEX_TILE;
+    uint64_t* d_rec_end = nullptr;
+    uint8_t* d_rec_blank = nullptr;
+    if (!array) {
+      IndexArgs ia;
+      ia.in = pin; ia.len = plen; ia.limit = plimit; ia.is_first = is_first; ia.is_last = is_last;
+      ia.tile = d_tile; ia.rec_start = (uint64_t*)pcols.ptr[PJ_COL_REC_START]; ia.cap = cap_records; ia.goff = pgoff;
+      k_nd_index<false><<<(unsigned)ntiles_index, INDEX_THREADS, 0, c->stream>>>(ia);
+      k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles_index, &c->d_res->n_records);
+      k_nd_index<true><<<(unsigned)ntiles_index, INDEX_THREADS, 0, c->stream>>>(ia);
+      count_launch(c, 0, 3);
+    } else {
+      d_rec_end = (uint64_t*)((uint8_t*)c->scratch.p + off_rend);
+      d_rec_blank = (uint8_t*)c->scratch.p + off_rblank;
+      ArrArgs aa;
+      aa.in = pin; aa.len = plen; aa.nwords = nwords;
+      aa.tile_fn = (ArrFn*)((uint8_t*)c->scratch.p + off_fn); aa.tile_in = (ArrState*)((uint8_t*)c->scratch.p + off_tin);
+      aa.sep = (uint64_t*)((uint8_t*)c->scratch.p + off_sep); aa.tile_cnt = d_tile;
+      aa.rec_start = (uint64_t*)pcols.ptr[PJ_COL_REC_START]; aa.rec_end = d_rec_end; aa.rec_blank = d_rec_blank;
+      aa.cap = cap_records; aa.goff = pgoff; aa.ntiles = (uint32_t)atiles; aa.res = c->d_res;
+      /* the two running minima start at "none" */
+      PJ_CUDA(c, cudaMemsetAsync(&c->d_res->doc_err_off, 0xFF, sizeof(unsigned long long), c->stream));
+      PJ_CUDA(c, cudaMemsetAsync(&c->d_res->first_opener, 0xFF, sizeof(unsigned long long), c->stream));
+      k_arr_summary<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+      k_arr_scan_tiles<<<1, 32, 0, c->stream>>>(aa);
+      k_arr_mark<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+      k_arr_records<false><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+      k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, atiles, &c->d_res->n_records);
+      k_arr_records<true><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+      count_launch(c, 0, 6);
     }
-    count_launch(c, 2);
     PJ_CUDA(c, cudaGetLastError());
-    stage.next(); /* stage 2: the tile kernel */
-    n_stages = 3;
+    stage.next();
+
+    if (c->staged) {
+      /* stage 1: size pass */
+      ParseArgs pa;
+      pa.in = pin; pa.limit = plimit; pa.goff = pgoff; pa.cap_records = cap_records;
+      pa.lf_ws = array ? 1u : 0u; pa.open_end = is_last ? 0u : 1u; pa.schema = schema; pa.slot_lo = slot_lo; pa.slot_hi = slot_hi;
+      pa.cnt = d_cnt - (size_t)slot_lo * stride; /* indexed by absolute slot */
+      pa.stride = stride; pa.rec_end = d_rec_end; pa.rec_blank = d_rec_blank; pa.res = c->d_res; pa.cols = pcols;
+      const int pgrid = persistent_grid(c, cap_records, PARSE_THREADS);
+      k_parse_size<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
+      count_launch(c, 1);
+      PJ_CUDA(c, cudaGetLastError());
+      stage.next();
+
+      /* stage 2: where every record starts in every arena */
+      { pj_status st = run_scan_u32(c, d_cnt, stride, nslots, slot_lo, cap_records, d_part, nchunks, 2); if (st) return st; }
+      k_check<<<1, 32, 0, c->stream>>>(fa);
+      count_launch(c, 2);
+      stage.next();
+
+      /* stage 3: emit pass */
+      k_parse_emit<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
+      count_launch(c, 3);
+      PJ_CUDA(c, cudaGetLastError());
+      stage.next();
+
+      /* stage 4: closing offsets */
+      k_finalize<<<1, 64, 0, c->stream>>>(fa);
+      count_launch(c, 4);
+      stage.next();
+    } else {
+      /* the tile kernel needs the record count to size its grid */
+      PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+      PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+      const uint64_t N0 = c->h_res->n_records;
+      if (count_only || N0 > cap_records) { count_only = true; rows_done += N0; continue; }
+      TileArgs ta;
+      memset(&ta, 0, sizeof ta);
+      ta.in = pin; ta.limit = plimit; ta.goff = pgoff; ta.n_records = N0;
+      ta.lf_ws = array ? 1u : 0u; ta.open_end = is_last ? 0u : 1u; ta.schema = schema; ta.slot_lo = slot_lo; ta.slot_hi = slot_hi;
+      ta.win_bytes = TILE_WIN_BYTES; ta.tape_cap = TILE_TAPE_CAP;
+      /* as many records per tile as fit the staging window on average */
+      const uint64_t avg = N0 ? plimit / N0 + 1 : 1;
+      uint32_t tile_recs = TILE_THREADS;
+      while (tile_recs > 4 && (uint64_t)tile_recs * avg + 3584 > TILE_WIN_BYTES) tile_recs >>= 1;
+      ta.tile_recs = tile_recs;
+      const uint64_t ntiles = N0 ? (N0 + tile_recs - 1) / tile_recs : 1;
+      ta.ntiles = (uint32_t)ntiles;
+      c->stats.tile_records = tile_recs; c->stats.tiles += (uint32_t)ntiles;
+      ta.rec_end = d_rec_end; ta.rec_blank = d_rec_blank;
+      const uint64_t nstates = ntiles; /* one look-back state per block */
+      { pj_status st = ensure(c, &c->tiles, nstates * sizeof(TileState) + 256); if (st) return st; }
+      ta.ticket = (uint32_t*)c->tiles.p;
+      ta.tiles = (TileState*)((uint8_t*)c->tiles.p + 128);
+      ta.res = c->d_res;
+      for (uint32_t k = 0; k < NSLOT; ++k) { ta.slot_cap[k] = ~0ull; ta.slot_base[k] = (uint32_t)total[k]; }
+      for (uint32_t k = 0; k < fa.plan.n; ++k) {
+        const FinalizeItem& it = fa.plan.item[k];
+        if (it.rows_slot == 0xFF) continue;
+        uint64_t room = fa.cap_elems[it.col];
+        if (it.sentinel_slot != 0xFF) room = room ? room - 1 : 0;
+        if (room < ta.slot_cap[it.rows_slot]) ta.slot_cap[it.rows_slot] = room;
+      }
+      ta.plan = fa.plan;
+      ta.cols = pcols;
+      PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, nstates * sizeof(TileState) + 128, c->stream));
+      const uint32_t one = 1;
+      PJ_CUDA(c, cudaMemcpyAsync(&c->d_res->ok, &one, sizeof one, cudaMemcpyHostToDevice, c->stream));
+      stage.next(); /* stage 1: set-up */
+      switch (schema) {
+        case PJ_SCHEMA_PET: k_parse_tile<PJ_SCHEMA_PET><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+        case PJ_SCHEMA_ORDER: k_parse_tile<PJ_SCHEMA_ORDER><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+        case PJ_SCHEMA_USER: k_parse_tile<PJ_SCHEMA_USER><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+        default: k_parse_tile<PJ_SCHEMA_MIXED><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+      }
+      count_launch(c, 2);
+      PJ_CUDA(c, cudaGetLastError());
+      stage.next(); /* stage 2: the tile kernel */
+      n_stages = 3;
+    }
+
+    PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+    PJ_CUDA(c, cudaGetLastError());
+    collect_times(c, n_stages);
+
+    const DevResult& r = *c->h_res;
+    last = r;
+    n_fast += r.n_fast;
+    for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] += r.phase_cycles[k];
+    c->stats.lookback_polls += r.lookback_polls; c->stats.lookback_rounds += r.lookback_rounds;
+    if (r.timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_parse: a bounded device-side wait ran out");
+    const uint64_t rows_new = rows_done + r.n_records;
+    n_errors += r.n_errors;
+    if (!r.ok) over = true;
+    /* this piece's part of every column goes back while the next piece is parsed */
+    if (host_out && !over) {
+      auto copy_back = [&](int col, uint64_t from, uint64_t to) -> cudaError_t {
+        const size_t e = col_info(col)->elem;
+        if (to <= from) return cudaSuccess;
+        c->stats.d2h_bytes += (to - from) * e;
+        return cudaMemcpyAsync((uint8_t*)out->col[col].ptr + from * e, (uint8_t*)dcols.ptr[col] + from * e, (to - from) * e, cudaMemcpyDeviceToHost, s_out);
+      };
+      for (int i = 0; i < nrc; ++i) PJ_CUDA(c, copy_back(rcols[i], rows_done, rows_new));
+      for (uint32_t k = 0; k < fa.plan.n; ++k) {
+        const FinalizeItem& it = fa.plan.item[k];
+        const uint64_t from = it.rows_slot == 0xFF ? rows_done : total[it.rows_slot];
+        const uint64_t to = (it.rows_slot == 0xFF ? rows_new : r.total[it.rows_slot]) + (it.sentinel_slot != 0xFF ? 1 : 0);
+        PJ_CUDA(c, copy_back(it.col, from, to));
+      }
+    }
+    rows_done = rows_new;
+    for (uint32_t k = 0; k < NSLOT; ++k) total[k] = r.total[k];
   }
-
-  PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
-  PJ_CUDA(c, cudaStreamSynchronize(c->stream));
-  PJ_CUDA(c, cudaGetLastError());
-  collect_times(c, n_stages);
   c->stats.main_kernel_ms = c->staged ? c->stats.stage_ms[1] + c->stats.stage_ms[3] : c->stats.stage_ms[2];
+  c->stats.fast_records = n_fast;
+  c->stats.pieces = (uint32_t)np;
 
-  const DevResult& r = *c->h_res;
-  c->stats.fast_records = r.n_fast;
-  for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] = r.phase_cycles[k];
-  c->stats.lookback_polls = r.lookback_polls; c->stats.lookback_rounds = r.lookback_rounds;
-  if (r.timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_parse: a bounded device-side wait ran out");
-  const uint64_t N = r.n_records;
+  const uint64_t N = rows_done;
+  if (count_only) {
+    out->schema = schema; out->n_records = N; out->n_errors = 0;
+    for (int i = 0; i < nrc; ++i) out->col[rcols[i]].count = N;
+    return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records, per-record buffers hold %llu", (unsigned long long)N, (unsigned long long)cap_all);
+  }
   out->schema = schema;
   out->n_records = N;
-  out->n_errors = r.n_errors;
+  out->n_errors = n_errors;
   out->doc_err_kind = 0; out->doc_err_off = 0;
   if (array) {
-    if (r.doc_err_off != ~0ull) { out->doc_err_kind = PJ_E_SYNTAX; out->doc_err_off = r.doc_err_off; }
-    else if (r.first_opener == ~0ull || r.arr_final_s || r.arr_final_d != 0) { out->doc_err_kind = PJ_E_EOF; out->doc_err_off = len; }
+    if (last.doc_err_off != ~0ull) { out->doc_err_kind = PJ_E_SYNTAX; out->doc_err_off = last.doc_err_off; }
+    else if (last.first_opener == ~0ull || last.arr_final_s || last.arr_final_d != 0) { out->doc_err_kind = PJ_E_EOF; out->doc_err_off = len; }
   }
   for (int t = 0; t < 4; ++t) out->n_rows[t] = 0;
-  if (schema == PJ_SCHEMA_MIXED) { out->n_rows[1] = r.total[SLOT_ROWS_PET]; out->n_rows[2] = r.total[SLOT_ROWS_ORD]; out->n_rows[3] = r.total[SLOT_ROWS_USR]; }
+  if (schema == PJ_SCHEMA_MIXED) { out->n_rows[1] = total[SLOT_ROWS_PET]; out->n_rows[2] = total[SLOT_ROWS_ORD]; out->n_rows[3] = total[SLOT_ROWS_USR]; }
   else out->n_rows[schema] = N;
   for (int i = 0; i < nrc; ++i) out->col[rcols[i]].count = N;
   for (uint32_t k = 0; k < fa.plan.n; ++k) {
     const FinalizeItem& it = fa.plan.item[k];
-    uint64_t rows = it.rows_slot == 0xFF ? N : r.total[it.rows_slot];
+    uint64_t rows = it.rows_slot == 0xFF ? N : total[it.rows_slot];
     out->col[it.col].count = rows + (it.sentinel_slot != 0xFF ? 1 : 0);
   }
   uint64_t alg = len;
   for (int i = 0; i < nneed; ++i) alg += out->col[need[i]].count * col_info(need[i])->elem;
   c->stats.algorithmic_bytes = alg;
-  if (!r.ok) return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records need larger output buffers", (unsigned long long)N);
-  if (host_out) {
-    for (int i = 0; i < nneed; ++i) {
-      size_t nb = (size_t)out->col[need[i]].count * col_info(need[i])->elem;
-      if (!nb) continue;
-      PJ_CUDA(c, cudaMemcpyAsync(out->col[need[i]].ptr, dcols.ptr[need[i]], nb, cudaMemcpyDeviceToHost, c->stream));
-      c->stats.d2h_bytes += nb;
-    }
-    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
-  }
+  if (over) return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records need larger output buffers", (unsigned long long)N);
+  if (host_out) PJ_CUDA(c, cudaStreamSynchronize(s_out));
   return PJ_OK;
 }
 
@@ -470,6 +567,7 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   c->device = dev;
   c->inclusion = opt ? opt->inclusion : PJ_INCLUDE_NON_EMPTY;
   c->staged = opt && (opt->flags & PJ_OPT_STAGED_PIPELINE);
+  c->piece_bytes = opt ? opt->host_piece_bytes : 0;
   DeviceGuard guard(dev);
   auto fail_create = [&](cudaError_t err, const char* what) {
     set_err(nullptr, PJ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
@@ -507,6 +605,9 @@ void pj_destroy(pj_ctx* c) {
   if (c->d_res) cudaFree(c->d_res);
   if (c->h_res) cudaFreeHost(c->h_res);
   for (auto& ev : c->ev) if (ev) cudaEventDestroy(ev);
+  for (auto& ev : c->ev_in) if (ev) cudaEventDestroy(ev);
+  if (c->s_in) cudaStreamDestroy(c->s_in);
+  if (c->s_out) cudaStreamDestroy(c->s_out);
   if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
   delete c;
 }

@@ -432,6 +432,8 @@ struct TileArgs {
   uint32_t* ticket;
   DevResult* res;
   uint64_t slot_cap[NSLOT]; /* largest total per slot the caller's buffers can take */
+  uint32_t slot_base[NSLOT]; /* totals of the pieces of the same call parsed before this launch: where this
+                                launch starts in every arena / child table (offsets stored are absolute) */
   FinalizePlan plan;
   DevCols cols;
 };
@@ -653,15 +655,16 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
 #pragma unroll
     for (uint32_t k = LO; k < HI; ++k) if (lane == k) excl = excl_all[k];
     if (tile != 0 && ok && lane < NSLOT) st_relaxed_u64(&me->inc[lane], TS_VALID | (unsigned long long)(excl + mine));
-    if (lane < NSLOT) sh_base[lane] = excl;
+    const uint64_t before = lane < NSLOT ? (uint64_t)a.slot_base[lane] + excl : 0; /* the tile's start, over the whole call */
+    if (lane < NSLOT) sh_base[lane] = (uint32_t)before;
     /* does the whole tile fit the caller's buffers? (totals only grow, so the last tile's verdict is the call's) */
-    const bool over = lane < NSLOT && (uint64_t)excl + mine > a.slot_cap[lane];
+    const bool over = lane < NSLOT && before + mine > a.slot_cap[lane];
     const uint32_t any_over = __ballot_sync(0xFFFFFFFFu, over);
     if (lane == 0) {
       sh_ok = ok && !any_over;
       if (any_over) a.res->ok = 0;
     }
-    if (tile == a.ntiles - 1 && lane < NSLOT) a.res->total[lane] = (unsigned long long)excl + mine;
+    if (tile == a.ntiles - 1 && lane < NSLOT) a.res->total[lane] = before + mine;
   }
   __syncthreads();
   const long long c3 = clock64();

@@ -251,6 +251,46 @@ def test_staged_pipeline_gives_the_same_columns(native, oracle, schema):
         assert c.stats().kernel_launches >= 7
 
 
+@pytest.mark.parametrize("schema", [1, 2, 3, 4])
+@pytest.mark.parametrize("piece", [1, 700, 4096, 100000, 0xFFFFFFFF])
+def test_host_buffers_parsed_in_pieces(native, oracle, schema, piece):
+    """Host input + host columns are cut after line feeds into up to 16 pieces that overlap copies and kernels;
+    the columns must not depend on where the cuts fall (blank lines, failed records and empty pieces included)."""
+    flags = abi.PJ_GEN_ESCAPES | abi.PJ_GEN_MALFORMED | abi.PJ_GEN_SPARSE | abi.PJ_GEN_WHITESPACE
+    text = bytes(pj.gen_text(schema, 77, 0, 1500, flags))
+    lines = text.split(b"\n")
+    body = as_u8(b"\n".join(lines[:200]) + b"\n" * 400 + b" \n\t\n" + b"\n".join(lines[200:-1]) + b"\n" + b'{"id":1,"name":"no line feed at the end","photoUrls":[]}')
+    want = oracle.parse(schema, body)
+    with native.Context(device=0, host_piece_bytes=piece) as c:
+        assert same_result(want, gpu_parse_host(c, schema, body)) == ""
+        st = c.stats()
+        assert 1 <= st.pieces <= 16
+        assert (st.pieces > 1) == (piece != 0xFFFFFFFF)
+        # a second call on the same context reuses the streams and staging buffers
+        assert same_result(want, gpu_parse_host(c, schema, body)) == ""
+
+
+def test_pieces_keep_capacity_errors(native, oracle):
+    """A call cut into pieces that does not fit the caller's buffers fails as a whole and still reports what it needs."""
+    text = as_u8(pj.gen_text(1, 5, 0, 2000, 0))
+    want = oracle.parse(1, text)
+    caps = abi.default_caps(1, nrec_bound(text), text.size)
+    with native.Context(device=0, host_piece_bytes=20000) as c:
+        small = dict(caps)
+        small[abi.COL_BY_NAME["pet_photo_data"].id] = 1000
+        out = abi.HostColumns(1, small)
+        assert c.parse(1, text, out, allow_capacity=True) == abi.PJ_ERR_CAPACITY
+        assert c.stats().pieces > 1
+        for col in abi.schema_columns(1):
+            assert out.count(col.id) == want.count(col.id), col.name
+        few = dict(caps)
+        few[abi.COL_BY_NAME["err_kind"].id] = 700
+        out = abi.HostColumns(1, few)
+        assert c.parse(1, text, out, allow_capacity=True) == abi.PJ_ERR_CAPACITY
+        assert out.n_records == 2000
+        assert same_result(want, gpu_parse_host(c, 1, text)) == ""
+
+
 def test_long_records_fall_back_to_unstaged_reads(ctx, oracle):
     """Records longer than the staging window are parsed straight from global memory."""
     big = b'{"name":"n","photoUrls":[' + b",".join(b'"' + b"u" * 50 + b'"' for _ in range(3000)) + b'],"tags":[' + \
