@@ -268,7 +268,8 @@ typedef struct pj_call_stats {
   float stage_ms[8];        /* CUDA-event time per stage. parse: [0] record index, [1] set-up between
                                the kernels (record count read-back, state reset), [2] the tile kernel
                                (with PJ_OPT_STAGED_PIPELINE: [1] size pass, [2] counter scans, [3] emit
-                               pass, [4] closing offsets); write: [0] size pass, [1] scan, [2] emit pass */
+                               pass, [4] closing offsets); write: [0] state reset, [1] the closing kernel, [2] the
+                               tile kernel (with PJ_OPT_STAGED_PIPELINE: [0] size pass, [1] scan, [2] emit pass) */
   uint32_t stage_launches[8]; /* kernels launched per stage                                      */
   uint64_t h2d_bytes;       /* bytes copied host->device by the call                            */
   uint64_t d2h_bytes;       /* bytes copied device->host by the call                            */

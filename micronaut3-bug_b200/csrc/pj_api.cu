@@ -589,6 +589,7 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_ORDER>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_USER>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_MIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_write_tile, cudaFuncAttributeMaxDynamicSharedMemorySize, WTILE_SMEM_BYTES);
   if (e != cudaSuccess) return fail_create(e, "cudaFuncSetAttribute");
   build_schema(&c->schema);
   e = cudaMemcpyToSymbol(c_schema, &c->schema, sizeof(Schema));
@@ -821,37 +822,69 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
   DevResult init;
   memset(&init, 0, sizeof init);
   init.n_records = n;
+  init.ok = c->staged ? 0 : 1;
   *c->h_res = init;
   PJ_CUDA(c, cudaMemcpyAsync(c->d_res, c->h_res, sizeof(DevResult), cudaMemcpyHostToDevice, c->stream));
-  Stage stage(c);
   WriteArgs wa;
   wa.n = n; wa.schema = schema; wa.array = framing == PJ_FRAMING_ARRAY; wa.inclusion = c->inclusion;
   wa.off = d_off; wa.out = d_out; wa.cap = cap; wa.res = c->d_res; wa.cols = dcols;
-  const int grid = persistent_grid(c, n, PARSE_THREADS);
-  k_write_size<<<grid, PARSE_THREADS, 0, c->stream>>>(wa);
-  count_launch(c, 0);
-  PJ_CUDA(c, cudaGetLastError());
-  stage.next();
-  ScanArgs sa;
-  sa.data = d_off; sa.stride = n + 1; sa.partial = d_part; sa.nchunks = nchunks; sa.slot_lo = 0;
-  sa.n_dev = &c->d_res->n_records; sa.n_cap = n; sa.totals = &c->d_res->out_bytes;
-  dim3 sgrid(nchunks, 1);
-  k_scan_reduce<uint64_t><<<sgrid, SCAN_THREADS, 0, c->stream>>>(sa);
-  k_scan_mid<uint64_t><<<1, 1024, 0, c->stream>>>(sa);
-  k_scan_apply<uint64_t><<<sgrid, SCAN_THREADS, 0, c->stream>>>(sa);
-  k_write_check<<<1, 32, 0, c->stream>>>(wa);
-  count_launch(c, 1, 4);
-  PJ_CUDA(c, cudaGetLastError());
-  stage.next();
-  k_write_emit<<<grid, PARSE_THREADS, 0, c->stream>>>(wa);
-  count_launch(c, 2);
-  PJ_CUDA(c, cudaGetLastError());
-  stage.next();
+  if (c->staged) {
+    /* the multi-pass writer: size pass, scan of the lengths, emit pass */
+    Stage stage(c);
+    const int grid = persistent_grid(c, n, PARSE_THREADS);
+    k_write_size<<<grid, PARSE_THREADS, 0, c->stream>>>(wa);
+    count_launch(c, 0);
+    PJ_CUDA(c, cudaGetLastError());
+    stage.next();
+    ScanArgs sa;
+    sa.data = d_off; sa.stride = n + 1; sa.partial = d_part; sa.nchunks = nchunks; sa.slot_lo = 0;
+    sa.n_dev = &c->d_res->n_records; sa.n_cap = n; sa.totals = &c->d_res->out_bytes;
+    dim3 sgrid(nchunks, 1);
+    k_scan_reduce<uint64_t><<<sgrid, SCAN_THREADS, 0, c->stream>>>(sa);
+    k_scan_mid<uint64_t><<<1, 1024, 0, c->stream>>>(sa);
+    k_scan_apply<uint64_t><<<sgrid, SCAN_THREADS, 0, c->stream>>>(sa);
+    k_write_check<<<1, 32, 0, c->stream>>>(wa);
+    count_launch(c, 1, 4);
+    PJ_CUDA(c, cudaGetLastError());
+    stage.next();
+    k_write_emit<<<grid, PARSE_THREADS, 0, c->stream>>>(wa);
+    count_launch(c, 2);
+    PJ_CUDA(c, cudaGetLastError());
+    stage.next();
+  } else {
+    /* the single-pass tile writer; stages: [0] state reset, [1] the closing kernel, [2] the tile kernel */
+    const uint64_t ntiles = n ? (n + TILE_THREADS - 1) / TILE_THREADS : 1;
+    { pj_status st = ensure(c, &c->tiles, 256 + ntiles * 16 + 256); if (st) return st; }
+    WTileArgs ta;
+    ta.w = wa;
+    ta.ticket = (uint32_t*)c->tiles.p;
+    ta.agg = (unsigned long long*)((uint8_t*)c->tiles.p + 256);
+    ta.inc = ta.agg + ntiles;
+    ta.ntiles = (uint32_t)ntiles;
+    Stage stage(c);
+    PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, 256 + ntiles * 16, c->stream));
+    stage.next();
+    cudaEvent_t ev_tile0 = c->ev[8], ev_tile1 = c->ev[9];
+    PJ_CUDA(c, cudaEventRecord(ev_tile0, c->stream));
+    k_write_tile<<<(unsigned)ntiles, TILE_THREADS, WTILE_SMEM_BYTES, c->stream>>>(ta);
+    PJ_CUDA(c, cudaEventRecord(ev_tile1, c->stream));
+    k_write_close<<<1, 32, 0, c->stream>>>(wa);
+    count_launch(c, 2); count_launch(c, 1);
+    PJ_CUDA(c, cudaGetLastError());
+    stage.next();
+    stage.next();
+  }
   PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
   PJ_CUDA(c, cudaStreamSynchronize(c->stream));
   PJ_CUDA(c, cudaGetLastError());
   collect_times(c, 3);
-  c->stats.main_kernel_ms = c->stats.stage_ms[0] + c->stats.stage_ms[2];
+  if (!c->staged) {
+    /* stage 1 covered both kernels: split it with the events around the tile kernel */
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, c->ev[8], c->ev[9]) == cudaSuccess) { c->stats.stage_ms[2] = ms; c->stats.stage_ms[1] -= ms; }
+    c->stats.main_kernel_ms = c->stats.stage_ms[2];
+  } else c->stats.main_kernel_ms = c->stats.stage_ms[0] + c->stats.stage_ms[2];
+  if (c->h_res->timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_write: a bounded device-side wait ran out");
   *out_len = c->h_res->out_bytes;
   c->stats.algorithmic_bytes = col_bytes + *out_len;
   if (!c->h_res->ok) return set_err(c, PJ_ERR_CAPACITY, "pj_write: %llu bytes needed, room for %llu", (unsigned long long)*out_len, (unsigned long long)cap);

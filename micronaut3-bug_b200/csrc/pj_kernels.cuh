@@ -713,5 +713,144 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
   }
 }
 
+/* ================================================================================================
+ * Single-pass tile writer (columns -> JSON text)
+ *
+ * One block takes TILE_THREADS consecutive records. Every thread measures its record (size pass of
+ * pj_write_core.cuh), the lengths are scanned inside the block, the tile's start in the output comes
+ * from a decoupled look-back over the tiles before it (one 64-bit running total; the protocol of the
+ * parse kernel), every thread then writes its record into a window in shared memory, and the block
+ * copies the window to the output with 16-byte stores. A tile whose text does not fit the window is
+ * written to global memory directly. Text is produced once and written to HBM once.
+ * ================================================================================================ */
+static constexpr uint32_t WTILE_WIN_BYTES = 48 * 1024;
+static constexpr uint32_t WTILE_SMEM_BYTES = WTILE_WIN_BYTES + 32;
+
+struct WTileArgs {
+  WriteArgs w;
+  unsigned long long* agg; /* [ntiles] text bytes of the tile | TS_VALID */
+  unsigned long long* inc; /* [ntiles] text bytes of all tiles up to and including it | TS_VALID */
+  uint32_t* ticket;
+  uint32_t ntiles;
+};
+
+/* Exclusive prefix of `tile` over all earlier tiles. Warp 0 only, all lanes; false when the bounded wait ran out. */
+__device__ __forceinline__ bool lookback_u64(const WTileArgs& a, uint32_t tile, uint32_t lane, unsigned long long* excl_out) {
+  unsigned long long excl = 0;
+  int64_t j = (int64_t)tile - 1;
+  const unsigned long long t0 = global_ns();
+  while (j >= 0) {
+    const int64_t mine = j - lane;
+    unsigned long long wa, wi;
+    uint32_t first_inc;
+    for (;;) {
+      wa = TS_VALID; wi = TS_VALID; /* tiles before the first: inclusive total 0 */
+      if (mine >= 0) { wi = ld_relaxed_u64(&a.inc[mine]); wa = ld_relaxed_u64(&a.agg[mine]); }
+      const bool has_inc = wi & TS_VALID, has_agg = wa & TS_VALID;
+      const uint32_t inc_mask = __ballot_sync(0xFFFFFFFFu, has_inc);
+      const uint32_t ready_mask = __ballot_sync(0xFFFFFFFFu, has_inc || has_agg);
+      first_inc = inc_mask ? (uint32_t)(__ffs((int)inc_mask) - 1) : 32u;
+      const uint32_t need = first_inc >= 31 ? 0xFFFFFFFFu : ((2u << first_inc) - 1u);
+      if ((ready_mask & need) == need) break;
+      uint32_t give_up = 0;
+      if (lane == 0) give_up = (global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)&a.w.res->timeout;
+      give_up = __shfl_sync(0xFFFFFFFFu, give_up, 0);
+      if (give_up) { if (lane == 0) atomicExch(&a.w.res->timeout, 1u); return false; }
+      __nanosleep(100);
+    }
+    unsigned long long c = lane < first_inc ? (wa & ~TS_VALID) : (lane == first_inc ? (wi & ~TS_VALID) : 0ull);
+#pragma unroll
+    for (int d = 16; d; d >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, d);
+    excl += c;
+    if (first_inc < 32) break;
+    j -= 32;
+  }
+  *excl_out = excl;
+  return true;
+}
+
+__global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_constant__ WTileArgs a) {
+  constexpr uint32_t NWARPS = TILE_THREADS / 32;
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ uint32_t sh_warp[NWARPS];
+  __shared__ uint32_t sh_tile, sh_ok;
+  __shared__ unsigned long long sh_base;
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) sh_tile = atomicAdd(a.ticket, 1u);
+  __syncthreads();
+  const uint32_t tile = sh_tile;
+  if (tile >= a.ntiles) return;
+  const uint64_t i = (uint64_t)tile * TILE_THREADS + tid;
+  uint32_t type = PJ_TYPE_NONE;
+  uint64_t row = 0;
+  const bool located = i < a.w.n && write_locate(a.w.schema, &a.w.cols, i, &type, &row);
+  uint32_t len = 0;
+  if (located) {
+    WOut w; w.dst = nullptr; w.n = 0;
+    write_record<false>(c_schema, &a.w.cols, type, row, a.w.inclusion, w);
+    len = (uint32_t)w.n + 1; /* LF, or the comma / closing bracket that follows the record */
+  }
+  const uint32_t incl = warp_incl_scan(len);
+  if (lane == 31) sh_warp[warp] = incl;
+  uint32_t loc = incl - len;
+  __syncthreads();
+  uint32_t tile_total = 0;
+#pragma unroll
+  for (uint32_t q = 0; q < NWARPS; ++q) { if (q < warp) loc += sh_warp[q]; tile_total += sh_warp[q]; }
+  const uint64_t lead = a.w.array ? 1 : 0; /* the opening bracket */
+  if (warp == 0) {
+    if (lane == 0) {
+      st_relaxed_u64(&a.agg[tile], TS_VALID | tile_total);
+      if (tile == 0) st_relaxed_u64(&a.inc[tile], TS_VALID | tile_total);
+    }
+    unsigned long long excl = 0;
+    const bool ok = lookback_u64(a, tile, lane, &excl);
+    if (lane == 0) {
+      if (tile != 0 && ok) st_relaxed_u64(&a.inc[tile], TS_VALID | (excl + tile_total));
+      const bool room = lead + excl + tile_total <= a.w.cap;
+      if (ok && !room) a.w.res->ok = 0;
+      if (tile == a.ntiles - 1) a.w.res->out_bytes = excl + tile_total; /* text bytes of all records */
+      sh_base = excl;
+      sh_ok = ok && room;
+    }
+  }
+  __syncthreads();
+  if (!sh_ok) return;
+  uint8_t* dst0 = a.w.out + lead + sh_base; /* where the tile's text starts */
+  const uint8_t sep = a.w.array ? (uint8_t)',' : (uint8_t)'\n';
+  if (tile_total + 16 <= WTILE_WIN_BYTES) {
+    /* the window mirrors the output's alignment: window byte k goes to (dst0 - pad)[k] */
+    const uint32_t pad = (uint32_t)(reinterpret_cast<uintptr_t>(dst0) & 15u);
+    if (located) {
+      WOut w; w.dst = smem + pad + loc; w.n = 0;
+      write_record<true>(c_schema, &a.w.cols, type, row, a.w.inclusion, w);
+      smem[pad + loc + w.n] = sep;
+    }
+    __syncthreads();
+    uint8_t* gbase = dst0 - pad;
+    const uint32_t end = pad + tile_total;
+    const uint32_t nchunks = (end + 15) >> 4;
+    for (uint32_t k = tid; k < nchunks; k += TILE_THREADS) {
+      const uint32_t lo = k << 4, hi = lo + 16;
+      if (lo >= pad && hi <= end) *reinterpret_cast<uint4*>(gbase + lo) = *reinterpret_cast<const uint4*>(smem + lo);
+      else for (uint32_t b = lo < pad ? pad : lo; b < (hi < end ? hi : end); ++b) gbase[b] = smem[b];
+    }
+  } else if (located) {
+    WOut w; w.dst = dst0 + loc; w.n = 0;
+    write_record<true>(c_schema, &a.w.cols, type, row, a.w.inclusion, w);
+    dst0[loc + w.n] = sep;
+  }
+}
+/* closes the text: brackets of array framing, the total, the verdict */
+__global__ void k_write_close(const __grid_constant__ WriteArgs a) {
+  if (threadIdx.x || blockIdx.x) return;
+  const uint64_t body = a.res->out_bytes;
+  const uint64_t total = a.array ? (body ? body + 1 : 2) : body;
+  a.res->out_bytes = total;
+  const bool ok = a.res->ok && total <= a.cap;
+  a.res->ok = ok;
+  if (a.array && ok) { a.out[0] = '['; a.out[total - 1] = ']'; }
+}
+
 }  // namespace pj
 #endif

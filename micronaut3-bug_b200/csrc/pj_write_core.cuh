@@ -40,9 +40,30 @@ PJ_HD void wput_i64(WOut& w, int64_t v) {
 template <bool WR>
 PJ_HD void wput_2d(WOut& w, uint32_t v) { wput<WR>(w, '0' + v / 10); wput<WR>(w, '0' + v % 10); }
 
+/* bytes the escapes of W3 add to the n bytes at s: 1 for the two-character escapes, 5 for \u00XX.
+ * Reads aligned 4-byte words where it can and looks closer only at words that hold a byte to escape. */
+PJ_HD uint32_t escape_extra_byte(uint32_t c) {
+  if (c >= 0x20) return (c == '"' || c == '\\') ? 1u : 0u;
+  return (c == 8 || c == 9 || c == 10 || c == 12 || c == 13) ? 1u : 5u;
+}
+PJ_HD uint32_t str_escape_extra(const uint8_t* s, uint32_t n) {
+  uint32_t extra = 0, i = 0;
+  while (i < n && ((uintptr_t)(s + i) & 3u)) extra += escape_extra_byte(ld_byte(s + i++));
+  for (; i + 4 <= n; i += 4) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(s + i);
+    const uint32_t xq = w ^ 0x22222222u, xb = w ^ 0x5C5C5C5Cu;
+    const uint32_t m = ((w - 0x20202020u) & ~w) | ((xq - 0x01010101u) & ~xq) | ((xb - 0x01010101u) & ~xb);
+    if (m & 0x80808080u)
+      for (uint32_t k = 0; k < 4; ++k) extra += escape_extra_byte((w >> (8 * k)) & 0xFFu);
+  }
+  for (; i < n; ++i) extra += escape_extra_byte(ld_byte(s + i));
+  return extra;
+}
+
 /* W3 */
 template <bool WR>
 PJ_HD void wput_str(WOut& w, const uint8_t* s, uint32_t n) {
+  if (!WR) { w.n += 2 + (uint64_t)n + str_escape_extra(s, n); return; }
   wput<WR>(w, '"');
   for (uint32_t i = 0; i < n; ++i) {
     uint32_t c = ld_byte(s + i);

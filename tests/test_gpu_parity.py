@@ -181,6 +181,45 @@ def test_writer_matches_checker(native, oracle, schema, framing, inclusion):
         assert c.write(schema, cols, np.zeros(100, np.uint8), framing, allow_capacity=True) == want.size
 
 
+@pytest.mark.parametrize("framing", [NDJSON, ARRAY])
+def test_staged_writer_matches_checker(native, oracle, framing):
+    """The multi-pass writer kept behind PJ_OPT_STAGED_PIPELINE gives the same text as the tile writer."""
+    flags = abi.PJ_GEN_ESCAPES | abi.PJ_GEN_SPARSE | abi.PJ_GEN_MALFORMED
+    text = pj.gen_text(4, 22, 0, 2500, flags)
+    cols = oracle.parse(4, text)
+    want = oracle.write(4, cols, framing, abi.PJ_INCLUDE_NON_NULL)
+    with native.Context(device=0, inclusion=abi.PJ_INCLUDE_NON_NULL, flags=abi.PJ_OPT_STAGED_PIPELINE) as c:
+        out = np.zeros(want.size + 16, np.uint8)
+        n = c.write(4, cols, out, framing)
+        assert n == want.size and np.array_equal(out[:n], want)
+        assert c.stats().kernel_launches >= 6
+
+
+@pytest.mark.parametrize("framing", [NDJSON, ARRAY])
+@pytest.mark.parametrize("misalign", [0, 1, 5, 15])
+def test_writer_tiles_larger_than_the_window_and_odd_alignment(native, oracle, framing, misalign):
+    """Tiles whose text exceeds the staging window are written straight to global memory; the output pointer
+    may have any alignment; records without a value (failed ones of a mixed stream) take no bytes."""
+    import torch
+
+    big = b'{"id":7,"name":"big","photoUrls":[' + b",".join(b'"' + bytes([97 + k % 26]) * 60 + b'"' for k in range(900)) + b"]}"
+    small = bytes(pj.gen_text(4, 9, 0, 400, abi.PJ_GEN_MALFORMED | abi.PJ_GEN_ESCAPES))
+    body = as_u8(small + big + b"\n" + small + b"{}\n" + big + b"\n")
+    cols = oracle.parse(4, body)
+    want = oracle.write(4, cols, framing, abi.PJ_INCLUDE_NON_EMPTY)
+    with native.Context(device=0) as c:
+        dcols = pj.DeviceColumns.from_host(cols, "cuda")
+        d_out = torch.zeros(want.size + 64, dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        n = c.write(4, dcols, d_out[misalign:], framing)
+        assert n == want.size and np.array_equal(d_out[misalign:misalign + n].cpu().numpy(), want)
+        assert int(d_out[misalign + n:].max()) == 0 and (misalign == 0 or int(d_out[:misalign].max()) == 0)
+        st = c.stats()
+        assert st.kernel_launches == 2
+        # too small an output: nothing but the needed size is promised
+        assert c.write(4, dcols, d_out[:1000], framing, allow_capacity=True) == want.size
+
+
 def test_writer_empty_tables(native):
     import torch
 
