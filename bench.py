@@ -182,7 +182,7 @@ def main():
     ap.add_argument("--records", type=int, default=1_000_000, help="records per GPU and step")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="pet", choices=["pet", "mixed"], help="pet: 1M Pet records (the headline configuration); mixed: Pet/Order/User 50/30/20 with 1%% malformed")
+    ap.add_argument("--workload", default="pet", choices=["pet", "mixed", "zipf"], help="pet: 1M Pet records (the headline configuration); mixed: Pet/Order/User 50/30/20 with 1%% malformed; zipf: Pets with zipf(1.2) list lengths, 5%% escaped strings, random blanks")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--host-piece-bytes", type=int, default=0, help="pj_options.host_piece_bytes of the end-to-end leg (0 = library default)")
     args = ap.parse_args()
@@ -208,9 +208,9 @@ def main():
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # NCCL's version banner must not land on stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     R = args.records
-    mixed_wl = args.workload == "mixed"
-    PET = abi.PJ_SCHEMA_MIXED if mixed_wl else abi.PJ_SCHEMA_PET  # the schema of the timed workload
-    gen_flags = abi.PJ_GEN_MALFORMED if mixed_wl else 0
+    mixed_wl = args.workload != "pet"  # a side workload: parse only, no end-to-end or CPU leg
+    PET = abi.PJ_SCHEMA_MIXED if args.workload == "mixed" else abi.PJ_SCHEMA_PET  # the schema of the timed workload
+    gen_flags = {"pet": 0, "mixed": abi.PJ_GEN_MALFORMED, "zipf": abi.PJ_GEN_ZIPF_LISTS | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE}[args.workload]
     if mixed_wl:
         args.no_e2e = True
         args.no_cpu_baseline = True
@@ -226,7 +226,7 @@ def main():
     stream = torch.cuda.Stream(device=dev)  # the library launches on this stream; the timing events are recorded on it
     torch.cuda.set_stream(stream)
     ctx = pj.Context(device=local, inclusion=abi.PJ_INCLUDE_NON_NULL, stream=stream.cuda_stream, host_piece_bytes=args.host_piece_bytes)
-    cols = pj.DeviceColumns.sized_for(PET, R + 16, nbytes + SLACK, 6 * R, dev)
+    cols = pj.DeviceColumns.sized_for(PET, R + 16, nbytes + SLACK, max(6 * R, (nbytes + SLACK) // 12), dev)
     sharded = None
     if world > 1:
         sharded = importlib.import_module("micronaut3-bug_b200.sharded").ShardedParser(ctx, PET, SLACK)
@@ -290,7 +290,7 @@ def main():
 
     # ---- the reverse direction on the parsed columns ------------------------------------------------------
     d_out = torch.empty(nbytes + 64, dtype=torch.uint8, device=dev)
-    w_ms, w_dev_ms, w_launch, w_alg, w_len = 0.0, 0.0, 0, 0, 0
+    w_ms, w_dev_ms, w_launch, w_alg, w_len, w_kernel_ms, w_phase = 0.0, 0.0, 0, 0, 0, 0.0, []
     wsteps = max(3, args.steps // 2)
     if not sharded and not mixed_wl:
         for _ in range(3):
@@ -302,6 +302,7 @@ def main():
             w_len = ctx.write(PET, cols, d_out)
             st = ctx.stats()
             w_dev_ms += st.device_ms; w_launch += st.kernel_launches; w_alg = st.algorithmic_bytes
+            w_kernel_ms += st.main_kernel_ms; w_phase = [int(x) // max(int(st.tiles), 1) for x in st.phase_cycles]
         w1.record(stream)
         torch.cuda.synchronize()
         w_ms = w0.elapsed_time(w1)
@@ -354,7 +355,7 @@ def main():
         "vs_baseline": None,
         "dtype": "u8",
         "data": "synthetic",
-        "config": {"workload": "Pet/Order/User 50/30/20 with 1% malformed records as NDJSON (BASELINE configs[2] distributions)" if mixed_wl else "1M Pet records as NDJSON, one record per line (BASELINE configs[1])", "records_per_gpu": R, "seed": SEED,
+        "config": {"workload": {"pet": "1M Pet records as NDJSON, one record per line (BASELINE configs[1])", "mixed": "Pet/Order/User 50/30/20 with 1% malformed records as NDJSON (BASELINE configs[2] distributions)", "zipf": "Pets with zipf(1.2) list lengths, 5% escaped strings, random blanks as NDJSON (BASELINE configs[3] distributions)"}[args.workload], "records_per_gpu": R, "seed": SEED,
                    "input_bytes_per_gpu": nbytes, "l2": "input (292 MB at 1M records) and columns are larger than the 126 MB L2; no flush between steps",
                    "sharding": "one byte range per GPU, 64 KiB slack from the next rank, counters all-gathered" if world > 1 else "single GPU"},
         "gb_per_s": total_rec * args.steps / (ms * 1e-3) * nbytes / R / 1e9,
@@ -379,7 +380,9 @@ def main():
         line["reserialise"] = {"records_per_s": R * wsteps / (w_ms * 1e-3), "gb_per_s_out": nbytes * wsteps / (w_ms * 1e-3) / 1e9, "ms_per_step": w_ms / wsteps,
                                "steps": wsteps, "gpu_launches": w_launch, "byte_identical_to_input": True,
                                "roofline": {"bound": "hbm", "achieved": wa, "peak": peak, "unit": "GB/s", "frac": wa / peak, "traffic": None,
-                                            "algorithmic_bytes_per_step": int(w_alg)}}
+                                            "algorithmic_bytes_per_step": int(w_alg), "kernel": "k_write_tile", "kernel_ms_per_launch": w_kernel_ms / wsteps,
+                                            "kernel_achieved": w_alg / (w_kernel_ms / wsteps * 1e-3) / 1e9,
+                                            "phase_cycles_per_block": w_phase}}
     if not args.no_cpu_baseline:
         threads = host_threads()
         sample = min(R, 200_000)

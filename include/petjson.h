@@ -268,7 +268,8 @@ typedef struct pj_call_stats {
   float stage_ms[8];        /* CUDA-event time per stage. parse: [0] record index, [1] set-up between
                                the kernels (record count read-back, state reset), [2] the tile kernel
                                (with PJ_OPT_STAGED_PIPELINE: [1] size pass, [2] counter scans, [3] emit
-                               pass, [4] closing offsets); write: [0] state reset, [1] the closing kernel, [2] the
+                               pass, [4] closing offsets); write: [0] state reset and the scan of the string arenas for bytes
+                               to escape, [1] the closing kernel, [2] the
                                tile kernel (with PJ_OPT_STAGED_PIPELINE: [0] size pass, [1] scan, [2] emit pass) */
   uint32_t stage_launches[8]; /* kernels launched per stage                                      */
   uint64_t h2d_bytes;       /* bytes copied host->device by the call                            */
@@ -276,12 +277,13 @@ typedef struct pj_call_stats {
   uint64_t algorithmic_bytes; /* input bytes + bytes of every produced column (parse), or column
                                  bytes read + JSON bytes written (write)                        */
   uint64_t fast_records;    /* parse: records decoded by the speculative word-at-a-time pass alone */
-  uint64_t phase_cycles[4]; /* parse: SM cycles summed over the blocks of the tile kernel: staging,
-                               tokenising, look-back wait, emission                              */
+  uint64_t phase_cycles[4]; /* SM cycles summed over the blocks of the tile kernel. parse: staging,
+                               tokenising, look-back wait, emission; write: size pass, look-back
+                               wait, text into the window, copy-out                              */
   uint64_t lookback_polls;  /* parse: times a block found the block before it not yet sized        */
   uint64_t lookback_rounds; /* parse: 32-block look-back rounds, summed over blocks                 */
   uint32_t tile_records;    /* parse: records per block of the tile kernel                       */
-  uint32_t tiles;           /* parse: blocks of the tile kernel                                   */
+  uint32_t tiles;           /* blocks of the tile kernel                                          */
 } pj_call_stats;
 
 /* Library version as major * 1000 + minor. */

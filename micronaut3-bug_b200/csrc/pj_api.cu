@@ -852,7 +852,7 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
     PJ_CUDA(c, cudaGetLastError());
     stage.next();
   } else {
-    /* the single-pass tile writer; stages: [0] state reset, [1] the closing kernel, [2] the tile kernel */
+    /* the single-pass tile writer; stages: [0] state reset and the look at the string arenas, [1] the closing kernel, [2] the tile kernel */
     const uint64_t ntiles = n ? (n + TILE_THREADS - 1) / TILE_THREADS : 1;
     { pj_status st = ensure(c, &c->tiles, 256 + ntiles * 16 + 256); if (st) return st; }
     WTileArgs ta;
@@ -861,8 +861,26 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
     ta.agg = (unsigned long long*)((uint8_t*)c->tiles.p + 256);
     ta.inc = ta.agg + ntiles;
     ta.ntiles = (uint32_t)ntiles;
+    /* the string arenas of the schema */
+    ArenaArgs aa;
+    memset(&aa, 0, sizeof aa);
+    aa.res = c->d_res;
+    auto add_arenas = [&](const ObjDesc& O, auto&& self) -> void {
+      for (int i = 0; i < (int)O.nfields; ++i) {
+        const FieldDesc& F = O.f[i];
+        int col = -1;
+        if (F.kind == K_STR) col = F.col + 1;
+        else if (F.kind == K_LIST_STR) col = F.col + 2;
+        else if (F.kind == K_OBJ || F.kind == K_LIST_OBJ) self(c->schema.obj[F.child], self);
+        if (col >= 0 && cols->col[col].count && aa.count < 12) { aa.p[aa.count] = (const uint8_t*)dcols.ptr[col]; aa.n[aa.count] = cols->col[col].count; aa.count++; }
+      }
+    };
+    if (schema == PJ_SCHEMA_PET || mixed) add_arenas(c->schema.obj[OBJ_PET], add_arenas);
+    if (schema == PJ_SCHEMA_ORDER || mixed) add_arenas(c->schema.obj[OBJ_ORDER], add_arenas);
+    if (schema == PJ_SCHEMA_USER || mixed) add_arenas(c->schema.obj[OBJ_USER], add_arenas);
     Stage stage(c);
     PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, 256 + ntiles * 16, c->stream));
+    if (aa.count) { k_arena_flags<<<persistent_grid(c, col_bytes / 16 + 1, 256), 256, 0, c->stream>>>(aa); count_launch(c, 0); }
     stage.next();
     cudaEvent_t ev_tile0 = c->ev[8], ev_tile1 = c->ev[9];
     PJ_CUDA(c, cudaEventRecord(ev_tile0, c->stream));
@@ -884,6 +902,8 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
     if (cudaEventElapsedTime(&ms, c->ev[8], c->ev[9]) == cudaSuccess) { c->stats.stage_ms[2] = ms; c->stats.stage_ms[1] -= ms; }
     c->stats.main_kernel_ms = c->stats.stage_ms[2];
   } else c->stats.main_kernel_ms = c->stats.stage_ms[0] + c->stats.stage_ms[2];
+  for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] = c->h_res->phase_cycles[k];
+  c->stats.tiles = c->staged ? 0 : (uint32_t)(n ? (n + TILE_THREADS - 1) / TILE_THREADS : 1);
   if (c->h_res->timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_write: a bounded device-side wait ran out");
   *out_len = c->h_res->out_bytes;
   c->stats.algorithmic_bytes = col_bytes + *out_len;

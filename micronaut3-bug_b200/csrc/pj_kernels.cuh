@@ -20,6 +20,7 @@
 #include "pj_fast.cuh"
 #include "pj_index.cuh"
 #include "pj_write_core.cuh"
+#include "pj_write_fast.cuh"
 
 namespace pj {
 
@@ -35,7 +36,7 @@ struct DevResult {
   uint32_t doc_err_kind;
   uint32_t ok;      /* every output fits its buffer */
   uint32_t timeout; /* a bounded wait ran out */
-  uint32_t pad;
+  uint32_t needs_escape; /* writer: some string byte of the columns has to be escaped (k_arena_flags) */
   unsigned long long n_fast;  /* records decoded by the speculative pass alone */
   unsigned long long phase_cycles[4]; /* tile kernel, summed over blocks: staging, tokenising, look-back, emit */
   unsigned long long lookback_polls, lookback_rounds;
@@ -717,7 +718,7 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
  * Single-pass tile writer (columns -> JSON text)
  *
  * One block takes TILE_THREADS consecutive records. Every thread measures its record (size pass of
- * pj_write_core.cuh), the lengths are scanned inside the block, the tile's start in the output comes
+ * pj_write_fast.cuh), the lengths are scanned inside the block, the tile's start in the output comes
  * from a decoupled look-back over the tiles before it (one 64-bit running total; the protocol of the
  * parse kernel), every thread then writes its record into a window in shared memory, and the block
  * copies the window to the output with 16-byte stores. A tile whose text does not fit the window is
@@ -769,6 +770,38 @@ __device__ __forceinline__ bool lookback_u64(const WTileArgs& a, uint32_t tile, 
   return true;
 }
 
+/* Does any byte of the string arenas need a JSON escape (below 0x20, '"', '\\')? Text is mostly free of
+ * them, and knowing so lets the tile writer take string lengths from the offset columns alone. */
+struct ArenaArgs {
+  const uint8_t* p[12];
+  uint64_t n[12];
+  uint32_t count;
+  DevResult* res;
+};
+__device__ __forceinline__ uint32_t word_needs_escape(uint32_t x) {
+  const uint32_t xq = x ^ 0x22222222u, xb = x ^ 0x5C5C5C5Cu;
+  return (((x - 0x20202020u) & ~x) | ((xq - 0x01010101u) & ~xq) | ((xb - 0x01010101u) & ~xb)) & 0x80808080u;
+}
+__global__ void __launch_bounds__(256) k_arena_flags(const __grid_constant__ ArenaArgs a) {
+  const uint64_t gtid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, gsize = (uint64_t)gridDim.x * blockDim.x;
+  uint32_t any = 0;
+  for (uint32_t r = 0; r < a.count; ++r) {
+    const uint8_t* p = a.p[r];
+    const uint64_t n = a.n[r];
+    uint64_t head = (16 - (reinterpret_cast<uintptr_t>(p) & 15u)) & 15u;
+    if (head > n) head = n;
+    const uint64_t nvec = (n - head) >> 4, tail = head + (nvec << 4);
+    const uint4* v = reinterpret_cast<const uint4*>(p + head);
+    for (uint64_t k = gtid; k < nvec; k += gsize) {
+      const uint4 x = __ldg(v + k);
+      any |= word_needs_escape(x.x) | word_needs_escape(x.y) | word_needs_escape(x.z) | word_needs_escape(x.w);
+    }
+    if (gtid < head) any |= escape_extra_byte(p[gtid]);
+    if (gtid < n - tail) any |= escape_extra_byte(p[tail + gtid]);
+  }
+  if (__syncthreads_or((int)any) && threadIdx.x == 0) a.res->needs_escape = 1u;
+}
+
 __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_constant__ WTileArgs a) {
   constexpr uint32_t NWARPS = TILE_THREADS / 32;
   extern __shared__ __align__(16) uint8_t smem[];
@@ -783,17 +816,20 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_con
   const uint64_t i = (uint64_t)tile * TILE_THREADS + tid;
   uint32_t type = PJ_TYPE_NONE;
   uint64_t row = 0;
+  const bool plain = !a.w.res->needs_escape; /* no string of the columns holds a byte to escape */
+  const long long c0 = clock64();
   const bool located = i < a.w.n && write_locate(a.w.schema, &a.w.cols, i, &type, &row);
   uint32_t len = 0;
   if (located) {
     WOut w; w.dst = nullptr; w.n = 0;
-    write_record<false>(c_schema, &a.w.cols, type, row, a.w.inclusion, w);
+    if (plain) fwrite_record<false, true>(&a.w.cols, type, row, a.w.inclusion, w); else fwrite_record<false, false>(&a.w.cols, type, row, a.w.inclusion, w);
     len = (uint32_t)w.n + 1; /* LF, or the comma / closing bracket that follows the record */
   }
   const uint32_t incl = warp_incl_scan(len);
   if (lane == 31) sh_warp[warp] = incl;
   uint32_t loc = incl - len;
   __syncthreads();
+  const long long c1 = clock64();
   uint32_t tile_total = 0;
 #pragma unroll
   for (uint32_t q = 0; q < NWARPS; ++q) { if (q < warp) loc += sh_warp[q]; tile_total += sh_warp[q]; }
@@ -815,6 +851,8 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_con
     }
   }
   __syncthreads();
+  const long long c2 = clock64();
+  long long c3 = c2;
   if (!sh_ok) return;
   uint8_t* dst0 = a.w.out + lead + sh_base; /* where the tile's text starts */
   const uint8_t sep = a.w.array ? (uint8_t)',' : (uint8_t)'\n';
@@ -823,10 +861,11 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_con
     const uint32_t pad = (uint32_t)(reinterpret_cast<uintptr_t>(dst0) & 15u);
     if (located) {
       WOut w; w.dst = smem + pad + loc; w.n = 0;
-      write_record<true>(c_schema, &a.w.cols, type, row, a.w.inclusion, w);
+      if (plain) fwrite_record<true, true>(&a.w.cols, type, row, a.w.inclusion, w); else fwrite_record<true, false>(&a.w.cols, type, row, a.w.inclusion, w);
       smem[pad + loc + w.n] = sep;
     }
     __syncthreads();
+    c3 = clock64();
     uint8_t* gbase = dst0 - pad;
     const uint32_t end = pad + tile_total;
     const uint32_t nchunks = (end + 15) >> 4;
@@ -837,8 +876,16 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_con
     }
   } else if (located) {
     WOut w; w.dst = dst0 + loc; w.n = 0;
-    write_record<true>(c_schema, &a.w.cols, type, row, a.w.inclusion, w);
+    if (plain) fwrite_record<true, true>(&a.w.cols, type, row, a.w.inclusion, w); else fwrite_record<true, false>(&a.w.cols, type, row, a.w.inclusion, w);
     dst0[loc + w.n] = sep;
+  }
+  __syncthreads();
+  if (tid == 0) { /* cycles per phase: size pass, look-back, text into the window, copy-out */
+    const long long c4 = clock64();
+    atomicAdd(&a.w.res->phase_cycles[0], (unsigned long long)(c1 - c0));
+    atomicAdd(&a.w.res->phase_cycles[1], (unsigned long long)(c2 - c1));
+    atomicAdd(&a.w.res->phase_cycles[2], (unsigned long long)(c3 - c2));
+    atomicAdd(&a.w.res->phase_cycles[3], (unsigned long long)(c4 - c3));
   }
 }
 /* closes the text: brackets of array framing, the total, the verdict */

@@ -215,7 +215,7 @@ def test_writer_tiles_larger_than_the_window_and_odd_alignment(native, oracle, f
         assert n == want.size and np.array_equal(d_out[misalign:misalign + n].cpu().numpy(), want)
         assert int(d_out[misalign + n:].max()) == 0 and (misalign == 0 or int(d_out[:misalign].max()) == 0)
         st = c.stats()
-        assert st.kernel_launches == 2
+        assert st.kernel_launches == 3  # the look at the string arenas, the tile writer, the closing kernel
         # too small an output: nothing but the needed size is promised
         assert c.write(4, dcols, d_out[:1000], framing, allow_capacity=True) == want.size
 
