@@ -45,12 +45,22 @@ def build_library(force: bool = False, verbose_ptxas: bool = False) -> str:
     deps = _sources(CSRC, (".cu", ".cuh", ".h", ".c")) + [os.path.join(INCLUDE, "petjson.h")]
     if not force and _newer(LIB, deps):
         return LIB
+    from concurrent.futures import ThreadPoolExecutor
+
     nvcc = os.environ.get("NVCC", "nvcc")
+    extra = ["-Xptxas", "-v"] if verbose_ptxas else []
     gen_o = os.path.join(CSRC, "pj_gen.o")
     api_o = os.path.join(CSRC, "pj_api.o")
-    _run(["gcc", "-O2", "-std=c11", "-fPIC", "-Wall", "-I", INCLUDE, "-c", os.path.join(CSRC, "pj_gen.c"), "-o", gen_o])
-    _run([nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose_ptxas else []), "-c", os.path.join(CSRC, "pj_api.cu"), "-o", api_o])
-    _run([nvcc, "-shared", "-o", LIB, api_o, gen_o, "-lm"])
+    jobs = [["gcc", "-O2", "-std=c11", "-fPIC", "-Wall", "-I", INCLUDE, "-c", os.path.join(CSRC, "pj_gen.c"), "-o", gen_o],
+            [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, "pj_api.cu"), "-o", api_o]]
+    tile_objs = []
+    for schema in (1, 2, 3, 4):  # the tile kernel once per model set (Pet, Order, User, mixed), side by side
+        obj = os.path.join(CSRC, f"pj_tile_{schema}.o")
+        tile_objs.append(obj)
+        jobs.append([nvcc, *NVCC_FLAGS, *extra, f"-DPJ_TILE_SCHEMA={schema}", "-c", os.path.join(CSRC, "pj_tile_inst.cu"), "-o", obj])
+    with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
+        list(pool.map(_run, jobs))
+    _run([nvcc, "-shared", "-o", LIB, api_o, *tile_objs, gen_o, "-lm"])
     return LIB
 
 

@@ -17,6 +17,14 @@
 
 using namespace pj;
 
+/* the four instantiations of the tile kernel live in objects of their own (pj_tile_inst.cu) */
+namespace pj {
+cudaError_t tile_init_1(const Schema*); cudaError_t tile_launch_1(const TileArgs*, unsigned, cudaStream_t);
+cudaError_t tile_init_2(const Schema*); cudaError_t tile_launch_2(const TileArgs*, unsigned, cudaStream_t);
+cudaError_t tile_init_3(const Schema*); cudaError_t tile_launch_3(const TileArgs*, unsigned, cudaStream_t);
+cudaError_t tile_init_4(const Schema*); cudaError_t tile_launch_4(const TileArgs*, unsigned, cudaStream_t);
+}
+
 namespace {
 
 thread_local char g_create_error[256] = "";
@@ -440,13 +448,12 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
       PJ_CUDA(c, cudaMemcpyAsync(&c->d_res->ok, &one, sizeof one, cudaMemcpyHostToDevice, c->stream));
       stage.next(); /* stage 1: set-up */
       switch (schema) {
-        case PJ_SCHEMA_PET: k_parse_tile<PJ_SCHEMA_PET><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
-        case PJ_SCHEMA_ORDER: k_parse_tile<PJ_SCHEMA_ORDER><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
-        case PJ_SCHEMA_USER: k_parse_tile<PJ_SCHEMA_USER><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
-        default: k_parse_tile<PJ_SCHEMA_MIXED><<<(unsigned)ntiles, TILE_THREADS, TILE_SMEM_BYTES, c->stream>>>(ta); break;
+        case PJ_SCHEMA_PET: PJ_CUDA(c, tile_launch_1(&ta, (unsigned)ntiles, c->stream)); break;
+        case PJ_SCHEMA_ORDER: PJ_CUDA(c, tile_launch_2(&ta, (unsigned)ntiles, c->stream)); break;
+        case PJ_SCHEMA_USER: PJ_CUDA(c, tile_launch_3(&ta, (unsigned)ntiles, c->stream)); break;
+        default: PJ_CUDA(c, tile_launch_4(&ta, (unsigned)ntiles, c->stream)); break;
       }
       count_launch(c, 2);
-      PJ_CUDA(c, cudaGetLastError());
       stage.next(); /* stage 2: the tile kernel */
       n_stages = 3;
     }
@@ -585,10 +592,11 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   e = cudaMallocHost(&c->h_res, sizeof(DevResult));
   if (e != cudaSuccess) return fail_create(e, "cudaMallocHost");
   for (auto& ev : c->ev) { e = cudaEventCreate(&ev); if (e != cudaSuccess) return fail_create(e, "cudaEventCreate"); }
-  e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_PET>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_ORDER>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_USER>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_parse_tile<PJ_SCHEMA_MIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM_BYTES);
+  build_schema(&c->schema);
+  e = tile_init_1(&c->schema);
+  if (e == cudaSuccess) e = tile_init_2(&c->schema);
+  if (e == cudaSuccess) e = tile_init_3(&c->schema);
+  if (e == cudaSuccess) e = tile_init_4(&c->schema);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(k_write_tile, cudaFuncAttributeMaxDynamicSharedMemorySize, WTILE_SMEM_BYTES);
   if (e != cudaSuccess) return fail_create(e, "cudaFuncSetAttribute");
   build_schema(&c->schema);

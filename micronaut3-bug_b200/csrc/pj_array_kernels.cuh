@@ -84,7 +84,7 @@ __device__ __forceinline__ ArrFn fn_warp_scan(ArrFn f) {
   return f;
 }
 
-__global__ void __launch_bounds__(ARR_THREADS) k_arr_summary(const __grid_constant__ ArrArgs a) {
+static __global__ void __launch_bounds__(ARR_THREADS) k_arr_summary(const __grid_constant__ ArrArgs a) {
   __shared__ ArrFn sh[ARR_THREADS / 32];
   const uint64_t w = (uint64_t)blockIdx.x * ARR_THREADS + threadIdx.x;
   ArrFn f = fn_identity();
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(ARR_THREADS) k_arr_summary(const __grid_consta
 }
 
 /* One thread walks the tiles in order. (A tile is 16 KiB, so even a 4 GiB input has 262144 of them.) */
-__global__ void k_arr_scan_tiles(const __grid_constant__ ArrArgs a) {
+static __global__ void k_arr_scan_tiles(const __grid_constant__ ArrArgs a) {
   if (threadIdx.x || blockIdx.x) return;
   ArrState st;
   st.c = 0; st.s = 0; st.d = 0;
@@ -112,7 +112,7 @@ __global__ void k_arr_scan_tiles(const __grid_constant__ ArrArgs a) {
   a.res->arr_final_d = st.d;
 }
 
-__global__ void __launch_bounds__(ARR_THREADS) k_arr_mark(const __grid_constant__ ArrArgs a) {
+static __global__ void __launch_bounds__(ARR_THREADS) k_arr_mark(const __grid_constant__ ArrArgs a) {
   __shared__ ArrFn sh[ARR_THREADS / 32];
   const uint64_t w = (uint64_t)blockIdx.x * ARR_THREADS + threadIdx.x;
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -21,7 +21,7 @@
 
 #if defined(__CUDACC__)
 #define PJ_HD __host__ __device__ __forceinline__
-#define PJ_HD_NOINLINE __host__ __device__ __noinline__
+#define PJ_HD_NOINLINE inline __host__ __device__ __noinline__
 #else
 #define PJ_HD inline
 #define PJ_HD_NOINLINE

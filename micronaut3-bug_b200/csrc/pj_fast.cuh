@@ -3,8 +3,7 @@
  * model tables of pj_schema.h.
  *
  * fast_record<>() reads a record 8 bytes at a time from a window staged in shared memory and accepts
- * it only when it is "plain": valid, every key known and met once, no null, no escape, printable
- * ASCII strings. Such a record never needs the byte-at-a-time machinery of
+ * it only when it is "plain": valid, every key known and met once. Such a record never needs the byte-at-a-time machinery of
  * pj_core.cuh, so its values, counts and the place of every string are known after ONE pass; they
  * are kept (values in registers, strings as 8-byte tape entries in shared memory) until the record's
  * output positions are known, and then replayed by fast_emit<>(). Anything else makes fast_record<>()
@@ -91,11 +90,12 @@ PJ_HD uint32_t swar_parse_k(uint64_t w, uint32_t k) {
 
 /* ---- tape ---------------------------------------------------------------------------------------
  * 32-bit words in reading order, kept in shared memory until the record's output positions are known:
- *   string          bits 0..3 byte-counter slot, bits 4..15 length (< 4096), bits 16..31 window offset
+ *   string          bits 0..3 byte-counter slot, bits 4..14 decoded length (< 2048), bit 15 "has backslash escapes",
+ *                   bits 16..31 window offset of the first content byte
  *   list element    bits 0..3 = TAPE_ELEM, bits 4..11 presence bits, bits 12..15 the list's item-counter slot;
  *                   followed by two words (low, high) for every non-string property of the element, in
  *                   property order, and then by the element's strings as ordinary string words          */
-enum { TAPE_ELEM = 15, TAPE_MAX_STR = 4095 };
+enum { TAPE_ELEM = 15, TAPE_MAX_STR = 2047, TAPE_ESC = 1u << 15 };
 static_assert(NSLOT <= 15, "slot numbers share four bits with the element marker");
 struct Tape {
   uint32_t* e; /* word k of this thread is e[k * stride] */
@@ -107,7 +107,7 @@ PJ_HD void tape_push(Tape& t, uint32_t v) {
 }
 PJ_HD void tape_set(Tape& t, uint32_t k, uint32_t v) { if (k < t.cap) t.e[(size_t)k * t.stride] = v; }
 PJ_HD uint32_t tape_get(const Tape& t, uint32_t k) { return t.e[(size_t)k * t.stride]; }
-PJ_HD uint32_t tape_str(uint32_t slot, uint32_t len, uint32_t pos) { return slot | (len << 4) | (pos << 16); }
+PJ_HD uint32_t tape_str(uint32_t slot, uint32_t len, uint32_t pos, uint32_t esc) { return slot | (len << 4) | (esc ? (uint32_t)TAPE_ESC : 0u) | (pos << 16); }
 
 /* tokeniser position: window offsets */
 struct FastState {
@@ -140,9 +140,84 @@ PJ_HD uint32_t fast_ws(const Win& w, FastState& f) {
   return x;
 }
 
-/* A plain string at f.p (opening quote): *pos = offset of the first content byte, *len = bytes.
- * Only for VALUES: it reports the failure a value string has when the record ends inside it. */
-PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len) {
+/* four hex digits at window offset q; false if one is not a hex digit */
+PJ_HD bool fast_hex4(const Win& w, uint32_t q, uint32_t* out) {
+  uint32_t v = 0;
+  for (uint32_t i = 0; i < 4; ++i) {
+    const int h = hexval(wbyte(w, q + i));
+    if (h < 0) return false;
+    v = v << 4 | (uint32_t)h;
+  }
+  *out = v;
+  return true;
+}
+PJ_HD uint32_t utf8_len(uint32_t cp) { return cp < 0x80 ? 1u : (cp < 0x800 ? 2u : (cp < 0x10000 ? 3u : 4u)); }
+
+/* The part of a string value after its first byte that is not plain (a backslash or a non-ASCII byte, at window
+ * offset q, with `dec` decoded bytes before it), out of line because it is rare and large. Accepts what
+ * lex_string() of pj_core.cuh accepts (escapes, surrogate pairs, well-formed UTF-8). Result: bits 0..31 offset
+ * of the closing quote, bits 32..55 decoded bytes, bit 56 "has backslash escapes", bits 60..61 status
+ * (0 accepted, 1 refused, 2 the record ends at bits 0..31 inside the string). */
+enum { FS_OK = 0, FS_REFUSED = 1, FS_EOF = 2 };
+PJ_HD uint64_t fs_result(uint32_t status, uint32_t q, uint32_t dec, uint32_t esc) {
+  return (uint64_t)q | ((uint64_t)(dec & 0xFFFFFFu) << 32) | ((uint64_t)esc << 56) | ((uint64_t)status << 60);
+}
+PJ_HD_NOINLINE uint64_t fast_string_tail(const uint8_t* ws, uint32_t q, uint32_t dec, uint32_t limit, uint32_t lf_ws) {
+  Win w;
+  w.s = ws; w.w0 = 0;
+  uint32_t any_esc = 0;
+  for (;;) {
+    const uint64_t m = swar_str_special(wpeek8(w, q));
+    if (!m) { q += 8; dec += 8; if (q > limit) return fs_result(FS_REFUSED, 0, 0, 0); continue; }
+    const uint32_t k = ctz64(m) >> 3;
+    q += k; dec += k;
+    if (q >= limit || dec > 0xFFFFFFu) return fs_result(FS_REFUSED, 0, 0, 0);
+    const uint32_t x = wbyte(w, q);
+    if (x == '"') return fs_result(FS_OK, q, dec, any_esc);
+    if (x == '\\') {
+      const uint32_t y = wbyte(w, q + 1);
+      if (y == 'u') {
+        uint32_t cp;
+        if (q + 6 > limit || !fast_hex4(w, q + 2, &cp)) return fs_result(FS_REFUSED, 0, 0, 0);
+        if (cp - 0xDC00u < 0x400u) return fs_result(FS_REFUSED, 0, 0, 0);
+        if (cp - 0xD800u < 0x400u) {
+          uint32_t lo;
+          if (q + 12 > limit || wbyte(w, q + 6) != '\\' || wbyte(w, q + 7) != 'u' || !fast_hex4(w, q + 8, &lo)) return fs_result(FS_REFUSED, 0, 0, 0);
+          if (lo - 0xDC00u >= 0x400u) return fs_result(FS_REFUSED, 0, 0, 0);
+          dec += 4; q += 12;
+        } else { dec += utf8_len(cp); q += 6; }
+      } else if (y == '"' || y == '\\' || y == '/' || y == 'b' || y == 'f' || y == 'n' || y == 'r' || y == 't') {
+        if (q + 2 > limit) return fs_result(FS_REFUSED, 0, 0, 0);
+        dec += 1; q += 2;
+      } else return fs_result(FS_REFUSED, 0, 0, 0);
+      any_esc = 1;
+      continue;
+    }
+    if (x < 0x20) return (x == '\n' && !lf_ws) ? fs_result(FS_EOF, q, 0, 0) : fs_result(FS_REFUSED, 0, 0, 0);
+    /* RFC 3629, the table of lex_string() */
+    uint32_t need, lo = 0x80, hi = 0xBF;
+    if (x - 0xC2u <= 0x1Du) need = 1;
+    else if (x == 0xE0) { need = 2; lo = 0xA0; }
+    else if (x == 0xED) { need = 2; hi = 0x9F; }
+    else if (x - 0xE1u <= 0x0Eu) need = 2;
+    else if (x == 0xF0) { need = 3; lo = 0x90; }
+    else if (x - 0xF1u <= 2u) need = 3;
+    else if (x == 0xF4) { need = 3; hi = 0x8F; }
+    else return fs_result(FS_REFUSED, 0, 0, 0);
+    if (q + need >= limit) return fs_result(FS_REFUSED, 0, 0, 0);
+    const uint32_t y1 = wbyte(w, q + 1);
+    if (y1 < lo || y1 > hi) return fs_result(FS_REFUSED, 0, 0, 0);
+    if (need >= 2 && wbyte(w, q + 2) - 0x80u > 0x3Fu) return fs_result(FS_REFUSED, 0, 0, 0);
+    if (need >= 3 && wbyte(w, q + 3) - 0x80u > 0x3Fu) return fs_result(FS_REFUSED, 0, 0, 0);
+    dec += need + 1; q += need + 1;
+  }
+}
+
+/* A string VALUE at f.p (opening quote): *pos = offset of the first content byte, *len = DECODED bytes,
+ * *esc = it holds backslash escapes (so raw and decoded bytes differ). Plain strings (printable ASCII, no
+ * backslash) are finished here, 8 bytes a step; the rest goes through fast_string_tail(). Refuses what it does not
+ * accept, but for the one failure it reports itself: the record ending inside the string. */
+PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len, uint32_t* esc) {
   uint32_t q = f.p + 1;
   for (;;) {
     const uint64_t m = swar_str_special(wpeek8(w, q));
@@ -151,14 +226,22 @@ PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len)
     if (q > f.limit) return false;
   }
   if (q >= f.limit) return false;
-  if (wbyte(w, q) != '"') {
-    /* a line feed inside a string of an LF-delimited record: the record's bytes end here */
-    if (wbyte(w, q) == '\n' && !f.lf_ws) return fast_fail(f, PJ_E_EOF, q);
-    return false;
+  uint32_t dec = q - (f.p + 1), any_esc = 0;
+  const uint32_t x = wbyte(w, q);
+  if (x != '"') {
+    if (x < 0x20) {
+      /* a line feed inside a string of an LF-delimited record: the record's bytes end here */
+      if (x == '\n' && !f.lf_ws) return fast_fail(f, PJ_E_EOF, q);
+      return false;
+    }
+    const uint64_t r = fast_string_tail(w.s, q, dec, f.limit, f.lf_ws);
+    const uint32_t status = (uint32_t)(r >> 60) & 3u;
+    if (status == FS_EOF) return fast_fail(f, PJ_E_EOF, (uint32_t)r);
+    if (status != FS_OK) return false;
+    q = (uint32_t)r; dec = (uint32_t)(r >> 32) & 0xFFFFFFu; any_esc = (uint32_t)(r >> 56) & 1u;
   }
-  const uint32_t n = q - (f.p + 1);
-  if (n > TAPE_MAX_STR || f.p + 1 > 0xFFFFu) return false;
-  *pos = f.p + 1; *len = n;
+  if (dec > TAPE_MAX_STR || f.p + 1 > 0xFFFFu) return false;
+  *pos = f.p + 1; *len = dec; *esc = any_esc;
   f.p = q + 1;
   return true;
 }
@@ -344,10 +427,42 @@ struct FVals {
 
 /* Where strings go: while tokenising, onto the tape (and into the counters). Arrays are indexed by
  * constant slot numbers only. */
-struct FSink {
+struct DrainState {
+  const DevCols* c;     /* null: nothing is emitted, the tape is only emptied (a counting pass that needs no tape) */
+  const uint32_t* base; /* the record's start in every arena / child table */
+  uint32_t cur[NSLOT];  /* bytes / items of the record emitted so far */
+};
+/* DR (a compile-time switch, so the first pass carries none of it): the record is tokenised a second time to be
+ * emitted, and the tape is emptied into the columns through d whenever it runs full (records whose strings and
+ * list elements outnumber the tape). */
+template <bool DR>
+struct FSinkT {
+  static constexpr bool drain = DR;
   Tape* t;
   uint32_t* cnt; /* [NSLOT] bytes / items counted so far */
+  DrainState* d;
 };
+/* Tape words one list element of flat object E can take: header, scalars, one string per string property. */
+template <int E, int I = 0>
+constexpr uint32_t string_fields() {
+  if constexpr (I >= CObj<E>::N) return 0;
+  else return (CObj<E>::f[I].kind == K_STR ? 1u : 0u) + string_fields<E, I + 1>();
+}
+enum { TAPE_MIN_CAP = 8 }; /* the largest unit pushed between two drain points is well below this */
+template <int OBJ, int I = 0>
+PJ_HD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32_t k, uint32_t word, const uint32_t* base, uint32_t* cur);
+/* replays what the tape holds into the columns and empties it (a call, not inlined: it is met at many places) */
+template <int OBJ>
+PJ_HD_NOINLINE void tape_drain(const Win& w, Tape& t, DrainState& d) {
+  if (d.c)
+    for (uint32_t k = 0; k < t.n;) k = replay_word<OBJ>(w, d.c, t, k, tape_get(t, k), d.base, d.cur);
+  t.n = 0;
+}
+/* In the emitting pass: make room for `need` more words. */
+template <int OBJ, class S>
+PJ_HD void tape_room(const Win& w, S& s, uint32_t need) {
+  if constexpr (S::drain) { if (s.t->n + need > s.t->cap) tape_drain<OBJ>(w, *s.t, *s.d); }
+}
 
 /* n bytes from window offset pos to dst (global memory): bytes up to 4-byte alignment of dst, then words */
 PJ_HD void copy_win(uint8_t* dst, const Win& w, uint32_t pos, uint32_t n) {
@@ -356,13 +471,63 @@ PJ_HD void copy_win(uint8_t* dst, const Win& w, uint32_t pos, uint32_t n) {
   while (n) { *dst++ = (uint8_t)wbyte(w, pos++); n--; }
 }
 
-/* Value of scalar property I of OBJ at f.p (kinds I64, I32, BOOL, STR, ENUM, DATETIME). null is left to
- * the generic parser. */
-template <int OBJ, int I>
-PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v) {
+/* n DECODED bytes of the string whose content starts at window offset pos, to dst. The string was accepted by
+ * fast_string(), so every escape in it is well formed. */
+PJ_HD_NOINLINE void copy_decoded(uint8_t* dst, const uint8_t* ws, uint32_t pos, uint32_t n) {
+  Win w;
+  w.s = ws; w.w0 = 0;
+  uint32_t k = 0;
+  while (k < n) {
+    const uint32_t x = wbyte(w, pos);
+    if (x != '\\') { dst[k++] = (uint8_t)x; pos++; continue; }
+    const uint32_t y = wbyte(w, pos + 1);
+    uint32_t cp;
+    pos += 2;
+    switch (y) {
+      case 'b': cp = 8; break;
+      case 'f': cp = 12; break;
+      case 'n': cp = 10; break;
+      case 'r': cp = 13; break;
+      case 't': cp = 9; break;
+      case 'u': {
+        cp = 0;
+        fast_hex4(w, pos, &cp);
+        pos += 4;
+        if (cp - 0xD800u < 0x400u) {
+          uint32_t lo = 0;
+          fast_hex4(w, pos + 2, &lo);
+          cp = 0x10000u + ((cp - 0xD800u) << 10) + (lo - 0xDC00u);
+          pos += 6;
+        }
+        break;
+      }
+      default: cp = y; break; /* '"', '\\', '/' */
+    }
+    if (cp < 0x80) dst[k++] = (uint8_t)cp;
+    else if (cp < 0x800) { dst[k++] = (uint8_t)(0xC0 | (cp >> 6)); dst[k++] = (uint8_t)(0x80 | (cp & 63)); }
+    else if (cp < 0x10000) { dst[k++] = (uint8_t)(0xE0 | (cp >> 12)); dst[k++] = (uint8_t)(0x80 | ((cp >> 6) & 63)); dst[k++] = (uint8_t)(0x80 | (cp & 63)); }
+    else { dst[k++] = (uint8_t)(0xF0 | (cp >> 18)); dst[k++] = (uint8_t)(0x80 | ((cp >> 12) & 63)); dst[k++] = (uint8_t)(0x80 | ((cp >> 6) & 63)); dst[k++] = (uint8_t)(0x80 | (cp & 63)); }
+  }
+}
+/* the string of one tape word to dst */
+PJ_HD void copy_tape_str(uint8_t* dst, const Win& w, uint32_t word) {
+  const uint32_t len = (word >> 4) & 0x7FFu, pos = word >> 16;
+  if (word & TAPE_ESC) copy_decoded(dst, w.s, pos, len); else copy_win(dst, w, pos, len);
+}
+
+/* the literal null at f.p */
+PJ_HD bool fast_null(const Win& w, FastState& f) {
+  if (wpeek4(w, f.p) != 0x6C6C756Eu || f.p + 4 > f.limit) return false;
+  f.p += 4;
+  return true;
+}
+/* Value of scalar property I of OBJ at f.p (kinds I64, I32, BOOL, STR, ENUM, DATETIME), or null. */
+template <int OBJ, int I, class S>
+PJ_HD bool fast_scalar(const Win& w, FastState& f, S& s, FVals& v) {
   constexpr uint32_t kind = FK<OBJ, I>::kind, slot = FK<OBJ, I>::cnt;
   if (v.present & (1u << I)) return false; /* repeated key */
   const uint32_t x = wbyte(w, f.p);
+  if (x == 'n') return fast_null(w, f); /* null: the property stays absent */
   if constexpr (kind == K_I64 || kind == K_I32) {
     int64_t val;
     if (!(x == '-' || x - '0' <= 9u)) return fast_wrong_type(f, x);
@@ -376,9 +541,9 @@ PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v) {
     else return false;
   } else if constexpr (kind == K_STR) {
     if (x != '"') return fast_wrong_type(f, x);
-    uint32_t pos, len;
-    if (!fast_string(w, f, &pos, &len)) return false;
-    tape_push(*s.t, tape_str(slot, len, pos));
+    uint32_t pos, len, esc;
+    if (!fast_string(w, f, &pos, &len, &esc)) return false;
+    tape_push(*s.t, tape_str(slot, len, pos, esc));
     s.cnt[slot] += len;
   } else if constexpr (kind == K_ENUM) {
     if (x != '"') return fast_wrong_type(f, x);
@@ -386,9 +551,9 @@ PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v) {
     uint32_t len; uint64_t lo, hi;
     if (!fast_short(w, f, &len, &lo, &hi)) {
       /* not a short plain string; a long plain one is a well-formed string that is no literal */
-      uint32_t pos;
-      if (fast_string(w, f, &pos, &len)) return fast_fail(f, PJ_E_ENUM, q);
-      return false;
+      uint32_t pos, esc;
+      if (fast_string(w, f, &pos, &len, &esc) && !esc) return fast_fail(f, PJ_E_ENUM, q);
+      return false; /* with escapes the decoded text decides: left to the generic parser */
     }
     const int e = match_enum<FK<OBJ, I>::child>(len, lo, hi);
     if (e < 0) return fast_fail(f, PJ_E_ENUM, q);
@@ -396,8 +561,8 @@ PJ_HD bool fast_scalar(const Win& w, FastState& f, FSink& s, FVals& v) {
   } else if constexpr (kind == K_DATETIME) {
     if (x != '"') return fast_wrong_type(f, x);
     const uint32_t q = f.p;
-    uint32_t pos, len;
-    if (!fast_string(w, f, &pos, &len)) return false;
+    uint32_t pos, len, esc;
+    if (!fast_string(w, f, &pos, &len, &esc) || esc) return false;
     int64_t ep; int32_t ns, of;
     if (!fast_datetime(w, pos, len, &ep, &ns, &of)) return fast_fail(f, PJ_E_DATETIME, q);
     v.v[I] = ep; v.aux = (int64_t)(((uint64_t)(uint32_t)ns << 32) | (uint32_t)of);
@@ -432,13 +597,13 @@ PJ_HD int fast_member_end(const Win& w, FastState& f) {
 }
 
 /* ---- flat objects (Category, Tag): scalar properties only ---------------------------------------- */
-template <int OBJ, int I>
-PJ_HD bool flat_value(const Win& w, FastState& f, FSink& s, FVals& v) {
+template <int OBJ, int I, class S>
+PJ_HD bool flat_value(const Win& w, FastState& f, S& s, FVals& v) {
   if constexpr (FK<OBJ, I>::kind <= K_ENUM) return fast_scalar<OBJ, I>(w, f, s, v);
   else return false;
 }
-template <int OBJ, int I = 0>
-PJ_HD bool flat_dispatch(int i, const Win& w, FastState& f, FSink& s, FVals& v) {
+template <int OBJ, int I = 0, class S>
+PJ_HD bool flat_dispatch(int i, const Win& w, FastState& f, S& s, FVals& v) {
   if constexpr (I >= CObj<OBJ>::N) return false;
   else {
     if (i == I) return flat_value<OBJ, I>(w, f, s, v);
@@ -447,8 +612,8 @@ PJ_HD bool flat_dispatch(int i, const Win& w, FastState& f, FSink& s, FVals& v) 
 }
 /* One pass over the properties in model order: every key spelled compactly and in order is matched with
  * one or two word compares. state: 1 = at a key, 2 = object closed, 0 = refuse. */
-template <int OBJ, int I = 0>
-PJ_HD int flat_inorder(const Win& w, FastState& f, FSink& s, FVals& v, int state) {
+template <int OBJ, int I = 0, class S>
+PJ_HD int flat_inorder(const Win& w, FastState& f, S& s, FVals& v, int state) {
   if constexpr (I >= CObj<OBJ>::N) return state;
   else {
     if (state == 1 && at_key<OBJ, I>(w, f)) {
@@ -460,8 +625,8 @@ PJ_HD int flat_inorder(const Win& w, FastState& f, FSink& s, FVals& v, int state
   }
 }
 /* Flat object at f.p == '{'. */
-template <int OBJ>
-PJ_HD bool fast_flat(const Win& w, FastState& f, FSink& s, FVals& v) {
+template <int OBJ, class S>
+PJ_HD bool fast_flat(const Win& w, FastState& f, S& s, FVals& v) {
   v.present = 0;
   f.p++;
   if (fast_ws(w, f) == '}') { f.p++; return true; }
@@ -492,13 +657,15 @@ PJ_HD void tape_put_scalars(Tape& t, uint32_t at, const FVals& v) {
 }
 
 /* Property I of a model root at f.p: scalars as above; an embedded object into cv; lists item by item. */
-template <int OBJ, int I>
-PJ_HD bool root_value(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv) {
+template <int OBJ, int I, class S>
+PJ_HD bool root_value(const Win& w, FastState& f, S& s, FVals& v, FVals& cv) {
   constexpr uint32_t kind = FK<OBJ, I>::kind, cnt = FK<OBJ, I>::cnt;
-  if constexpr (kind <= K_ENUM || kind == K_DATETIME) return fast_scalar<OBJ, I>(w, f, s, v);
+  if constexpr (kind <= K_ENUM || kind == K_DATETIME) { tape_room<OBJ>(w, s, 1); return fast_scalar<OBJ, I>(w, f, s, v); }
   else {
     if (v.present & (1u << I)) return false;
+    if (wbyte(w, f.p) == 'n') return fast_null(w, f); /* null: no object, no list */
     if constexpr (kind == K_OBJ) {
+      tape_room<OBJ>(w, s, string_fields<FK<OBJ, I>::child>());
       if (wbyte(w, f.p) != '{') return fast_wrong_type(f, wbyte(w, f.p));
       if (!fast_flat<FK<OBJ, I>::child>(w, f, s, cv)) return false;
     } else {
@@ -509,14 +676,17 @@ PJ_HD bool root_value(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv)
       else {
         for (;;) {
           if constexpr (kind == K_LIST_STR) {
+            tape_room<OBJ>(w, s, 1);
             if (wbyte(w, f.p) != '"') return fast_wrong_type(f, wbyte(w, f.p));
-            uint32_t pos, len;
-            if (!fast_string(w, f, &pos, &len)) return false;
-            tape_push(*s.t, tape_str(cnt + 1, len, pos));
+            uint32_t pos, len, esc;
+            if (!fast_string(w, f, &pos, &len, &esc)) return false;
+            tape_push(*s.t, tape_str(cnt + 1, len, pos, esc));
             s.cnt[cnt + 1] += len;
           } else {
             /* header word, room for the scalars, then the element's strings as they are met */
             constexpr int E = FK<OBJ, I>::child;
+            static_assert(1 + scalar_words<E>() + string_fields<E>() <= TAPE_MIN_CAP, "a list element fits an empty tape");
+            tape_room<OBJ>(w, s, 1 + scalar_words<E>() + string_fields<E>());
             if (wbyte(w, f.p) != '{') return fast_wrong_type(f, wbyte(w, f.p));
             const uint32_t at = s.t->n;
             for (uint32_t k = 0; k < 1 + scalar_words<E>(); ++k) tape_push(*s.t, 0);
@@ -538,16 +708,16 @@ PJ_HD bool root_value(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv)
     return true;
   }
 }
-template <int OBJ, int I = 0>
-PJ_HD bool root_dispatch(int i, const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv) {
+template <int OBJ, int I = 0, class S>
+PJ_HD bool root_dispatch(int i, const Win& w, FastState& f, S& s, FVals& v, FVals& cv) {
   if constexpr (I >= CObj<OBJ>::N) return false;
   else {
     if (i == I) return root_value<OBJ, I>(w, f, s, v, cv);
     return root_dispatch<OBJ, I + 1>(i, w, f, s, v, cv);
   }
 }
-template <int OBJ, int I = 0>
-PJ_HD int root_inorder(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv, int state) {
+template <int OBJ, int I = 0, class S>
+PJ_HD int root_inorder(const Win& w, FastState& f, S& s, FVals& v, FVals& cv, int state) {
   if constexpr (I >= CObj<OBJ>::N) return state;
   else {
     if (state == 1 && at_key<OBJ, I>(w, f)) {
@@ -560,8 +730,8 @@ PJ_HD int root_inorder(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv
 }
 /* Members of a model root. f.p is after `{ ws*`, or at the value of property `pending` (>= 0) whose key
  * was read already. Ends after the closing brace. */
-template <int OBJ>
-PJ_HD bool fast_root(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv, int pending) {
+template <int OBJ, class S>
+PJ_HD bool fast_root(const Win& w, FastState& f, S& s, FVals& v, FVals& cv, int pending) {
   int state = 1;
   if (pending >= 0) {
     if (!root_dispatch<OBJ>(pending, w, f, s, v, cv)) return false;
@@ -579,12 +749,14 @@ PJ_HD bool fast_root(const Win& w, FastState& f, FSink& s, FVals& v, FVals& cv, 
 template <int SCHEMA> struct RootOf { static constexpr int obj = SCHEMA == PJ_SCHEMA_PET ? (int)OBJ_PET : (SCHEMA == PJ_SCHEMA_ORDER ? (int)OBJ_ORDER : (int)OBJ_USER); };
 
 enum { FAST_REFUSED = 0, FAST_ACCEPTED = 1, FAST_FAILED = 2 };
-template <int SCHEMA>
-PJ_HD bool fast_record_body(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, uint32_t* cnt, Tape& t);
+template <int SCHEMA, bool DR>
+PJ_HD bool fast_record_body(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, uint32_t* cnt, Tape& t, DrainState* d);
 
 /* One record at window offset `start`, ending before window offset `limit`.
  * FAST_ACCEPTED: model in *type_out, root values in v, the embedded object's in cv, counts in cnt[slot]
- *                (all NSLOT entries are reset), strings and list elements on the tape.
+ *                (all NSLOT entries are reset), strings and list elements on the tape. If t.n > t.cap
+ *                afterwards the tape was too small to hold them all: such a record is emitted with
+ *                fast_outline<>(), which tokenises it once more.
  * FAST_FAILED:   the record fails validation with *err_kind at window offset *err_pos, exactly as the
  *                generic parser reports it.
  * FAST_REFUSED:  the generic parser has to look at the record. */
@@ -593,20 +765,20 @@ PJ_HD uint32_t fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_
                            FVals& v, FVals& cv, uint32_t* cnt, Tape& t, uint32_t* err_kind, uint32_t* err_pos) {
   FastState f;
   f.p = start; f.limit = limit; f.lf_ws = lf_ws; f.err = 0; f.err_pos = 0;
-  if (fast_record_body<SCHEMA>(w, f, open_end, type_out, v, cv, cnt, t)) return FAST_ACCEPTED;
+  if (fast_record_body<SCHEMA, false>(w, f, open_end, type_out, v, cv, cnt, t, nullptr)) return FAST_ACCEPTED;
   if (!f.err) return FAST_REFUSED;
   *err_kind = f.err; *err_pos = f.err_pos;
   return FAST_FAILED;
 }
-template <int SCHEMA>
-PJ_HD bool fast_record_body(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, uint32_t* cnt, Tape& t) {
+template <int SCHEMA, bool DR>
+PJ_HD bool fast_record_body(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, uint32_t* cnt, Tape& t, DrainState* d) {
   const uint32_t limit = f.limit, lf_ws = f.lf_ws;
 #pragma unroll
   for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = 0;
   t.n = 0;
   v.present = 0; cv.present = 0;
-  FSink s;
-  s.t = &t; s.cnt = cnt;
+  FSinkT<DR> s;
+  s.t = &t; s.cnt = cnt; s.d = d;
   if (fast_ws(w, f) != '{' || f.p >= limit) return false;
   f.p++;
   fast_ws(w, f);
@@ -655,7 +827,6 @@ PJ_HD bool fast_record_body(const Win& w, FastState& f, uint32_t open_end, uint3
   if (f.p > limit) return false;
   if (f.p < limit) { if (lf_ws || x != '\n') return false; }
   else if (open_end) return false;
-  if (t.n > t.cap) return false;
   if constexpr (SCHEMA == PJ_SCHEMA_MIXED) {
     if (type == PJ_TYPE_PET) cnt[SLOT_ROWS_PET] = 1; else if (type == PJ_TYPE_ORDER) cnt[SLOT_ROWS_ORD] = 1; else cnt[SLOT_ROWS_USR] = 1;
   }
@@ -705,37 +876,37 @@ PJ_HD void tape_get_scalars(const Tape& t, uint32_t at, FVals& v) {
 }
 /* a string word that belongs to a flat object CH (embedded object or list element): copy it to its arena */
 template <int CH, int I = 0>
-PJ_HD bool replay_flat_string(const Win& w, const DevCols* c, uint32_t slot, uint32_t len, uint32_t pos, const uint32_t* base, uint32_t* cur) {
+PJ_HD bool replay_flat_string(const Win& w, const DevCols* c, uint32_t word, const uint32_t* base, uint32_t* cur) {
   if constexpr (I >= CObj<CH>::N) return false;
   else {
     if constexpr (FK<CH, I>::kind == K_STR) {
       constexpr uint32_t cnt = FK<CH, I>::cnt;
-      if (slot == cnt) { copy_win(colp<uint8_t>(c, FK<CH, I>::col + 1) + base[cnt] + cur[cnt], w, pos, len); cur[cnt] += len; return true; }
+      if ((word & 15u) == cnt) { copy_tape_str(colp<uint8_t>(c, FK<CH, I>::col + 1) + base[cnt] + cur[cnt], w, word); cur[cnt] += (word >> 4) & 0x7FFu; return true; }
     }
-    return replay_flat_string<CH, I + 1>(w, c, slot, len, pos, base, cur);
+    return replay_flat_string<CH, I + 1>(w, c, word, base, cur);
   }
 }
 
 /* One tape word of a record whose root is OBJ (k = its index; returns the index of the next word): finds
  * the property it belongs to by an unrolled chain over the properties and emits it. cur[] holds, per slot,
  * the bytes (byte slots) or items (item slots) emitted so far. */
-template <int OBJ, int I = 0>
+template <int OBJ, int I>
 PJ_HD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32_t k, uint32_t word, const uint32_t* base, uint32_t* cur) {
   if constexpr (I >= CObj<OBJ>::N) return k + 1;
   else {
     constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col, cnt = FK<OBJ, I>::cnt;
-    const uint32_t slot = word & 15u, len = (word >> 4) & 0xFFFu, pos = word >> 16;
+    const uint32_t slot = word & 15u, len = (word >> 4) & 0x7FFu;
     if constexpr (kind == K_STR) {
-      if (slot == cnt) { copy_win(colp<uint8_t>(c, col + 1) + base[cnt] + cur[cnt], w, pos, len); cur[cnt] += len; return k + 1; }
+      if (slot == cnt) { copy_tape_str(colp<uint8_t>(c, col + 1) + base[cnt] + cur[cnt], w, word); cur[cnt] += len; return k + 1; }
     } else if constexpr (kind == K_LIST_STR) {
       if (slot == cnt + 1) {
         colp<uint32_t>(c, col + 1)[(uint64_t)base[cnt] + cur[cnt]] = base[cnt + 1] + cur[cnt + 1];
-        copy_win(colp<uint8_t>(c, col + 2) + base[cnt + 1] + cur[cnt + 1], w, pos, len);
+        copy_tape_str(colp<uint8_t>(c, col + 2) + base[cnt + 1] + cur[cnt + 1], w, word);
         cur[cnt + 1] += len; cur[cnt] += 1;
         return k + 1;
       }
     } else if constexpr (kind == K_OBJ) {
-      if (replay_flat_string<FK<OBJ, I>::child>(w, c, slot, len, pos, base, cur)) return k + 1;
+      if (replay_flat_string<FK<OBJ, I>::child>(w, c, word, base, cur)) return k + 1;
     } else if constexpr (kind == K_LIST_OBJ) {
       constexpr int E = FK<OBJ, I>::child;
       if (slot == TAPE_ELEM && (word >> 12 & 15u) == cnt) {
@@ -748,7 +919,7 @@ PJ_HD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32
         store_vals<E, true>(c, ev, erow, base);
         return k + 1 + scalar_words<E>();
       }
-      if (slot != TAPE_ELEM && replay_flat_string<E>(w, c, slot, len, pos, base, cur)) return k + 1;
+      if (slot != TAPE_ELEM && replay_flat_string<E>(w, c, word, base, cur)) return k + 1;
     }
     return replay_word<OBJ, I + 1>(w, c, t, k, word, base, cur);
   }
@@ -767,27 +938,64 @@ PJ_HD void store_embedded(const DevCols* c, const FVals& v, const FVals& cv, uin
   }
 }
 
+/* cur[]: bytes / items of the record already emitted per slot (zeros, unless the tape was emptied on the way) */
 template <int OBJ>
-PJ_HD void emit_root(const Win& w, const DevCols* c, const FVals& v, const FVals& cv, const Tape& t, uint64_t row, const uint32_t* base) {
+PJ_HD void emit_root(const Win& w, const DevCols* c, const FVals& v, const FVals& cv, const Tape& t, uint64_t row, const uint32_t* base, uint32_t* cur) {
   store_vals<OBJ, false>(c, v, row, base);
   store_embedded<OBJ>(c, v, cv, row, base);
-  uint32_t cur[NSLOT];
-#pragma unroll
-  for (uint32_t k = 0; k < NSLOT; ++k) cur[k] = 0;
   for (uint32_t k = 0; k < t.n;) k = replay_word<OBJ>(w, c, t, k, tape_get(t, k), base, cur);
 }
+template <int SCHEMA>
+PJ_HD void emit_typed(const Win& w, const DevCols* c, uint32_t type, const FVals& v, const FVals& cv, const Tape& t, const uint32_t* base,
+                      uint64_t rec_index, uint32_t* cur) {
+  if constexpr (SCHEMA != PJ_SCHEMA_MIXED) emit_root<RootOf<SCHEMA>::obj>(w, c, v, cv, t, rec_index, base, cur);
+  else {
+    if (type == PJ_TYPE_PET) emit_root<OBJ_PET>(w, c, v, cv, t, base[SLOT_ROWS_PET], base, cur);
+    else if (type == PJ_TYPE_ORDER) emit_root<OBJ_ORDER>(w, c, v, cv, t, base[SLOT_ROWS_ORD], base, cur);
+    else emit_root<OBJ_USER>(w, c, v, cv, t, base[SLOT_ROWS_USR], base, cur);
+  }
+}
 
-/* Replays a record accepted by fast_record<SCHEMA>(): every column of its row, then the tape.
- * base[slot] = the record's start in every arena / child table. */
+/* Replays a record accepted by fast_record<SCHEMA>() whose strings and list elements all fit the tape (t.n <= t.cap):
+ * every column of its row, then the tape. base[slot] = the record's start in every arena / child table. */
 template <int SCHEMA>
 PJ_HD void fast_emit(const Win& w, const DevCols* c, uint32_t type, const FVals& v, const FVals& cv, const Tape& t, const uint32_t* base,
                      uint64_t rec_index) {
-  if constexpr (SCHEMA != PJ_SCHEMA_MIXED) emit_root<RootOf<SCHEMA>::obj>(w, c, v, cv, t, rec_index, base);
-  else {
-    if (type == PJ_TYPE_PET) emit_root<OBJ_PET>(w, c, v, cv, t, base[SLOT_ROWS_PET], base);
-    else if (type == PJ_TYPE_ORDER) emit_root<OBJ_ORDER>(w, c, v, cv, t, base[SLOT_ROWS_ORD], base);
-    else emit_root<OBJ_USER>(w, c, v, cv, t, base[SLOT_ROWS_USR], base);
+  uint32_t cur[NSLOT];
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) cur[k] = 0;
+  emit_typed<SCHEMA>(w, c, type, v, cv, t, base, rec_index, cur);
+}
+/* The out-of-line form of the tokeniser, for the records the inlined first pass does not finish alone:
+ *  - c != null: emits a record that fast_record<SCHEMA>() (or a counting call of this function) accepted and whose
+ *    strings and list elements outnumber the tape: it is tokenised again, and this time the tape (at least
+ *    TAPE_MIN_CAP words) is emptied into the columns whenever the next unit would not fit;
+ *  - c == null: the counting pass for a record that is read where it lies instead of from the staged window (w then
+ *    points into global memory): verdict as fast_record<>(), counts in cnt_out[NSLOT], nothing is kept on the tape.
+ * Arguments are passed by value so that the caller's copies stay in registers. */
+template <int SCHEMA>
+PJ_HD_NOINLINE uint32_t fast_outline(const Win w, uint32_t start, uint32_t limit, uint32_t lf_ws, uint32_t open_end, const DevCols* c,
+                                     const uint32_t* base, uint64_t rec_index, Tape t, uint32_t* cnt_out, uint32_t* type_out,
+                                     uint32_t* err_kind, uint32_t* err_pos) {
+  FastState f;
+  f.p = start; f.limit = limit; f.lf_ws = lf_ws; f.err = 0; f.err_pos = 0;
+  DrainState d;
+  d.c = c; d.base = base;
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) d.cur[k] = 0;
+  FVals v, cv;
+  uint32_t cnt[NSLOT], type = PJ_TYPE_NONE;
+  if (!fast_record_body<SCHEMA, true>(w, f, open_end, &type, v, cv, cnt, t, &d)) {
+    if (!f.err) return FAST_REFUSED;
+    *err_kind = f.err; *err_pos = f.err_pos;
+    return FAST_FAILED;
   }
+  if (c) emit_typed<SCHEMA>(w, c, type, v, cv, t, base, rec_index, d.cur);
+  else {
+    for (uint32_t k = 0; k < NSLOT; ++k) cnt_out[k] = cnt[k];
+    *type_out = type;
+  }
+  return FAST_ACCEPTED;
 }
 
 }  // namespace pj

@@ -24,7 +24,8 @@
 
 namespace pj {
 
-__constant__ Schema c_schema;
+/* one copy per translation unit that includes this header (each sets its own, see tile_init_*) */
+static __constant__ Schema c_schema;
 
 /* Written by the kernels, read back by the host once per call. */
 struct DevResult {
@@ -256,7 +257,7 @@ struct ParseArgs {
 static constexpr int PARSE_THREADS = 128;
 
 /* Size pass: one record per thread. */
-__global__ void __launch_bounds__(PARSE_THREADS) k_parse_size(const __grid_constant__ ParseArgs a) {
+static __global__ void __launch_bounds__(PARSE_THREADS) k_parse_size(const __grid_constant__ ParseArgs a) {
   const uint64_t n = min((uint64_t)a.res->n_records, a.cap_records);
   const uint64_t* rec_start = colp<uint64_t>(&a.cols, PJ_COL_REC_START);
   uint32_t nerr = 0;
@@ -284,7 +285,7 @@ __global__ void __launch_bounds__(PARSE_THREADS) k_parse_size(const __grid_const
 }
 
 /* Emit pass. */
-__global__ void __launch_bounds__(PARSE_THREADS) k_parse_emit(const __grid_constant__ ParseArgs a) {
+static __global__ void __launch_bounds__(PARSE_THREADS) k_parse_emit(const __grid_constant__ ParseArgs a) {
   if (!a.res->ok) return;
   const uint64_t n = (uint64_t)a.res->n_records;
   const uint64_t* rec_start = colp<uint64_t>(&a.cols, PJ_COL_REC_START);
@@ -322,7 +323,7 @@ struct FinalizeArgs {
   DevResult* res;
   DevCols cols;
 };
-__global__ void k_check(const __grid_constant__ FinalizeArgs a) {
+static __global__ void k_check(const __grid_constant__ FinalizeArgs a) {
   if (threadIdx.x || blockIdx.x) return;
   uint64_t n = a.res->n_records;
   uint32_t ok = n <= a.cap_records;
@@ -333,7 +334,7 @@ __global__ void k_check(const __grid_constant__ FinalizeArgs a) {
   }
   a.res->ok = ok;
 }
-__global__ void k_finalize(const __grid_constant__ FinalizeArgs a) {
+static __global__ void k_finalize(const __grid_constant__ FinalizeArgs a) {
   if (!a.res->ok) return;
   uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
   if (k >= a.plan.n) return;
@@ -354,7 +355,7 @@ struct WriteArgs {
   DevResult* res;
   DevCols cols;
 };
-__global__ void __launch_bounds__(PARSE_THREADS) k_write_size(const __grid_constant__ WriteArgs a) {
+static __global__ void __launch_bounds__(PARSE_THREADS) k_write_size(const __grid_constant__ WriteArgs a) {
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
     uint32_t type; uint64_t row;
     uint64_t len = 0;
@@ -366,7 +367,7 @@ __global__ void __launch_bounds__(PARSE_THREADS) k_write_size(const __grid_const
     a.off[i] = len;
   }
 }
-__global__ void k_write_check(const __grid_constant__ WriteArgs a) {
+static __global__ void k_write_check(const __grid_constant__ WriteArgs a) {
   if (threadIdx.x || blockIdx.x) return;
   uint64_t body = a.res->out_bytes; /* sum of the record lengths, set by the scan */
   uint64_t total = a.array ? (body ? body + 1 : 2) : body;
@@ -374,7 +375,7 @@ __global__ void k_write_check(const __grid_constant__ WriteArgs a) {
   a.res->ok = total <= a.cap;
   if (a.array && total <= a.cap) { a.out[0] = '['; if (!body) a.out[1] = ']'; }
 }
-__global__ void __launch_bounds__(PARSE_THREADS) k_write_emit(const __grid_constant__ WriteArgs a) {
+static __global__ void __launch_bounds__(PARSE_THREADS) k_write_emit(const __grid_constant__ WriteArgs a) {
   if (!a.res->ok) return;
   const uint64_t total = a.res->out_bytes;
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -572,8 +573,17 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
 
   const long long c1 = clock64();
   /* ---- tokenise every record once ------------------------------------------------------------------ */
+  /* A record that is not (wholly) in the window is read where it lies: the same word-at-a-time code, on global
+     memory through L1. It looks up to 16 bytes ahead, so the last bytes of the input are left to the generic parser. */
+  const bool direct = active && !fits && my_end + 32 <= a.limit;
   Win w;
   w.s = win; w.w0 = w0;
+  Win wd = w; /* the view of a record read where it lies */
+  if (direct) {
+    const uint32_t mis4 = (uint32_t)(reinterpret_cast<uintptr_t>(a.in + start) & 3u);
+    wd.s = a.in + start - mis4; wd.w0 = (int64_t)start - mis4;
+  }
+  uint32_t start32 = 0, lim32 = 0;
   Tape tp;
   tp.e = tape + tid; tp.stride = TILE_THREADS; tp.cap = a.tape_cap; tp.n = 0;
   uint32_t cnt[NSLOT], base[NSLOT];
@@ -583,12 +593,20 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
   uint32_t type = PJ_TYPE_NONE, err = 0, fast = 0, verdict = FAST_REFUSED;
   if (active) {
     const bool blank = a.rec_blank && a.rec_blank[i];
-    if (fits && !blank) {
-      const uint64_t rel = (uint64_t)((int64_t)my_limit - w0);
-      const uint32_t lim32 = rel > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)rel;
-      const uint32_t start32 = (uint32_t)((int64_t)start - w0);
+    if ((fits || direct) && !blank) {
+      const uint64_t rel = (uint64_t)((int64_t)my_limit - wd.w0);
+      lim32 = rel > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)rel;
+      start32 = (uint32_t)((int64_t)start - wd.w0);
       uint32_t fpos = 0;
-      verdict = fast_record<SCHEMA>(w, start32, lim32, a.lf_ws, a.open_end, &type, v, cv, cnt, tp, &err, &fpos);
+      if (!direct) verdict = fast_record<SCHEMA>(w, start32, lim32, a.lf_ws, a.open_end, &type, v, cv, cnt, tp, &err, &fpos);
+      else {
+        /* out of line, and without a tape: what it accepts is tokenised again when it is emitted */
+        uint32_t cnt_d[NSLOT], type_d = PJ_TYPE_NONE, err_d = 0;
+        verdict = fast_outline<SCHEMA>(wd, start32, lim32, a.lf_ws, a.open_end, nullptr, nullptr, i, tp, cnt_d, &type_d, &err_d, &fpos);
+        type = type_d; err = err_d;
+#pragma unroll
+        for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = cnt_d[k];
+      }
       fast = verdict == FAST_ACCEPTED;
       if (verdict == FAST_FAILED) {
         /* a validation failure found by the word-at-a-time path: no row values, no bytes anywhere */
@@ -679,8 +697,16 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
       const uint32_t row = type == PJ_TYPE_PET ? base[SLOT_ROWS_PET] : (type == PJ_TYPE_ORDER ? base[SLOT_ROWS_ORD] : base[SLOT_ROWS_USR]);
       colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = type == PJ_TYPE_NONE ? 0xFFFFFFFFu : row;
     }
-    if (fast) fast_emit<SCHEMA>(w, &a.cols, type, v, cv, tp, base, i);
-    else {
+    if (fast) {
+      if (!direct && tp.n <= tp.cap) fast_emit<SCHEMA>(w, &a.cols, type, v, cv, tp, base, i);
+      else {
+        /* an out-of-line call: it gets a copy of the bases, so that base[] itself can stay in registers */
+        uint32_t base_copy[NSLOT], t_d, e_d, p_d;
+#pragma unroll
+        for (uint32_t k = 0; k < NSLOT; ++k) base_copy[k] = base[k];
+        fast_outline<SCHEMA>(direct ? wd : w, start32, lim32, a.lf_ws, a.open_end, &a.cols, base_copy, i, tp, nullptr, &t_d, &e_d, &p_d);
+      }
+    } else {
       Out<true> o;
       o.cols = &a.cols;
 #pragma unroll
@@ -782,7 +808,7 @@ __device__ __forceinline__ uint32_t word_needs_escape(uint32_t x) {
   const uint32_t xq = x ^ 0x22222222u, xb = x ^ 0x5C5C5C5Cu;
   return (((x - 0x20202020u) & ~x) | ((xq - 0x01010101u) & ~xq) | ((xb - 0x01010101u) & ~xb)) & 0x80808080u;
 }
-__global__ void __launch_bounds__(256) k_arena_flags(const __grid_constant__ ArenaArgs a) {
+static __global__ void __launch_bounds__(256) k_arena_flags(const __grid_constant__ ArenaArgs a) {
   const uint64_t gtid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, gsize = (uint64_t)gridDim.x * blockDim.x;
   uint32_t any = 0;
   for (uint32_t r = 0; r < a.count; ++r) {
@@ -802,7 +828,7 @@ __global__ void __launch_bounds__(256) k_arena_flags(const __grid_constant__ Are
   if (__syncthreads_or((int)any) && threadIdx.x == 0) a.res->needs_escape = 1u;
 }
 
-__global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_constant__ WTileArgs a) {
+static __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_constant__ WTileArgs a) {
   constexpr uint32_t NWARPS = TILE_THREADS / 32;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ uint32_t sh_warp[NWARPS];
@@ -889,7 +915,7 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_con
   }
 }
 /* closes the text: brackets of array framing, the total, the verdict */
-__global__ void k_write_close(const __grid_constant__ WriteArgs a) {
+static __global__ void k_write_close(const __grid_constant__ WriteArgs a) {
   if (threadIdx.x || blockIdx.x) return;
   const uint64_t body = a.res->out_bytes;
   const uint64_t total = a.array ? (body ? body + 1 : 2) : body;
