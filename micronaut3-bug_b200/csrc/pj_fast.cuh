@@ -453,15 +453,14 @@ template <int OBJ, int I = 0>
 PJ_HD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32_t k, uint32_t word, const uint32_t* base, uint32_t* cur);
 /* replays what the tape holds into the columns and empties it (a call, not inlined: it is met at many places) */
 template <int OBJ>
-PJ_HD_NOINLINE void tape_drain(const Win& w, Tape& t, DrainState& d) {
-  if (d.c)
-    for (uint32_t k = 0; k < t.n;) k = replay_word<OBJ>(w, d.c, t, k, tape_get(t, k), d.base, d.cur);
-  t.n = 0;
+PJ_HD_NOINLINE void tape_drain(const Win w, const Tape t, DrainState* d) { /* by value: the caller's tape stays in registers */
+  if (d->c)
+    for (uint32_t k = 0; k < t.n;) k = replay_word<OBJ>(w, d->c, t, k, tape_get(t, k), d->base, d->cur);
 }
 /* In the emitting pass: make room for `need` more words. */
 template <int OBJ, class S>
 PJ_HD void tape_room(const Win& w, S& s, uint32_t need) {
-  if constexpr (S::drain) { if (s.t->n + need > s.t->cap) tape_drain<OBJ>(w, *s.t, *s.d); }
+  if constexpr (S::drain) { if (s.t->n + need > s.t->cap) { tape_drain<OBJ>(w, *s.t, s.d); s.t->n = 0; } }
 }
 
 /* n bytes from window offset pos to dst (global memory): bytes up to 4-byte alignment of dst, then words */
