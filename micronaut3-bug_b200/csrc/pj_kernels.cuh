@@ -507,6 +507,41 @@ __device__ __forceinline__ bool tile_lookback(const TileArgs& a, uint32_t tile, 
   return true;
 }
 
+/* ---- bulk asynchronous copy (TMA, untiled form) global -> shared, completion on an mbarrier ------------ */
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+/* dst and src 16-byte aligned, bytes a multiple of 16; no multicast: the copy lands in this block's own shared memory */
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)), "l"(src),
+               "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+/* bounded: false when the copy has not landed after PJ_SPIN_LIMIT_NS */
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (global_ns() - t0 > PJ_SPIN_LIMIT_NS) return false;
+    __nanosleep(64);
+  }
+}
+
 template <int SCHEMA> struct SlotRange {
   static constexpr uint32_t lo = SCHEMA == PJ_SCHEMA_PET ? (uint32_t)SLOT_PET_CAT_NAME : (SCHEMA == PJ_SCHEMA_USER ? (uint32_t)SLOT_USR_STR0 : 0u);
   static constexpr uint32_t hi = SCHEMA == PJ_SCHEMA_PET ? (uint32_t)SLOT_USR_STR0 : (SCHEMA == PJ_SCHEMA_ORDER ? 0u : (uint32_t)NSLOT);
@@ -520,11 +555,12 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
   __shared__ uint32_t sh_warp[NSLOT][NWARPS];
   __shared__ uint32_t sh_tot[NSLOT], sh_base[NSLOT];
   __shared__ uint32_t sh_tile, sh_ok;
+  __shared__ __align__(8) unsigned long long sh_mbar; /* completion of the bulk copy that stages the window */
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* win = smem;
   uint32_t* tape = reinterpret_cast<uint32_t*>(smem + ((a.win_bytes + 64 + 15) & ~15u));
 
-  if (tid == 0) sh_tile = atomicAdd(a.ticket, 1u);
+  if (tid == 0) { sh_tile = atomicAdd(a.ticket, 1u); mbar_init(&sh_mbar, 1); }
   __syncthreads();
   const uint32_t tile = sh_tile;
   if (tile >= a.ntiles) return;
@@ -544,6 +580,7 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
      are in it (for the last record of the input that means: the window reaches the end of the input). */
   int64_t w0 = 0;
   uint64_t win_hi = 0; /* input offset of the first byte that is not staged */
+  int stage_failed = 0;
   if (nrec) {
     const uint64_t span_lo = rec_start[r0] - a.goff;
     uint64_t span_hi;
@@ -554,15 +591,19 @@ __global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_con
     const uint64_t need_hi = a.limit < span_hi + 32 ? a.limit : span_hi + 32;
     const uint64_t cap_hi = (uint64_t)(w0 + (int64_t)a.win_bytes - 64);
     win_hi = need_hi < cap_hi ? need_hi : cap_hi;
-    const uint64_t nbytes = (uint64_t)((int64_t)win_hi - w0);
-    const uint4* src = reinterpret_cast<const uint4*>(a.in + w0);
-    uint4* dst = reinterpret_cast<uint4*>(win);
-    const uint32_t n16 = (uint32_t)((nbytes + 15) >> 4);
-    for (uint32_t k = tid; k < n16; k += TILE_THREADS) dst[k] = __ldg(src + k);
-    __syncthreads();
+    const uint32_t nbytes = (uint32_t)((int64_t)win_hi - w0);
+    /* One bulk copy (cp.async.bulk, the untiled TMA form) brings the whole 16-byte multiples; the threads add the
+       last odd bytes and the line-feed padding, which lie behind the bulk region, and then wait for the copy. */
+    const uint32_t nb16 = nbytes & ~15u;
+    if (tid == 0 && nb16) { mbar_expect_tx(&sh_mbar, nb16); bulk_g2s(win, a.in + w0, nb16, &sh_mbar); }
+    if (tid < nbytes - nb16) win[nb16 + tid] = a.in[w0 + (int64_t)(nb16 + tid)];
     if (tid < 32) win[nbytes + tid] = '\n';
+    stage_failed = nb16 && !mbar_wait_bounded(&sh_mbar, 0);
   }
-  __syncthreads();
+  if (__syncthreads_or(stage_failed)) { /* the whole block leaves together */
+    if (tid == 0) atomicExch(&a.res->timeout, 1u);
+    return;
+  }
   uint64_t my_end = !active ? 0 : (a.rec_end ? a.rec_end[i] : (i + 1 < N ? rec_start[i + 1] - a.goff : a.limit));
   if (active && !a.rec_end && i + 1 == N && my_end > win_hi && start < win_hi) {
     /* the last record of a shard with slack: it ends at its LF, which may well be staged */
