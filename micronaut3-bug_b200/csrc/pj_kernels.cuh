@@ -542,6 +542,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint3
   }
 }
 
+/* bulk asynchronous copy shared -> global (same alignment rules); the issuing thread waits until shared memory
+ * has been read before the block may leave */
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_addr(src)), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_s2g_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+/* makes this thread's earlier writes to shared memory visible to the asynchronous proxy (the bulk copy engine) */
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 template <int SCHEMA> struct SlotRange {
   static constexpr uint32_t lo = SCHEMA == PJ_SCHEMA_PET ? (uint32_t)SLOT_PET_CAT_NAME : (SCHEMA == PJ_SCHEMA_USER ? (uint32_t)SLOT_USR_STR0 : 0u);
   static constexpr uint32_t hi = SCHEMA == PJ_SCHEMA_PET ? (uint32_t)SLOT_USR_STR0 : (SCHEMA == PJ_SCHEMA_ORDER ? 0u : (uint32_t)NSLOT);
@@ -931,15 +941,20 @@ static __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __g
       if (plain) fwrite_record<true, true>(&a.w.cols, type, row, a.w.inclusion, w); else fwrite_record<true, false>(&a.w.cols, type, row, a.w.inclusion, w);
       smem[pad + loc + w.n] = sep;
     }
+    fence_async_smem();
     __syncthreads();
     c3 = clock64();
+    /* the 16-byte multiples in the middle leave with one bulk copy (cp.async.bulk shared -> global), the odd
+       bytes at both ends with plain stores */
     uint8_t* gbase = dst0 - pad;
     const uint32_t end = pad + tile_total;
-    const uint32_t nchunks = (end + 15) >> 4;
-    for (uint32_t k = tid; k < nchunks; k += TILE_THREADS) {
-      const uint32_t lo = k << 4, hi = lo + 16;
-      if (lo >= pad && hi <= end) *reinterpret_cast<uint4*>(gbase + lo) = *reinterpret_cast<const uint4*>(smem + lo);
-      else for (uint32_t b = lo < pad ? pad : lo; b < (hi < end ? hi : end); ++b) gbase[b] = smem[b];
+    const uint32_t lo16 = (pad + 15u) & ~15u, hi16 = end & ~15u;
+    if (hi16 > lo16) {
+      if (tid == 0) { bulk_s2g(gbase + lo16, smem + lo16, hi16 - lo16); bulk_s2g_wait_read(); }
+      if (tid >= 32 && tid < 32 + (lo16 - pad)) gbase[pad + tid - 32] = smem[pad + tid - 32];
+      if (tid >= 64 && tid < 64 + (end - hi16)) gbase[hi16 + tid - 64] = smem[hi16 + tid - 64];
+    } else {
+      for (uint32_t b = pad + tid; b < end; b += TILE_THREADS) gbase[b] = smem[b];
     }
   } else if (located) {
     WOut w; w.dst = dst0 + loc; w.n = 0;
