@@ -558,7 +558,7 @@ template <int SCHEMA> struct SlotRange {
 };
 
 template <int SCHEMA>
-__global__ void __launch_bounds__(TILE_THREADS, 4) k_parse_tile(const __grid_constant__ TileArgs a) {
+__global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 4) k_parse_tile(const __grid_constant__ TileArgs a) {
   constexpr uint32_t LO = SlotRange<SCHEMA>::lo, HI = SlotRange<SCHEMA>::hi;
   constexpr uint32_t NWARPS = TILE_THREADS / 32;
   extern __shared__ __align__(16) uint8_t smem[];
