@@ -171,7 +171,7 @@ def run_reference(args, pj, abi):
                                    "CPU restatement in C (oracle/), not the JVM reference, which cannot run on this box"},
         "e2e": {"value": rps, "unit": "records/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    _emit_line(line)
 
 
 def main():
@@ -398,10 +398,28 @@ def main():
                                 "single_thread_records_per_s": n1 / dt1,
                                 "sample": f"{sample} Pet records ({sample_text.size / 1e6:.1f} MB) x {reps} passes, {threads} LF-aligned ranges, one thread each; "
                                           "CPU restatement in C (oracle/), not the JVM reference, which cannot run on this box"}
-    print(json.dumps(line), flush=True)
+    _emit_line(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+def _emit_line(line: dict) -> None:
+    """The one JSON line, written to the process's original stdout (see _quiet_stdout)."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = 1
+
+
+def _quiet_stdout() -> None:
+    """Native libraries (NCCL's version banner, for one) print to file descriptor 1. The contract is ONE JSON line on
+    stdout, so descriptor 1 is pointed at stderr for the whole run and the line goes to a saved copy of the original."""
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
+
+
 if __name__ == "__main__":
+    _quiet_stdout()
     main()
