@@ -354,10 +354,26 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
       IndexArgs ia;
       ia.in = pin; ia.len = plen; ia.limit = plimit; ia.is_first = is_first; ia.is_last = is_last;
       ia.tile = d_tile; ia.rec_start = (uint64_t*)pcols.ptr[PJ_COL_REC_START]; ia.cap = cap_records; ia.goff = pgoff;
-      k_nd_index<false><<<(unsigned)ntiles_index, INDEX_THREADS, 0, c->stream>>>(ia);
-      k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles_index, &c->d_res->n_records);
-      k_nd_index<true><<<(unsigned)ntiles_index, INDEX_THREADS, 0, c->stream>>>(ia);
-      count_launch(c, 0, 3);
+      if (c->staged) {
+        k_nd_index<false><<<(unsigned)ntiles_index, INDEX_THREADS, 0, c->stream>>>(ia);
+        k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles_index, &c->d_res->n_records);
+        k_nd_index<true><<<(unsigned)ntiles_index, INDEX_THREADS, 0, c->stream>>>(ia);
+        count_launch(c, 0, 3);
+      } else {
+        /* one pass: count, look back, write (the look-back state shares the buffer the tile kernel uses afterwards) */
+        const uint64_t nt = (plen + 15 + INDEX_LB_TILE) / INDEX_LB_TILE;
+        { pj_status st = ensure(c, &c->tiles, 256 + nt * 16 + 256); if (st) return st; }
+        IndexLbArgs la;
+        la.ix = ia;
+        la.ticket = (uint32_t*)c->tiles.p;
+        la.agg = (unsigned long long*)((uint8_t*)c->tiles.p + 256);
+        la.inc = la.agg + nt;
+        la.ntiles = (uint32_t)nt;
+        la.res = c->d_res;
+        PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, 256 + nt * 16, c->stream));
+        k_nd_index_lb<<<(unsigned)nt, INDEX_THREADS, 0, c->stream>>>(la);
+        count_launch(c, 0, 1);
+      }
     } else {
       d_rec_end = (uint64_t*)((uint8_t*)c->scratch.p + off_rend);
       d_rec_blank = (uint8_t*)c->scratch.p + off_rblank;

@@ -813,7 +813,8 @@ struct WTileArgs {
 };
 
 /* Exclusive prefix of `tile` over all earlier tiles. Warp 0 only, all lanes; false when the bounded wait ran out. */
-__device__ __forceinline__ bool lookback_u64(const WTileArgs& a, uint32_t tile, uint32_t lane, unsigned long long* excl_out) {
+__device__ __forceinline__ bool lookback_u64(const unsigned long long* agg, const unsigned long long* inc, uint32_t* timeout_flag, uint32_t tile,
+                                             uint32_t lane, unsigned long long* excl_out) {
   unsigned long long excl = 0;
   int64_t j = (int64_t)tile - 1;
   const unsigned long long t0 = global_ns();
@@ -823,7 +824,7 @@ __device__ __forceinline__ bool lookback_u64(const WTileArgs& a, uint32_t tile, 
     uint32_t first_inc;
     for (;;) {
       wa = TS_VALID; wi = TS_VALID; /* tiles before the first: inclusive total 0 */
-      if (mine >= 0) { wi = ld_relaxed_u64(&a.inc[mine]); wa = ld_relaxed_u64(&a.agg[mine]); }
+      if (mine >= 0) { wi = ld_relaxed_u64(&inc[mine]); wa = ld_relaxed_u64(&agg[mine]); }
       const bool has_inc = wi & TS_VALID, has_agg = wa & TS_VALID;
       const uint32_t inc_mask = __ballot_sync(0xFFFFFFFFu, has_inc);
       const uint32_t ready_mask = __ballot_sync(0xFFFFFFFFu, has_inc || has_agg);
@@ -831,9 +832,9 @@ __device__ __forceinline__ bool lookback_u64(const WTileArgs& a, uint32_t tile, 
       const uint32_t need = first_inc >= 31 ? 0xFFFFFFFFu : ((2u << first_inc) - 1u);
       if ((ready_mask & need) == need) break;
       uint32_t give_up = 0;
-      if (lane == 0) give_up = (global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)&a.w.res->timeout;
+      if (lane == 0) give_up = (global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)timeout_flag;
       give_up = __shfl_sync(0xFFFFFFFFu, give_up, 0);
-      if (give_up) { if (lane == 0) atomicExch(&a.w.res->timeout, 1u); return false; }
+      if (give_up) { if (lane == 0) atomicExch(timeout_flag, 1u); return false; }
       __nanosleep(100);
     }
     unsigned long long c = lane < first_inc ? (wa & ~TS_VALID) : (lane == first_inc ? (wi & ~TS_VALID) : 0ull);
@@ -845,6 +846,85 @@ __device__ __forceinline__ bool lookback_u64(const WTileArgs& a, uint32_t tile, 
   }
   *excl_out = excl;
   return true;
+}
+
+/* The NDJSON record index in one pass: the candidates of a 16 KiB tile are counted, the tile's first record number
+ * comes from a look-back over the tiles before it (the protocol of the tile kernels, one running total), and the
+ * record starts are written at once. The input is read once; the last tile leaves the record count. */
+struct IndexLbArgs {
+  IndexArgs ix;            /* ix.tile is not used */
+  unsigned long long* agg; /* [ntiles] */
+  unsigned long long* inc; /* [ntiles] */
+  uint32_t* ticket;
+  uint32_t ntiles;
+  DevResult* res;
+};
+static constexpr int INDEX_LB_CHUNKS = 4;                           /* 64-byte chunks per thread */
+static constexpr int INDEX_LB_TILE = INDEX_TILE * INDEX_LB_CHUNKS; /* 64 KiB per block: fewer, larger tiles keep the look-back cheap */
+static __global__ void __launch_bounds__(INDEX_THREADS) k_nd_index_lb(const __grid_constant__ IndexLbArgs a) {
+  __shared__ uint32_t sh[33];
+  __shared__ uint32_t sh_tile, sh_ok;
+  __shared__ unsigned long long sh_base;
+  const uint32_t tid = threadIdx.x, lane = tid & 31;
+  if (tid == 0) sh_tile = atomicAdd(a.ticket, 1u);
+  __syncthreads();
+  const uint32_t tile = sh_tile;
+  if (tile >= a.ntiles) return;
+  const IndexArgs& x = a.ix;
+  const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(x.in) & 15u);
+  const uint8_t* base = x.in - mis; /* 16-byte aligned */
+  const uint64_t vend = x.len ? x.len + mis : 0;
+  /* a thread owns INDEX_LB_CHUNKS consecutive 64-byte chunks, so its records are consecutive too */
+  const uint64_t t0 = (uint64_t)tile * INDEX_LB_TILE + (uint64_t)tid * (INDEX_BYTES_PER_THREAD * INDEX_LB_CHUNKS); /* offset from base */
+  const bool head_keep = x.is_first && tile == 0 && tid == 0 && nd_is_record(x.in, 0, x.limit, x.is_last);
+  uint64_t keep[INDEX_LB_CHUNKS];
+  uint32_t cnt = head_keep ? 1u : 0u;
+#pragma unroll
+  for (int c = 0; c < INDEX_LB_CHUNKS; ++c) {
+    const uint64_t v0 = t0 + (uint64_t)c * INDEX_BYTES_PER_THREAD;
+    uint64_t m = 0;
+    if (v0 < vend) {
+      m = lf_mask64(base + v0, vend - v0);
+      if (v0 < mis) m &= ~0ull << (mis - v0);
+      if (vend - v0 < 64) m &= ~(~0ull << (vend - v0));
+    }
+    uint64_t k = 0;
+    for (uint64_t t = m; t; t &= t - 1) {
+      const int b = __ffsll((long long)t) - 1;
+      const uint64_t p = v0 + (uint64_t)b - mis + 1;
+      if (nd_is_record(x.in, p, x.limit, x.is_last)) { k |= 1ull << b; cnt++; }
+    }
+    keep[c] = k;
+  }
+  uint32_t total;
+  const uint32_t local = block_excl_scan(cnt, &total, sh);
+  if (tid < 32) {
+    if (lane == 0) {
+      st_relaxed_u64(&a.agg[tile], TS_VALID | total);
+      if (tile == 0) st_relaxed_u64(&a.inc[tile], TS_VALID | total);
+    }
+    unsigned long long excl = 0;
+    const bool ok = lookback_u64(a.agg, a.inc, &a.res->timeout, tile, lane, &excl);
+    if (lane == 0) {
+      if (tile != 0 && ok) st_relaxed_u64(&a.inc[tile], TS_VALID | (excl + total));
+      if (tile == a.ntiles - 1) a.res->n_records = excl + total;
+      sh_base = excl;
+      sh_ok = ok;
+    }
+  }
+  __syncthreads();
+  if (!sh_ok) return;
+  uint64_t at = sh_base + local;
+  if (head_keep) { if (at < x.cap) x.rec_start[at] = x.goff; at++; }
+#pragma unroll
+  for (int c = 0; c < INDEX_LB_CHUNKS; ++c) {
+    const uint64_t v0 = t0 + (uint64_t)c * INDEX_BYTES_PER_THREAD;
+    for (uint64_t t = keep[c]; t; t &= t - 1) {
+      const uint64_t p = v0 + (uint64_t)(__ffsll((long long)t) - 1) - mis + 1;
+      if (at < x.cap) x.rec_start[at] = p + x.goff;
+      at++;
+    }
+  }
 }
 
 /* Does any byte of the string arenas need a JSON escape (below 0x20, '"', '\\')? Text is mostly free of
@@ -917,7 +997,7 @@ static __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __g
       if (tile == 0) st_relaxed_u64(&a.inc[tile], TS_VALID | tile_total);
     }
     unsigned long long excl = 0;
-    const bool ok = lookback_u64(a, tile, lane, &excl);
+    const bool ok = lookback_u64(a.agg, a.inc, &a.w.res->timeout, tile, lane, &excl);
     if (lane == 0) {
       if (tile != 0 && ok) st_relaxed_u64(&a.inc[tile], TS_VALID | (excl + tile_total));
       const bool room = lead + excl + tile_total <= a.w.cap;
