@@ -697,14 +697,20 @@ pj_status pj_index_records(pj_ctx* c, uint32_t framing, const uint8_t* in, uint6
                            uint64_t cap, uint64_t* n) {
   if (!c) return PJ_ERR_ARG;
   if ((!in && len) || !n || (!rec_start && cap) || kind > PJ_MEM_DEVICE) return set_err(c, PJ_ERR_ARG, "pj_index_records: bad argument");
-  if (framing != PJ_FRAMING_NDJSON) return set_err(c, PJ_ERR_ARG, "pj_index_records: framing %u is not available", framing);
+  if (framing > PJ_FRAMING_ARRAY) return set_err(c, PJ_ERR_ARG, "pj_index_records: unknown framing %u", framing);
   if (len >= (1ull << 32)) return set_err(c, PJ_ERR_TOO_LARGE, "pj_index_records: input too large");
+  const bool array = framing == PJ_FRAMING_ARRAY;
   DeviceGuard guard(c->device);
   c->stats = pj_call_stats{};
   const uint8_t* d_in = in;
   uint64_t* d_rs = rec_start;
   const uint64_t ntiles = (len + 15 + INDEX_TILE) / INDEX_TILE;
-  size_t off_rs = align_up((ntiles + 1) * 4, 256);
+  const uint64_t nwords = (len + 63) >> 6;
+  const uint64_t atiles = nwords ? (nwords + ARR_THREADS - 1) / ARR_THREADS : 1;
+  size_t off_fn = align_up(((ntiles > atiles ? ntiles : atiles) + 1) * 4, 256);
+  size_t off_tin = align_up(off_fn + (array ? atiles * sizeof(ArrFn) : 0), 256);
+  size_t off_sep = align_up(off_tin + (array ? atiles * sizeof(ArrState) : 0), 256);
+  size_t off_rs = align_up(off_sep + (array ? (nwords + 1) * 8 : 0), 256);
   { pj_status st = ensure(c, &c->scratch, off_rs + (kind == PJ_MEM_HOST ? cap * 8 : 0) + 256); if (st) return st; }
   if (kind == PJ_MEM_HOST) {
     if (len) {
@@ -719,13 +725,31 @@ pj_status pj_index_records(pj_ctx* c, uint32_t framing, const uint8_t* in, uint6
   uint32_t* d_tile = (uint32_t*)c->scratch.p;
   PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream));
   Stage stage(c);
-  IndexArgs ia;
-  ia.in = d_in; ia.len = len; ia.limit = len; ia.is_first = 1; ia.is_last = 1;
-  ia.tile = d_tile; ia.rec_start = d_rs; ia.cap = cap; ia.goff = 0;
-  k_nd_index<false><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
-  k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles, &c->d_res->n_records);
-  k_nd_index<true><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
-  count_launch(c, 0, 3);
+  if (!array) {
+    IndexArgs ia;
+    ia.in = d_in; ia.len = len; ia.limit = len; ia.is_first = 1; ia.is_last = 1;
+    ia.tile = d_tile; ia.rec_start = d_rs; ia.cap = cap; ia.goff = 0;
+    k_nd_index<false><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
+    k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles, &c->d_res->n_records);
+    k_nd_index<true><<<(unsigned)ntiles, INDEX_THREADS, 0, c->stream>>>(ia);
+    count_launch(c, 0, 3);
+  } else {
+    ArrArgs aa;
+    aa.in = d_in; aa.len = len; aa.nwords = nwords;
+    aa.tile_fn = (ArrFn*)((uint8_t*)c->scratch.p + off_fn); aa.tile_in = (ArrState*)((uint8_t*)c->scratch.p + off_tin);
+    aa.sep = (uint64_t*)((uint8_t*)c->scratch.p + off_sep); aa.tile_cnt = d_tile;
+    aa.rec_start = d_rs; aa.rec_end = nullptr; aa.rec_blank = nullptr; /* an index-only call keeps the starts alone */
+    aa.cap = cap; aa.goff = 0; aa.ntiles = (uint32_t)atiles; aa.res = c->d_res;
+    PJ_CUDA(c, cudaMemsetAsync(&c->d_res->doc_err_off, 0xFF, sizeof(unsigned long long), c->stream));
+    PJ_CUDA(c, cudaMemsetAsync(&c->d_res->first_opener, 0xFF, sizeof(unsigned long long), c->stream));
+    k_arr_summary<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+    k_arr_scan_tiles<<<1, 32, 0, c->stream>>>(aa);
+    k_arr_mark<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+    k_arr_records<false><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+    k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, atiles, &c->d_res->n_records);
+    k_arr_records<true><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+    count_launch(c, 0, 6);
+  }
   PJ_CUDA(c, cudaGetLastError());
   stage.next();
   PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));

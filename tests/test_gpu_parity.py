@@ -156,6 +156,22 @@ def test_index_records_only(ctx, oracle):
     assert ctx.index_records(text, np.zeros(10, np.uint64), allow_capacity=True) == want.size
 
 
+def test_index_records_of_an_array(ctx, oracle):
+    """Index only, array framing: the extent starts the checker finds, including extents without a value."""
+    import torch
+
+    text = pj.gen_text(4, 15, 0, 3000, abi.PJ_GEN_ARRAY | abi.PJ_GEN_WHITESPACE | abi.PJ_GEN_ESCAPES)
+    for body in (text, as_u8(b' [ {"a":"]\\"[,"} , , [1,[2]] ,"x]" ] '), as_u8(b"[]"), as_u8(b"")):
+        want = oracle.index(body, ARRAY)
+        rs = np.zeros(want.size + 8, np.uint64)
+        assert ctx.index_records(body, rs, ARRAY) == want.size and np.array_equal(rs[:want.size], want)
+    d_text = torch.from_numpy(text).cuda()
+    d_rs = torch.zeros(3100, dtype=torch.int64, device="cuda")
+    n = ctx.index_records(d_text, d_rs, ARRAY)
+    want = oracle.index(text, ARRAY)
+    assert n == want.size and np.array_equal(d_rs[:n].cpu().numpy().view(np.uint64), want)
+
+
 # ---- writer ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("schema", [1, 2, 3, 4])
 @pytest.mark.parametrize("framing", [NDJSON, ARRAY])
