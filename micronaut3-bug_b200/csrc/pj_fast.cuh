@@ -675,11 +675,21 @@ PJ_HD bool root_value(const Win& w, FastState& f, S& s, FVals& v, FVals& cv) {
       else {
         for (;;) {
           if constexpr (kind == K_LIST_STR) {
-            tape_room<OBJ>(w, s, 1);
             if (wbyte(w, f.p) != '"') return fast_wrong_type(f, wbyte(w, f.p));
             uint32_t pos, len, esc;
             if (!fast_string(w, f, &pos, &len, &esc)) return false;
-            tape_push(*s.t, tape_str(cnt + 1, len, pos, esc));
+            if constexpr (S::drain) {
+              /* the second pass over a long record: a list of strings is where its bytes are, so the strings go
+                 straight to the columns (their slots belong to this list alone, so the order against the words
+                 still on the tape does not matter) */
+              DrainState& d = *s.d;
+              if (d.c) {
+                constexpr uint32_t col = FK<OBJ, I>::col;
+                colp<uint32_t>(d.c, col + 1)[(uint64_t)d.base[cnt] + d.cur[cnt]] = d.base[cnt + 1] + d.cur[cnt + 1];
+                copy_tape_str(colp<uint8_t>(d.c, col + 2) + d.base[cnt + 1] + d.cur[cnt + 1], w, tape_str(0, len, pos, esc));
+              }
+              d.cur[cnt + 1] += len; d.cur[cnt] += 1;
+            } else tape_push(*s.t, tape_str(cnt + 1, len, pos, esc));
             s.cnt[cnt + 1] += len;
           } else {
             /* header word, room for the scalars, then the element's strings as they are met */
