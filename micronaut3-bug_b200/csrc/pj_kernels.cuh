@@ -552,6 +552,33 @@ __device__ __forceinline__ void bulk_s2g_wait_read() { asm volatile("cp.async.bu
 /* makes this thread's earlier writes to shared memory visible to the asynchronous proxy (the bulk copy engine) */
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+/* A cheap guess at the model of the record at p (n readable bytes), from the first key that is not `id`:
+ * 1 Pet, 2 Order, 3 User, 0 no idea. It only decides which records share a warp, never a result. */
+__device__ __forceinline__ uint32_t guess_model(const uint8_t* p, uint64_t n) {
+  const uint32_t lim = n < 96 ? (uint32_t)n : 96u;
+  uint32_t q = 0;
+  for (int key = 0; key < 2; ++key) {
+    while (q < lim && (p[q] == ' ' || p[q] == '\t' || p[q] == '\r' || p[q] == '{' || p[q] == ',')) ++q;
+    if (q + 6 >= lim || p[q] != '"') return 0;
+    const uint32_t c0 = p[q + 1], c1 = p[q + 2], c3 = p[q + 4];
+    if (c0 == 'i' && c1 == 'd' && p[q + 3] == '"') { /* common to all: skip its value */
+      q += 4;
+      while (q < lim && p[q] != ',') ++q;
+      continue;
+    }
+    switch (c0) {
+      case 'c': return c1 == 'a' ? 1u : 2u;            /* category | complete */
+      case 'n': case 't': return 1u;                  /* name, tags */
+      case 'q': return 2u;                            /* quantity */
+      case 'u': case 'f': case 'l': case 'e': return 3u; /* username, userStatus, firstName, lastName, email */
+      case 's': return c1 == 'h' ? 2u : 0u;            /* shipDate | status (Pet or Order) */
+      case 'p': return c1 == 'e' ? 2u : (c1 == 'a' ? 3u : (c3 == 't' ? 1u : 3u)); /* petId | password | photoUrls | phone */
+      default: return 0;
+    }
+  }
+  return 0;
+}
+
 template <int SCHEMA> struct SlotRange {
   static constexpr uint32_t lo = SCHEMA == PJ_SCHEMA_PET ? (uint32_t)SLOT_PET_CAT_NAME : (SCHEMA == PJ_SCHEMA_USER ? (uint32_t)SLOT_USR_STR0 : 0u);
   static constexpr uint32_t hi = SCHEMA == PJ_SCHEMA_PET ? (uint32_t)SLOT_USR_STR0 : (SCHEMA == PJ_SCHEMA_ORDER ? 0u : (uint32_t)NSLOT);
@@ -566,6 +593,10 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
   __shared__ uint32_t sh_tot[NSLOT], sh_base[NSLOT];
   __shared__ uint32_t sh_tile, sh_ok;
   __shared__ __align__(8) unsigned long long sh_mbar; /* completion of the bulk copy that stages the window */
+  constexpr bool SORTED = SCHEMA == PJ_SCHEMA_MIXED;
+  __shared__ uint32_t sh_cls[5][NWARPS];
+  __shared__ uint32_t sh_perm[SORTED ? TILE_THREADS : 1];
+  __shared__ uint32_t sh_x[SORTED ? NSLOT * TILE_THREADS : 1]; /* counts, then tile-local bases, in record order */
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* win = smem;
   uint32_t* tape = reinterpret_cast<uint32_t*>(smem + ((a.win_bytes + 64 + 15) & ~15u));
@@ -579,8 +610,38 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
   const uint64_t left = N > r0 ? N - r0 : 0;
   const uint32_t nrec = left < a.tile_recs ? (uint32_t)left : a.tile_recs;
   const uint64_t* rec_start = colp<uint64_t>(&a.cols, PJ_COL_REC_START);
-  const bool active = tid < nrec;
-  const uint64_t i = r0 + tid;
+  /* Which record of the tile this thread takes. In a stream of several models the records are first grouped by
+     (a guess at) their model, so that the lanes of a warp mostly run the same model's code; everything that depends
+     on the order of the records (the scan of the counts) goes through shared memory in record order. */
+  uint32_t rid = tid;
+  if constexpr (SCHEMA == PJ_SCHEMA_MIXED) {
+    uint32_t cls = 4; /* threads without a record go last */
+    if (tid < nrec) {
+      const uint64_t st = rec_start[r0 + tid] - a.goff;
+      cls = guess_model(a.in + st, a.limit - st);
+    }
+    uint32_t before = 0, rank = 0;
+#pragma unroll
+    for (uint32_t c = 0; c < 5; ++c) {
+      const uint32_t b = __ballot_sync(0xFFFFFFFFu, cls == c);
+      if (lane == 0) sh_cls[c][warp] = __popc(b);
+      if (cls == c) rank = __popc(b & ((1u << lane) - 1u));
+    }
+    __syncthreads();
+#pragma unroll
+    for (uint32_t c = 0; c < 5; ++c) {
+#pragma unroll
+      for (uint32_t q = 0; q < NWARPS; ++q) {
+        const uint32_t n_cq = sh_cls[c][q];
+        if (c < cls || (c == cls && q < warp)) before += n_cq;
+      }
+    }
+    sh_perm[before + rank] = tid;
+    __syncthreads();
+    rid = sh_perm[tid];
+  }
+  const bool active = rid < nrec;
+  const uint64_t i = r0 + rid;
   const uint64_t start = active ? rec_start[i] - a.goff : 0;
   const uint64_t my_limit = (active && a.rec_end) ? a.rec_end[i] : a.limit;
 
@@ -694,11 +755,17 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
 
   /* ---- positions: scan inside the tile (two barriers for all counters), then look back ------------- */
   if (tid < NSLOT) sh_tot[tid] = 0;
+  if constexpr (SORTED) {
+#pragma unroll
+    for (uint32_t k = LO; k < HI; ++k) sh_x[k * TILE_THREADS + rid] = cnt[k];
+    __syncthreads();
+  }
 #pragma unroll
   for (uint32_t k = LO; k < HI; ++k) {
-    const uint32_t inc = warp_incl_scan(cnt[k]);
+    const uint32_t mine_k = SORTED ? sh_x[k * TILE_THREADS + tid] : cnt[k]; /* the count of record number tid */
+    const uint32_t inc = warp_incl_scan(mine_k);
     if (lane == 31) sh_warp[k][warp] = inc;
-    base[k] = inc - cnt[k];
+    base[k] = inc - mine_k;
   }
   __syncthreads();
   const long long c2 = clock64();
@@ -706,6 +773,7 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
   for (uint32_t k = LO; k < HI; ++k) {
 #pragma unroll
     for (uint32_t q = 0; q < NWARPS; ++q) if (q < warp) base[k] += sh_warp[k][q];
+    if constexpr (SORTED) sh_x[k * TILE_THREADS + tid] = base[k]; /* record tid's place in the tile; read back by its owner below */
   }
   if (warp == 0) {
     TileState* me = &a.tiles[tile];
@@ -743,7 +811,7 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
   /* ---- emit ---------------------------------------------------------------------------------------- */
   if (active) {
 #pragma unroll
-    for (uint32_t k = LO; k < HI; ++k) base[k] += sh_base[k];
+    for (uint32_t k = LO; k < HI; ++k) base[k] = (SORTED ? sh_x[k * TILE_THREADS + rid] : base[k]) + sh_base[k];
     if (SCHEMA == PJ_SCHEMA_MIXED) {
       const uint32_t row = type == PJ_TYPE_PET ? base[SLOT_ROWS_PET] : (type == PJ_TYPE_ORDER ? base[SLOT_ROWS_ORD] : base[SLOT_ROWS_USR]);
       colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = type == PJ_TYPE_NONE ? 0xFFFFFFFFu : row;
