@@ -182,7 +182,7 @@ def main():
     ap.add_argument("--records", type=int, default=1_000_000, help="records per GPU and step")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="pet", choices=["pet", "mixed", "zipf"], help="pet: 1M Pet records (the headline configuration); mixed: Pet/Order/User 50/30/20 with 1%% malformed; zipf: Pets with zipf(1.2) list lengths, 5%% escaped strings, random blanks")
+    ap.add_argument("--workload", default="pet", choices=["pet", "mixed", "zipf", "array1k"], help="pet: 1M Pet records (the headline configuration); mixed: Pet/Order/User 50/30/20 with 1%% malformed; zipf: Pets with zipf(1.2) list lengths, 5%% escaped strings, random blanks; array1k: a JSON array of 1000 Pets (the reference's own CPU-runnable case), parse and re-serialise")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--host-piece-bytes", type=int, default=0, help="pj_options.host_piece_bytes of the end-to-end leg (0 = library default)")
     args = ap.parse_args()
@@ -208,9 +208,17 @@ def main():
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # NCCL's version banner must not land on stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     R = args.records
-    mixed_wl = args.workload != "pet"  # a side workload: parse only, no end-to-end or CPU leg
+    mixed_wl = args.workload in ("mixed", "zipf")  # a side workload: parse only, no end-to-end or CPU leg
+    array_wl = args.workload == "array1k"
+    framing = abi.PJ_FRAMING_ARRAY if array_wl else abi.PJ_FRAMING_NDJSON
+    if array_wl:
+        args.records = 1000
+        R = 1000
+        args.no_e2e = True
+        args.no_cpu_baseline = True
     PET = abi.PJ_SCHEMA_MIXED if args.workload == "mixed" else abi.PJ_SCHEMA_PET  # the schema of the timed workload
-    gen_flags = {"pet": 0, "mixed": abi.PJ_GEN_MALFORMED, "zipf": abi.PJ_GEN_ZIPF_LISTS | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE}[args.workload]
+    gen_flags = {"pet": 0, "mixed": abi.PJ_GEN_MALFORMED, "zipf": abi.PJ_GEN_ZIPF_LISTS | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE,
+                 "array1k": abi.PJ_GEN_ARRAY}[args.workload]
     if mixed_wl:
         args.no_e2e = True
         args.no_cpu_baseline = True
@@ -235,7 +243,7 @@ def main():
     def step_device():
         if sharded:
             return sharded.parse(d_text, nbytes, cols, wait=False)
-        ctx.parse(PET, d_text[:nbytes], cols)
+        ctx.parse(PET, d_text[:nbytes], cols, framing)
         return None
 
     launches = 0
@@ -294,12 +302,12 @@ def main():
     wsteps = max(3, args.steps // 2)
     if not sharded and not mixed_wl:
         for _ in range(3):
-            ctx.write(PET, cols, d_out)
+            ctx.write(PET, cols, d_out, framing)
         torch.cuda.synchronize()
         w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0.record(stream)
         for _ in range(wsteps):
-            w_len = ctx.write(PET, cols, d_out)
+            w_len = ctx.write(PET, cols, d_out, framing)
             st = ctx.stats()
             w_dev_ms += st.device_ms; w_launch += st.kernel_launches; w_alg = st.algorithmic_bytes
             w_kernel_ms += st.main_kernel_ms; w_phase = [int(x) // max(int(st.tiles), 1) for x in st.phase_cycles]
@@ -355,7 +363,7 @@ def main():
         "vs_baseline": None,
         "dtype": "u8",
         "data": "synthetic",
-        "config": {"workload": {"pet": "1M Pet records as NDJSON, one record per line (BASELINE configs[1])", "mixed": "Pet/Order/User 50/30/20 with 1% malformed records as NDJSON (BASELINE configs[2] distributions)", "zipf": "Pets with zipf(1.2) list lengths, 5% escaped strings, random blanks as NDJSON (BASELINE configs[3] distributions)"}[args.workload], "records_per_gpu": R, "seed": SEED,
+        "config": {"workload": {"pet": "1M Pet records as NDJSON, one record per line (BASELINE configs[1])", "mixed": "Pet/Order/User 50/30/20 with 1% malformed records as NDJSON (BASELINE configs[2] distributions)", "zipf": "Pets with zipf(1.2) list lengths, 5% escaped strings, random blanks as NDJSON (BASELINE configs[3] distributions)", "array1k": "JSON array of 1000 Pets (BASELINE configs[0]); launch-latency bound at this size"}[args.workload], "records_per_gpu": R, "seed": SEED,
                    "input_bytes_per_gpu": nbytes, "l2": "input (292 MB at 1M records) and columns are larger than the 126 MB L2; no flush between steps",
                    "sharding": "one byte range per GPU, 64 KiB slack from the next rank, counters all-gathered" if world > 1 else "single GPU"},
         "gb_per_s": total_rec * args.steps / (ms * 1e-3) * nbytes / R / 1e9,

@@ -9,7 +9,6 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
-#include <cstdlib>
 #include <new>
 
 #include "petjson.h"
@@ -100,7 +99,6 @@ struct pj_ctx {
   cudaStream_t s_in = nullptr, s_out = nullptr;
   cudaEvent_t ev_in[16] = {};
   uint32_t piece_bytes = 0;
-  uint32_t min_tile_recs = 128;
   Schema schema;
   pj_call_stats stats = {};
   char err[256] = "";
@@ -437,11 +435,9 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
       ta.in = pin; ta.limit = plimit; ta.goff = pgoff; ta.n_records = N0;
       ta.lf_ws = array ? 1u : 0u; ta.open_end = is_last ? 0u : 1u; ta.schema = schema; ta.slot_lo = slot_lo; ta.slot_hi = slot_hi;
       ta.win_bytes = TILE_WIN_BYTES; ta.tape_cap = TILE_TAPE_CAP;
-      /* As many records per tile as fit the staging window on average, but never fewer than a warp's worth: records
-         that miss the window are read where they lie, which costs less than idle threads. */
-      const uint64_t avg = N0 ? plimit / N0 + 1 : 1;
-      uint32_t tile_recs = TILE_THREADS;
-      while (tile_recs > c->min_tile_recs && (uint64_t)tile_recs * avg + 3584 > TILE_WIN_BYTES) tile_recs >>= 1;
+      /* A tile is always one record per thread: records that miss the staging window are read where they lie, which
+         costs less than idle threads (measured on long records: 128 per tile beat 16, 32 and 64). */
+      const uint32_t tile_recs = TILE_THREADS;
       ta.tile_recs = tile_recs;
       const uint64_t ntiles = N0 ? (N0 + tile_recs - 1) / tile_recs : 1;
       ta.ntiles = (uint32_t)ntiles;
@@ -594,7 +590,6 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   c->inclusion = opt ? opt->inclusion : PJ_INCLUDE_NON_EMPTY;
   c->staged = opt && (opt->flags & PJ_OPT_STAGED_PIPELINE);
   c->piece_bytes = opt ? opt->host_piece_bytes : 0;
-  if (const char* e = getenv("PJ_MIN_TILE_RECS")) { int v = atoi(e); if (v >= 4 && v <= 128) c->min_tile_recs = (uint32_t)v; }
   DeviceGuard guard(dev);
   auto fail_create = [&](cudaError_t err, const char* what) {
     set_err(nullptr, PJ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
