@@ -2,14 +2,23 @@
  * pj_fast.cuh — the speculative word-at-a-time record tokeniser, instantiated on the compile-time
  * model tables of pj_schema.h.
  *
- * fast_record<>() reads a record 8 bytes at a time from a window staged in shared memory and accepts
- * it only when it is "plain": valid, every key known and met once. Such a record never needs the byte-at-a-time machinery of
- * pj_core.cuh, so its values, counts and the place of every string are known after ONE pass; they
- * are kept (values in registers, strings as 8-byte tape entries in shared memory) until the record's
- * output positions are known, and then replayed by fast_emit<>(). Anything else makes fast_record<>()
- * return false, and the caller runs the exact generic parser on the record. fast_record<>() therefore
- * never reports a validation failure itself: it may refuse, but what it accepts it must decode
- * exactly as the generic parser would.
+ * fast_record<>() reads a record 8 bytes at a time from a window staged in shared memory (or, for a record
+ * that missed the window, from where it lies in global memory). It gives one of three verdicts:
+ *   accepted  the record is valid, every key is known and met once (in any order, with any blanks, with
+ *             null values, escapes and UTF-8 in its strings). Its values, counts and the place of every
+ *             string are known after ONE pass; they are kept (values in registers, strings as 32-bit tape
+ *             words in shared memory) until the record's output positions are known, and then replayed by
+ *             fast_emit<>() - or, when they outnumber the tape, by a second pass of fast_outline<>();
+ *   failed    the record fails validation in one of the common ways (wrong JSON type, unknown enum literal,
+ *             missing required property, bad date-time, record ending inside a string); kind and byte offset
+ *             are exactly what the generic parser reports, because everything before was accepted;
+ *   refused   anything else (unknown or repeated key, number with a fraction, ...): the caller runs the exact
+ *             byte-wise parser of pj_core.cuh on the record.
+ * What it accepts it decodes exactly as the generic parser would; a host build of this header is fuzzed
+ * against the CPU checker for that.
+ *
+ * Rare and large parts (escapes and UTF-8 in strings, decoding at emission, the second pass) are out of
+ * line on purpose: inlined into the hot loop they made it miss the instruction cache and run 3x slower.
  *
  * All positions here are 32-bit offsets into the window; every property index, kind, column and
  * counter slot is a template constant, so per-record state lives in registers.

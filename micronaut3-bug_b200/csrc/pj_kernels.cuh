@@ -1,15 +1,20 @@
 /*
- * pj_kernels.cuh — the sm_100a kernels of the staged pipeline: NDJSON record index, per-record
- * size / emit passes, the counter scans between them, and the JSON writer.
+ * pj_kernels.cuh — the sm_100a kernels.
  *
- *   input bytes --k_nd_index<false>--> records per 16 KiB tile --scan--> tile bases
- *               --k_nd_index<true>--> rec_start[]
- *               --k_parse<false>----> err_kind / err_off / model, counters[slot][record]
- *               --scan (per slot)--> start of every record in every arena; totals; capacity check
- *               --k_parse<true>-----> every column, string bytes, list offsets
- *               --k_finalize--------> closing offsets
+ * Parse, single pass (the default):
+ *   input bytes --k_nd_index_lb--> rec_start[]            one pass, look-back on the record count
+ *               --k_parse_tile<SCHEMA>--> every column     128 records per block: bulk-copy staging, one tokenising
+ *                                                          pass per record, block scan + decoupled look-back, emission
+ * Write, single pass:
+ *   columns --k_arena_flags--> "any byte to escape?" --k_write_tile--> text --k_write_close--> brackets, total
+ * Array framing gets its record index from pj_array_kernels.cuh.
  *
- * Nothing here waits on another thread block, so no kernel can hang on a peer.
+ * The first, multi-pass pipelines are kept behind PJ_OPT_STAGED_PIPELINE as an independent implementation:
+ *   k_nd_index<false> / k_scan_single / k_nd_index<true>, k_parse_size, k_scan_*, k_check, k_parse_emit, k_finalize,
+ *   k_write_size, k_write_check, k_write_emit. Nothing in them waits on another thread block.
+ *
+ * Kernels that do wait on other blocks (the look-backs) take their tile from an atomic ticket, so every block they
+ * wait for is running or done, and every wait is bounded (PJ_SPIN_LIMIT_NS -> DevResult.timeout -> PJ_ERR_TIMEOUT).
  */
 #ifndef PJ_KERNELS_CUH
 #define PJ_KERNELS_CUH
