@@ -1,0 +1,162 @@
+"""The device-side parsers and writers, compiled for the host and fuzzed against the CPU checker (no GPU needed).
+
+tests/host_emu/pj_host_emu.cpp includes the library's host+device headers and runs them one "thread" after
+another; what is compared is bit-exact: every column, error kind and offset, and the re-serialised bytes.
+"""
+import ctypes as C
+import os
+import random
+import subprocess
+
+import numpy as np
+import pytest
+
+from pj_testlib import abi, as_u8, nrec_bound, pj, same_result
+from test_oracle_crosscheck import mutate
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+SRC = os.path.join(HERE, "host_emu", "pj_host_emu.cpp")
+LIB = os.path.join(HERE, "host_emu", "libpj_host_emu.so")
+u32, u64 = C.c_uint32, C.c_uint64
+NDJSON, ARRAY = abi.PJ_FRAMING_NDJSON, abi.PJ_FRAMING_ARRAY
+G = abi  # generator flags live in the abi module
+
+
+@pytest.fixture(scope="session")
+def emu(native):  # `native` builds libpetjson.so, whose generator the tests use
+    csrc = os.path.join(ROOT, "micronaut3-bug_b200", "csrc")
+    deps = [SRC] + [os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith((".cuh", ".h"))]
+    if not os.path.exists(LIB) or any(os.path.getmtime(d) > os.path.getmtime(LIB) for d in deps):
+        subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I", os.path.join(ROOT, "include"), "-I", csrc,
+                        "-x", "c++", SRC, "-o", LIB], check=True)
+    return C.CDLL(LIB)
+
+
+def garbage_columns(schema, n, nbytes):
+    """Buffers pre-filled with 0xA5, so a column the code forgets to write shows up."""
+    return abi.HostColumns(schema, abi.default_caps(schema, n, nbytes), alloc=lambda nb: np.full(nb, 0xA5, np.uint8))
+
+
+def extents(oracle, buf):
+    cap = nrec_bound(buf)
+    s, e, b, n = np.zeros(cap, np.uint64), np.zeros(cap, np.uint64), np.zeros(cap, np.uint8), u64()
+    st = oracle.lib.pjo_extents(u32(ARRAY), C.c_void_p(buf.ctypes.data), u64(buf.size), C.c_void_p(s.ctypes.data), C.c_void_p(e.ctypes.data),
+                                C.c_void_p(b.ctypes.data), u64(cap), C.byref(n), None, None)
+    assert st == 0
+    return s[:n.value], e[:n.value], b[:n.value]
+
+
+def emu_parse_tiles(emu, oracle, schema, buf, framing=NDJSON, tile=128, win=45056, tape=20):
+    """The tile kernel's per-record work on the host: windows of `win` bytes, tapes of `tape` words, `tile` records a tile."""
+    buf = as_u8(buf)
+    hc = garbage_columns(schema, nrec_bound(buf), buf.size)
+    if framing == ARRAY:
+        s, e, b = extents(oracle, buf)
+    else:
+        s = e = np.zeros(1, np.uint64)
+        b = np.zeros(1, np.uint8)
+    nfast = u64()
+    pad = np.concatenate([buf, np.zeros(64, np.uint8)])  # the code looks 16 bytes ahead
+    st = emu.emu_parse_fast(u32(schema), u32(framing), C.c_void_p(pad.ctypes.data), u64(buf.size), u64(0), 1, 1, u64(0), C.byref(hc.raw),
+                            C.byref(nfast), u32(tile), u32(win), u32(tape), C.c_void_p(s.ctypes.data), C.c_void_p(e.ctypes.data),
+                            C.c_void_p(b.ctypes.data), u64(len(s) if framing == ARRAY else 0))
+    assert st == 0, st
+    return hc, nfast.value
+
+
+def emu_write(emu, fn, schema, cols, framing, inclusion, cap):
+    out, ln = np.zeros(cap, np.uint8), u64()
+    st = getattr(emu, fn)(u32(schema), u32(framing), inclusion, C.byref(cols.raw), C.c_void_p(out.ctypes.data), u64(cap), C.byref(ln))
+    assert st == 0, st
+    return out[: ln.value]
+
+
+ALL = G.PJ_GEN_ESCAPES | G.PJ_GEN_WHITESPACE | G.PJ_GEN_MALFORMED | G.PJ_GEN_SPARSE
+FLAG_SETS = [0, G.PJ_GEN_ESCAPES, G.PJ_GEN_WHITESPACE, G.PJ_GEN_MALFORMED, G.PJ_GEN_SPARSE, ALL, G.PJ_GEN_ZIPF_LISTS | ALL]
+SHAPES = [(128, 45056, 20), (16, 45056, 8), (128, 2048, 20), (7, 45056, 8)]
+
+
+@pytest.mark.parametrize("schema", [1, 2, 3, 4])
+@pytest.mark.parametrize("flags", FLAG_SETS)
+def test_tile_code_matches_checker_on_generated_text(emu, oracle, schema, flags):
+    text = pj.gen_text(schema, 0xE11, 0, 700, flags)
+    want = oracle.parse(schema, text)
+    for tile, win, tape in SHAPES:
+        got, nfast = emu_parse_tiles(emu, oracle, schema, text, NDJSON, tile, win, tape)
+        assert same_result(want, got) == "", (tile, win, tape)
+        if flags == 0:
+            assert nfast >= want.n_records - 1  # everything but, at most, the record at the very end of the input
+
+
+def test_common_failures_are_found_by_the_word_path(emu, oracle):
+    """Wrong type, unknown literal, missing required property, record ending in a string: same kind and offset as the checker."""
+    emu.emu_fail_fast_count.restype = C.c_uint64
+    before = emu.emu_fail_fast_count()
+    nerr = 0
+    for schema in (1, 2, 3, 4):
+        text = pj.gen_text(schema, 99, 0, 3000, G.PJ_GEN_MALFORMED)
+        want = oracle.parse(schema, text)
+        got, _ = emu_parse_tiles(emu, oracle, schema, text)
+        assert same_result(want, got) == ""
+        nerr += want.n_errors
+    assert nerr > 60 and emu.emu_fail_fast_count() - before >= nerr * 9 // 10
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_tile_code_matches_checker_on_mutated_text(emu, oracle, seed):
+    rng = random.Random(seed)
+    for it in range(60):
+        schema = rng.choice([1, 1, 2, 3, 4, 4])
+        flags = rng.choice(FLAG_SETS)
+        lines = bytes(pj.gen_text(schema, rng.randrange(1 << 30), rng.randrange(1000), 40, flags)).split(b"\n")[:-1]
+        out = []
+        for ln in lines:
+            out.append(ln if rng.random() < 0.2 else mutate(rng, ln))
+            if rng.random() < 0.05:
+                out.append(rng.choice([b"", b"  ", b"\r", b"\t \r"]))
+        body = as_u8(b"\n".join(out) + (b"\n" if rng.random() < 0.8 else b""))
+        if body.size == 0:
+            continue
+        want = oracle.parse(schema, body)
+        tile, win, tape = rng.choice(SHAPES)
+        got, _ = emu_parse_tiles(emu, oracle, schema, body, NDJSON, tile, win, tape)
+        assert same_result(want, got) == "", (seed, it, schema, flags, tile, win, tape)
+        # whatever parsed goes back to text through both writers
+        for incl in (abi.PJ_INCLUDE_NON_EMPTY, abi.PJ_INCLUDE_NON_NULL, abi.PJ_INCLUDE_ALWAYS):
+            text = oracle.write(schema, want, NDJSON, incl)
+            for fn in ("emu_write", "emu_write_fast"):
+                assert np.array_equal(text, emu_write(emu, fn, schema, want, NDJSON, incl, body.size * 8 + 128)), (fn, seed, it)
+
+
+def test_tile_code_on_array_framing(emu, oracle):
+    rng = random.Random(5)
+    for it in range(40):
+        schema = rng.choice([1, 2, 3, 4])
+        flags = G.PJ_GEN_ARRAY | rng.choice([0, G.PJ_GEN_WHITESPACE | G.PJ_GEN_ESCAPES, ALL])
+        body = as_u8(pj.gen_text(schema, rng.randrange(1 << 30), 0, 50, flags))
+        want = oracle.parse(schema, body, ARRAY)
+        tile, win, tape = rng.choice(SHAPES)
+        got, _ = emu_parse_tiles(emu, oracle, schema, body, ARRAY, tile, win, tape)
+        assert same_result(want, got) == "", (it, schema, flags)
+
+
+def test_integer_text_at_every_digit_count(emu, oracle):
+    """The writer's 8-digit groups: powers of ten, their neighbours, both signs, both widths."""
+    vals = [0, 1, -1, 9223372036854775807, -9223372036854775808]
+    for d in range(1, 19):
+        vals += [10 ** d - 1, 10 ** d, 10 ** d + 1, -(10 ** d - 1), -(10 ** d), 10 ** d * 7 + 12345 % 10 ** d]
+    recs = [b'{"id":%d,"category":{"id":%d,"name":"c\\u0001\\"x\\\\y\\n"},"name":"n","photoUrls":["a\\tb","plain-0123456789","\\u00e9\\u20ac\\ud83d\\ude00z"],'
+            b'"tags":[{"id":%d,"name":"t"},{"id":%d}],"status":"sold"}' % (v, -v if v > -2 ** 63 else v, v, v // 7) for v in vals]
+    orders = [b'{"id":%d,"petId":%d,"quantity":%d,"shipDate":"20%02d-02-28T23:59:59.%03dZ","status":"approved","complete":%s}'
+              % (v, v, max(-2 ** 31, min(2 ** 31 - 1, v)), k % 100, k % 1000, b"true" if k & 1 else b"false") for k, v in enumerate(vals)]
+    for schema, lines in ((1, recs), (2, orders), (4, recs + orders)):
+        body = as_u8(b"\n".join(lines) + b"\n")
+        cols = oracle.parse(schema, body)
+        assert cols.n_errors == 0
+        got, _ = emu_parse_tiles(emu, oracle, schema, body)
+        assert same_result(cols, got) == ""
+        for framing in (NDJSON, ARRAY):
+            for incl in (abi.PJ_INCLUDE_NON_EMPTY, abi.PJ_INCLUDE_NON_NULL, abi.PJ_INCLUDE_ALWAYS):
+                want = oracle.write(schema, cols, framing, incl)
+                assert np.array_equal(want, emu_write(emu, "emu_write_fast", schema, cols, framing, incl, body.size * 4 + 128))
