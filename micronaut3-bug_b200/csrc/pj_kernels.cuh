@@ -1032,6 +1032,24 @@ static __global__ void __launch_bounds__(256) k_arena_flags(const __grid_constan
   if (__syncthreads_or((int)any) && threadIdx.x == 0) a.res->needs_escape = 1u;
 }
 
+/* The writer is bound by the latency of its column loads (one dependent chain per property). Asking for all the
+ * row-indexed values of a record at once, before the first is needed, lets those latencies overlap. */
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+template <int OBJ, int I = 0>
+__device__ __forceinline__ void prefetch_row(const DevCols* c, uint64_t row) {
+  if constexpr (I == 0) prefetch_l1(colp<uint8_t>(c, CObj<OBJ>::present_col) + row);
+  if constexpr (I < CObj<OBJ>::N) {
+    constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col;
+    if constexpr (kind == K_I64) prefetch_l1(colp<int64_t>(c, col) + row);
+    else if constexpr (kind == K_I32) prefetch_l1(colp<int32_t>(c, col) + row);
+    else if constexpr (kind == K_BOOL || kind == K_ENUM) prefetch_l1(colp<uint8_t>(c, col) + row);
+    else if constexpr (kind == K_DATETIME) { prefetch_l1(colp<int64_t>(c, col) + row); prefetch_l1(colp<int32_t>(c, col + 1) + row); prefetch_l1(colp<int32_t>(c, col + 2) + row); }
+    else if constexpr (kind == K_STR || kind == K_LIST_STR || kind == K_LIST_OBJ) prefetch_l1(colp<uint32_t>(c, col) + row + 1);
+    else if constexpr (kind == K_OBJ) prefetch_row<FK<OBJ, I>::child>(c, row);
+    prefetch_row<OBJ, I + 1>(c, row);
+  }
+}
+
 static __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_constant__ WTileArgs a) {
   constexpr uint32_t NWARPS = TILE_THREADS / 32;
   extern __shared__ __align__(16) uint8_t smem[];
@@ -1051,6 +1069,9 @@ static __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __g
   const bool located = i < a.w.n && write_locate(a.w.schema, &a.w.cols, i, &type, &row);
   uint32_t len = 0;
   if (located) {
+    if (type == PJ_TYPE_PET) prefetch_row<OBJ_PET>(&a.w.cols, row);
+    else if (type == PJ_TYPE_ORDER) prefetch_row<OBJ_ORDER>(&a.w.cols, row);
+    else prefetch_row<OBJ_USER>(&a.w.cols, row);
     WOut w; w.dst = nullptr; w.n = 0;
     if (plain) fwrite_record<false, true>(&a.w.cols, type, row, a.w.inclusion, w); else fwrite_record<false, false>(&a.w.cols, type, row, a.w.inclusion, w);
     len = (uint32_t)w.n + 1; /* LF, or the comma / closing bracket that follows the record */

@@ -74,9 +74,25 @@ PJ_HD void copy_bytes_fast(uint8_t* d, const uint8_t* s, uint32_t n) {
     const uint32_t sh = (uint32_t)((uintptr_t)s & 3u) * 8u;
     const uint32_t* sw = reinterpret_cast<const uint32_t*>((uintptr_t)s & ~(uintptr_t)3);
     if (sh == 0) {
+      for (; n >= 16; n -= 16) { /* four loads in flight, then four stores */
+        const uint32_t a0 = sw[0], a1 = sw[1], a2 = sw[2], a3 = sw[3];
+        uint32_t* dw = reinterpret_cast<uint32_t*>(d);
+        dw[0] = a0; dw[1] = a1; dw[2] = a2; dw[3] = a3;
+        sw += 4; d += 16; s += 16;
+      }
       for (; n >= 4; n -= 4) { *reinterpret_cast<uint32_t*>(d) = *sw++; d += 4; s += 4; }
     } else {
       uint32_t x0 = *sw++;
+      for (; n >= 16; n -= 16) { /* the four words that hold the next 16 bytes, loaded together */
+        const uint32_t a1 = sw[0], a2 = sw[1], a3 = sw[2], a4 = sw[3];
+        uint32_t* dw = reinterpret_cast<uint32_t*>(d);
+#if defined(__CUDA_ARCH__)
+        dw[0] = __funnelshift_r(x0, a1, sh); dw[1] = __funnelshift_r(a1, a2, sh); dw[2] = __funnelshift_r(a2, a3, sh); dw[3] = __funnelshift_r(a3, a4, sh);
+#else
+        dw[0] = (x0 >> sh) | (a1 << (32 - sh)); dw[1] = (a1 >> sh) | (a2 << (32 - sh)); dw[2] = (a2 >> sh) | (a3 << (32 - sh)); dw[3] = (a3 >> sh) | (a4 << (32 - sh));
+#endif
+        x0 = a4; sw += 4; d += 16; s += 16;
+      }
       for (; n >= 4; n -= 4) {
         const uint32_t x1 = *sw++;
 #if defined(__CUDA_ARCH__)
