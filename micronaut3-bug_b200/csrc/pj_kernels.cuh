@@ -874,7 +874,7 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
  * copies the window to the output with 16-byte stores. A tile whose text does not fit the window is
  * written to global memory directly. Text is produced once and written to HBM once.
  * ================================================================================================ */
-static constexpr uint32_t WTILE_WIN_BYTES = 48 * 1024;
+static constexpr uint32_t WTILE_WIN_BYTES = 40 * 1024;
 static constexpr uint32_t WTILE_SMEM_BYTES = WTILE_WIN_BYTES + 32;
 
 struct WTileArgs {
@@ -1050,7 +1050,7 @@ __device__ __forceinline__ void prefetch_row(const DevCols* c, uint64_t row) {
   }
 }
 
-static __global__ void __launch_bounds__(TILE_THREADS, 4) k_write_tile(const __grid_constant__ WTileArgs a) {
+static __global__ void __launch_bounds__(TILE_THREADS, 5) k_write_tile(const __grid_constant__ WTileArgs a) {
   constexpr uint32_t NWARPS = TILE_THREADS / 32;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ uint32_t sh_warp[NWARPS];
