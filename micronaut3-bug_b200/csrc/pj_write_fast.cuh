@@ -180,6 +180,27 @@ PJ_HD void fput_enum(WOut& w, uint32_t e) {
 template <bool WR, bool PLAIN, int OBJ, int LEVEL>
 PJ_HD void fwrite_object(const DevCols* c, uint64_t row, int incl, WOut& w);
 
+/* a hint to start fetching the line at p (nothing on the host) */
+PJ_HD void wr_prefetch(const void* p) {
+#if defined(__CUDA_ARCH__)
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+#else
+  (void)p;
+#endif
+}
+/* the scalar columns of flat object E (a list element) at `row` */
+template <int E, int I = 0>
+PJ_HD void wr_prefetch_row(const DevCols* c, uint64_t row) {
+  if constexpr (I == 0) wr_prefetch(colp<uint8_t>(c, CObj<E>::present_col) + row);
+  if constexpr (I < CObj<E>::N) {
+    constexpr uint32_t kind = FK<E, I>::kind, col = FK<E, I>::col;
+    if constexpr (kind == K_I64) wr_prefetch(colp<int64_t>(c, col) + row);
+    else if constexpr (kind == K_I32 || kind == K_STR) wr_prefetch(colp<uint32_t>(c, col) + row);
+    else if constexpr (kind == K_BOOL || kind == K_ENUM) wr_prefetch(colp<uint8_t>(c, col) + row);
+    wr_prefetch_row<E, I + 1>(c, row);
+  }
+}
+
 /* property I of OBJ and, by recursion, the ones after it */
 template <bool WR, bool PLAIN, int OBJ, int LEVEL, int I = 0>
 PJ_HD void fwrite_fields(const DevCols* c, uint64_t row, int incl, uint32_t present, bool& first, WOut& w) {
@@ -191,6 +212,15 @@ PJ_HD void fwrite_fields(const DevCols* c, uint64_t row, int incl, uint32_t pres
     if constexpr (kind == K_STR || kind == K_LIST_STR || kind == K_LIST_OBJ) {
       a = colp<uint32_t>(c, col)[row]; b = colp<uint32_t>(c, col)[row + 1];
       empty = a == b;
+      if constexpr (!WR && PLAIN) {
+        /* the measuring pass does not look at string bytes or child rows here: ask for them now, the writing pass
+           that follows finds them on their way */
+        if (a < b) {
+          if constexpr (kind == K_STR) wr_prefetch(colp<uint8_t>(c, col + 1) + a);
+          else if constexpr (kind == K_LIST_STR) wr_prefetch(colp<uint8_t>(c, col + 2) + colp<uint32_t>(c, col + 1)[a]);
+          else if constexpr (LEVEL == 0) wr_prefetch_row<FK<OBJ, I>::child>(c, a);
+        }
+      }
     }
     if (included(incl, pr, empty)) {
       if (!first) wput<WR>(w, ',');
