@@ -3,7 +3,7 @@
  *
  *   k_arr_summary   every thread summarises its 64-byte word as a function of the incoming (escape carry,
  *                   in-string) state; an ordered shuffle reduction gives one function per 16 KiB tile
- *   k_arr_scan_tiles   composes the tile functions in order -> incoming state of every tile, final state
+ *   k_arr_scan_tiles   composes the tile functions in order (one warp, 32 runs) -> incoming state of every tile, final state
  *   k_arr_mark      re-evaluates every word with its exact incoming state (ordered scan inside the block),
  *                   writes the separator bitmap, finds the first opener and the first stray byte
  *   k_arr_records<> one candidate per separator: extent, blank test, keep / drop; count per tile, then
@@ -99,17 +99,30 @@ static __global__ void __launch_bounds__(ARR_THREADS) k_arr_summary(const __grid
   }
 }
 
-/* One thread walks the tiles in order. (A tile is 16 KiB, so even a 4 GiB input has 262144 of them.) */
+/* One warp: every lane composes a contiguous run of tile functions, an ordered scan over the 32 runs gives each lane
+ * the state its run starts in, and the lane walks its run once more to leave every tile's incoming state. */
 static __global__ void k_arr_scan_tiles(const __grid_constant__ ArrArgs a) {
-  if (threadIdx.x || blockIdx.x) return;
+  if (blockIdx.x || threadIdx.x >= 32) return;
+  const unsigned lane = threadIdx.x;
+  const uint32_t per = (a.ntiles + 31) / 32;
+  const uint32_t lo = lane * per < a.ntiles ? lane * per : a.ntiles;
+  const uint32_t hi = lo + per < a.ntiles ? lo + per : a.ntiles;
+  ArrFn f = fn_identity();
+  for (uint32_t t = lo; t < hi; ++t) f = fn_compose(f, a.tile_fn[t]);
+  const ArrFn inc = fn_warp_scan(f);
+  ArrFn prev = fn_shfl_up(inc, 1);
+  if (lane == 0) prev = fn_identity();
   ArrState st;
   st.c = 0; st.s = 0; st.d = 0;
-  for (uint32_t t = 0; t < a.ntiles; ++t) {
+  st = fn_apply(prev, st);
+  for (uint32_t t = lo; t < hi; ++t) {
     a.tile_in[t] = st;
     st = fn_apply(a.tile_fn[t], st);
   }
-  a.res->arr_final_s = st.s;
-  a.res->arr_final_d = st.d;
+  if (lane == 31) { /* its run is the last one (possibly empty): the state after every tile */
+    a.res->arr_final_s = st.s;
+    a.res->arr_final_d = st.d;
+  }
 }
 
 static __global__ void __launch_bounds__(ARR_THREADS) k_arr_mark(const __grid_constant__ ArrArgs a) {

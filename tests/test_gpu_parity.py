@@ -386,6 +386,18 @@ def test_array_framing_generated(ctx, oracle, schema, flags):
     assert same_result(want, pj.gen_columns(schema, 0x5EED, 0, 20000, flags, text.size)) == ""
 
 
+def test_array_framing_over_many_tiles(ctx, oracle):
+    """A 10 MB array: hundreds of 16 KiB index tiles, so every lane of the tile scan has a run of its own."""
+    text = pj.gen_text(1, 77, 0, 30000, abi.PJ_GEN_ARRAY | abi.PJ_GEN_WHITESPACE | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_MALFORMED)
+    want = oracle.parse(1, text, ARRAY)
+    got = gpu_parse_device(ctx, 1, text, ARRAY)
+    assert same_result(want, got) == "" and same_doc(want, got)
+    for cut in (text.size - 1, text.size // 2 + 1, 16384 * 33 + 5):  # documents that end early, inside whatever they end in
+        want = oracle.parse(1, text[:cut], ARRAY)
+        got = gpu_parse_device(ctx, 1, text[:cut], ARRAY)
+        assert same_result(want, got) == "" and same_doc(want, got), cut
+
+
 def test_array_framing_mutated(ctx, oracle):
     rng = random.Random(99)
     special = [b'"', b"\\", b"\\\\", b'\\"', b"[", b"]", b"{", b"}", b",", b" ", b"\n", b"\\" * 63, b"\\" * 64, b"\\" * 65, b'"a,b]"', b"[]", b"x"]
