@@ -201,16 +201,42 @@ PJ_HD void wr_prefetch_row(const DevCols* c, uint64_t row) {
   }
 }
 
-/* property I of OBJ and, by recursion, the ones after it */
-template <bool WR, bool PLAIN, int OBJ, int LEVEL, int I = 0>
-PJ_HD void fwrite_fields(const DevCols* c, uint64_t row, int incl, uint32_t present, bool& first, WOut& w) {
+/* Every row-indexed value of one object, loaded before any of them is used: the loads are issued back to back and
+ * their latencies overlap, instead of one load per property each waiting behind the stores of the one before.
+ * Indexed with constants only, so it lives in registers. */
+struct RowSnap {
+  int64_t v[8];       /* I64 / I32 / BOOL / ENUM value, DATETIME seconds */
+  uint32_t a[8], b[8]; /* STR / LIST offsets of the row and of the next one; DATETIME nanos and offset */
+  uint32_t present;
+};
+template <int OBJ, int I = 0>
+PJ_HD void snap_row(const DevCols* c, uint64_t row, RowSnap& r) {
+  if constexpr (I == 0) r.present = colp<uint8_t>(c, CObj<OBJ>::present_col)[row];
   if constexpr (I < CObj<OBJ>::N) {
     constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col;
-    const bool pr = (present >> I) & 1;
+    if constexpr (kind == K_I64) r.v[I] = colp<int64_t>(c, col)[row];
+    else if constexpr (kind == K_I32) r.v[I] = colp<int32_t>(c, col)[row];
+    else if constexpr (kind == K_BOOL || kind == K_ENUM) r.v[I] = colp<uint8_t>(c, col)[row];
+    else if constexpr (kind == K_DATETIME) {
+      r.v[I] = colp<int64_t>(c, col)[row];
+      r.a[I] = (uint32_t)colp<int32_t>(c, col + 1)[row]; r.b[I] = (uint32_t)colp<int32_t>(c, col + 2)[row];
+    } else if constexpr (kind == K_STR || kind == K_LIST_STR || kind == K_LIST_OBJ) {
+      r.a[I] = colp<uint32_t>(c, col)[row]; r.b[I] = colp<uint32_t>(c, col)[row + 1];
+    }
+    snap_row<OBJ, I + 1>(c, row, r);
+  }
+}
+
+/* property I of OBJ and, by recursion, the ones after it */
+template <bool WR, bool PLAIN, int OBJ, int LEVEL, int I = 0>
+PJ_HD void fwrite_fields(const DevCols* c, uint64_t row, int incl, const RowSnap& r, bool& first, WOut& w) {
+  if constexpr (I < CObj<OBJ>::N) {
+    constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col;
+    const bool pr = (r.present >> I) & 1;
     bool empty = false;
     uint32_t a = 0, b = 0;
     if constexpr (kind == K_STR || kind == K_LIST_STR || kind == K_LIST_OBJ) {
-      a = colp<uint32_t>(c, col)[row]; b = colp<uint32_t>(c, col)[row + 1];
+      a = r.a[I]; b = r.b[I];
       empty = a == b;
       if constexpr (!WR && PLAIN) {
         /* the measuring pass does not look at string bytes or child rows here: ask for them now, the writing pass
@@ -227,15 +253,14 @@ PJ_HD void fwrite_fields(const DevCols* c, uint64_t row, int incl, uint32_t pres
       first = false;
       fput_const<WR>(w, FK<OBJ, I>::pat0, FK<OBJ, I>::pat1, FK<OBJ, I>::pat_len); /* "name": */
       if (!pr) fput_const<WR>(w, 0x6C6C756Eull, 0, 4); /* null */
-      else if constexpr (kind == K_I64) fput_i64<WR>(w, colp<int64_t>(c, col)[row]);
-      else if constexpr (kind == K_I32) fput_i64<WR>(w, colp<int32_t>(c, col)[row]);
+      else if constexpr (kind == K_I64 || kind == K_I32) fput_i64<WR>(w, r.v[I]);
       else if constexpr (kind == K_BOOL) {
-        if (colp<uint8_t>(c, col)[row]) fput_const<WR>(w, 0x65757274ull, 0, 4); else fput_const<WR>(w, 0x65736C6166ull, 0, 5);
+        if (r.v[I]) fput_const<WR>(w, 0x65757274ull, 0, 4); else fput_const<WR>(w, 0x65736C6166ull, 0, 5);
       } else if constexpr (kind == K_ENUM) {
         constexpr int E = FK<OBJ, I>::child;
-        fput_enum<WR, E>(w, colp<uint8_t>(c, col)[row] % (uint32_t)CEnum<E>::N);
+        fput_enum<WR, E>(w, (uint32_t)r.v[I] % (uint32_t)CEnum<E>::N);
       } else if constexpr (kind == K_DATETIME) {
-        wput_datetime<WR>(w, colp<int64_t>(c, col)[row], colp<int32_t>(c, col + 1)[row], colp<int32_t>(c, col + 2)[row]);
+        wput_datetime<WR>(w, r.v[I], (int32_t)r.a[I], (int32_t)r.b[I]);
       } else if constexpr (kind == K_STR) {
         fput_str<WR, PLAIN>(w, colp<uint8_t>(c, col + 1) + a, b - a);
       } else if constexpr (kind == K_OBJ) {
@@ -264,16 +289,17 @@ PJ_HD void fwrite_fields(const DevCols* c, uint64_t row, int incl, uint32_t pres
         wput<WR>(w, ']');
       }
     }
-    fwrite_fields<WR, PLAIN, OBJ, LEVEL, I + 1>(c, row, incl, present, first, w);
+    fwrite_fields<WR, PLAIN, OBJ, LEVEL, I + 1>(c, row, incl, r, first, w);
   }
 }
 /* LEVEL 0: model root; LEVEL 1: Category / Tag */
 template <bool WR, bool PLAIN, int OBJ, int LEVEL>
 PJ_HD void fwrite_object(const DevCols* c, uint64_t row, int incl, WOut& w) {
-  const uint32_t present = colp<uint8_t>(c, CObj<OBJ>::present_col)[row];
+  RowSnap r;
+  snap_row<OBJ>(c, row, r);
   bool first = true;
   wput<WR>(w, '{');
-  fwrite_fields<WR, PLAIN, OBJ, LEVEL>(c, row, incl, present, first, w);
+  fwrite_fields<WR, PLAIN, OBJ, LEVEL>(c, row, incl, r, first, w);
   wput<WR>(w, '}');
 }
 
