@@ -57,16 +57,32 @@ def lib() -> C.CDLL:
         L.pj_index_records.argtypes = [C.c_void_p, u32, C.c_void_p, u64, u32, C.c_void_p, u64, C.POINTER(u64)]
         L.pj_index_records_static.argtypes = [C.c_void_p, u64, C.c_void_p, u64, C.c_void_p, C.c_void_p]
         L.pj_write.argtypes = [C.c_void_p, u32, u32, C.POINTER(abi.pj_columns), C.c_void_p, u64, u32, C.POINTER(u64)]
-        L.pj_gen_text.argtypes = [u32, u64, u64, u64, u32, C.c_void_p, u64, C.POINTER(u64)]
-        L.pj_gen_columns.argtypes = [u32, u64, u64, u64, u32, C.POINTER(abi.pj_columns)]
         _lib = L
     return _lib
+
+
+GEN_LIB_PATH = os.path.join(_PKG, "libpj_gen.so")
+_gen_lib = None
+
+
+def gen_lib() -> C.CDLL:
+    """The seeded workload generator (host-only C, include/petjson_gen.h): a library of its own, so that a
+    process which needs inputs but not the GPU path (the CPU baseline) maps nothing of libpetjson.so."""
+    global _gen_lib
+    if _gen_lib is None:
+        if not os.path.exists(GEN_LIB_PATH):
+            raise ImportError(f"{GEN_LIB_PATH} is missing: run `python {os.path.join(_PKG, 'build.py')}`")
+        L = C.CDLL(GEN_LIB_PATH)
+        L.pj_gen_text.argtypes = [u32, u64, u64, u64, u32, C.c_void_p, u64, C.POINTER(u64)]
+        L.pj_gen_columns.argtypes = [u32, u64, u64, u64, u32, C.POINTER(abi.pj_columns)]
+        _gen_lib = L
+    return _gen_lib
 
 
 # ---- seeded workloads (host) -------------------------------------------------------------------
 def gen_text(schema: int, seed: int, first: int, n: int, flags: int = 0, out: np.ndarray | None = None) -> np.ndarray:
     """JSON text of records [first, first+n) of stream `seed` as a uint8 array."""
-    L = lib()
+    L = gen_lib()
     ln = u64()
     if out is None:
         L.pj_gen_text(schema, seed, first, n, flags, None, 0, C.byref(ln))
@@ -80,7 +96,7 @@ def gen_text(schema: int, seed: int, first: int, n: int, flags: int = 0, out: np
 def gen_columns(schema: int, seed: int, first: int, n: int, flags: int, text_bytes: int) -> abi.HostColumns:
     """The values of the same records as host columns."""
     hc = abi.HostColumns(schema, abi.default_caps(schema, n, text_bytes))
-    st = lib().pj_gen_columns(schema, seed, first, n, flags, C.byref(hc.raw))
+    st = gen_lib().pj_gen_columns(schema, seed, first, n, flags, C.byref(hc.raw))
     if st != abi.PJ_OK:
         raise PetJsonError(st, "pj_gen_columns")
     return hc

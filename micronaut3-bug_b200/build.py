@@ -15,6 +15,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 LIB = os.path.join(PKG, "libpetjson.so")
+GEN_LIB = os.path.join(PKG, "libpj_gen.so")
 ORACLE_DIR = os.path.join(ROOT, "oracle")
 ORACLE_LIB = os.path.join(ORACLE_DIR, "libpj_oracle.so")
 FACADE_DEMO = os.path.join(PKG, "host", "object_mapper_demo")
@@ -42,17 +43,15 @@ def _sources(d: str, exts: tuple[str, ...]) -> list[str]:
 
 
 def build_library(force: bool = False, verbose_ptxas: bool = False) -> str:
-    deps = _sources(CSRC, (".cu", ".cuh", ".h", ".c")) + [os.path.join(INCLUDE, "petjson.h")]
+    deps = _sources(CSRC, (".cu", ".cuh", ".h")) + [os.path.join(INCLUDE, "petjson.h")]
     if not force and _newer(LIB, deps):
         return LIB
     from concurrent.futures import ThreadPoolExecutor
 
     nvcc = os.environ.get("NVCC", "nvcc")
     extra = ["-Xptxas", "-v"] if verbose_ptxas else []
-    gen_o = os.path.join(CSRC, "pj_gen.o")
     api_o = os.path.join(CSRC, "pj_api.o")
-    jobs = [["gcc", "-O2", "-std=c11", "-fPIC", "-Wall", "-I", INCLUDE, "-c", os.path.join(CSRC, "pj_gen.c"), "-o", gen_o],
-            [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, "pj_api.cu"), "-o", api_o]]
+    jobs = [[nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, "pj_api.cu"), "-o", api_o]]
     tile_objs = []
     for schema in (1, 2, 3, 4):  # the tile kernel once per model set (Pet, Order, User, mixed), side by side
         obj = os.path.join(CSRC, f"pj_tile_{schema}.o")
@@ -60,8 +59,17 @@ def build_library(force: bool = False, verbose_ptxas: bool = False) -> str:
         jobs.append([nvcc, *NVCC_FLAGS, *extra, f"-DPJ_TILE_SCHEMA={schema}", "-c", os.path.join(CSRC, "pj_tile_inst.cu"), "-o", obj])
     with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
         list(pool.map(_run, jobs))
-    _run([nvcc, "-shared", "-o", LIB, api_o, *tile_objs, gen_o, "-lm"])
+    _run([nvcc, "-shared", "-o", LIB, api_o, *tile_objs])
     return LIB
+
+
+def build_generator(force: bool = False) -> str:
+    """The seeded workload generator: host-only C, a library of its own (no CUDA, no link to libpetjson.so)."""
+    src = os.path.join(PKG, "gen", "pj_gen.c")
+    if not force and _newer(GEN_LIB, [src, os.path.join(INCLUDE, "petjson.h"), os.path.join(INCLUDE, "petjson_gen.h")]):
+        return GEN_LIB
+    _run(["gcc", "-O2", "-std=c11", "-fPIC", "-shared", "-Wall", "-I", INCLUDE, src, "-o", GEN_LIB, "-lm"])
+    return GEN_LIB
 
 
 def build_oracle(force: bool = False) -> str:
@@ -87,6 +95,7 @@ def build_facade_demo(force: bool = False) -> str:
 
 def build_all(force: bool = False) -> None:
     build_library(force)
+    build_generator(force)
     build_oracle(force)
     build_facade_demo(force)
 

@@ -16,7 +16,7 @@
 #include <stdlib.h>
 #include <string.h>
 
-#include "petjson.h"
+#include "petjson_gen.h"
 
 /* ------------------------------------------------------------------------------------------ */
 /* counter-based randomness                                                                    */

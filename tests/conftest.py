@@ -23,6 +23,7 @@ def native():
     from pj_testlib import build, pj
 
     build.build_library()
+    build.build_generator()
     return pj
 
 

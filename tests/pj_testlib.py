@@ -15,6 +15,7 @@ if ROOT not in sys.path:
 pj = importlib.import_module("micronaut3-bug_b200")
 abi = importlib.import_module("micronaut3-bug_b200.abi")
 build = importlib.import_module("micronaut3-bug_b200.build")
+build.build_generator()  # host-only C: the seeded inputs of every test
 
 u32, u64 = C.c_uint32, C.c_uint64
 

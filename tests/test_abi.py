@@ -10,18 +10,23 @@ import pytest
 from pj_testlib import ROOT, abi, pj
 
 
-def declared_functions():
-    text = open(os.path.join(ROOT, "include", "petjson.h")).read()
+def declared_functions(header="petjson.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(pj_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_every_declared_symbol_is_exported(native):
     names = declared_functions()
-    assert {"pj_create", "pj_destroy", "pj_parse", "pj_parse_shard", "pj_write", "pj_index_records", "pj_gen_text"} <= set(names)
+    assert {"pj_create", "pj_destroy", "pj_parse", "pj_parse_shard", "pj_write", "pj_index_records"} <= set(names)
     L = native.lib()
     for n in names:
         assert hasattr(L, n), n
+    gen = declared_functions("petjson_gen.h")
+    assert {"pj_gen_text", "pj_gen_columns"} <= set(gen)
+    for n in gen:
+        assert hasattr(native.gen_lib(), n), n
+        assert not hasattr(L, n), "the generator is not part of the GPU library"
 
 
 def test_no_entry_point_takes_a_library_type():
