@@ -239,22 +239,22 @@ typedef struct pj_columns {
   pj_buf col[PJ_MAX_COLS];
 } pj_columns;
 
-/* pj_options.flags */
-enum {
-  PJ_OPT_STAGED_PIPELINE = 1u << 0 /* parse with the multi-pass pipeline (index, size pass, scans, emit pass)
-                                      instead of the single-pass tile kernel; same results, kept for cross-checks */
-};
-
 typedef struct pj_options {
   int32_t device;            /* CUDA device ordinal; -1 = the calling thread's current device   */
   int32_t inclusion;         /* PJ_INCLUDE_* for pj_write                                       */
   void* stream;              /* a cudaStream_t to run on, or NULL for a stream the context owns */
-  uint32_t flags;            /* PJ_OPT_* bits                                                   */
+  uint32_t flags;            /* PJ_OPT_* bits (none defined: must be 0)                         */
   uint32_t host_piece_bytes; /* pj_parse with host input and host columns (NDJSON): the input is cut after
                                 line feeds into pieces of about this many bytes (at most 16), and the copy of
-                                one piece to the device, the kernels of the previous one and the copy of the
-                                columns of the one before run at the same time. 0 = 64 MiB; 0xFFFFFFFF = never
+                                one piece to the device, the kernel of the previous one and the copy of the
+                                columns of the one before run at the same time. 0 = 32 MiB; 0xFFFFFFFF = never
                                 cut. The result does not depend on it.                            */
+  uint32_t tile_bytes;       /* NDJSON: input bytes per thread block of the parse kernel (1024 .. 32768, rounded
+                                down to a multiple of 16). 0 = chosen by the library from the bytes per record
+                                of the context's earlier calls. The result does not depend on it.  */
+  uint32_t spin_limit_us;    /* bound, in microseconds, of every wait of a thread block on another one or on
+                                its staging copy; when one runs out the call answers PJ_ERR_TIMEOUT and the
+                                context stays usable. 0 = 2 seconds.                               */
 } pj_options;
 
 typedef struct pj_ctx pj_ctx;
@@ -265,12 +265,11 @@ typedef struct pj_call_stats {
   uint32_t pieces;          /* pj_parse: pieces the input was parsed in (see pj_options.host_piece_bytes) */
   float device_ms;          /* CUDA-event time from first launch to last, on the call's stream  */
   float main_kernel_ms;     /* CUDA-event time of the dominant kernel(s) of the call            */
-  float stage_ms[8];        /* CUDA-event time per stage. parse: [0] record index, [1] set-up between
-                               the kernels (record count read-back, state reset), [2] the tile kernel
-                               (with PJ_OPT_STAGED_PIPELINE: [1] size pass, [2] counter scans, [3] emit
-                               pass, [4] closing offsets); write: [0] state reset and the scan of the string arenas for bytes
-                               to escape, [1] the closing kernel, [2] the
-                               tile kernel (with PJ_OPT_STAGED_PIPELINE: [0] size pass, [1] scan, [2] emit pass) */
+  float stage_ms[8];        /* CUDA-event time per stage. parse, NDJSON: [2] the parse kernel(s), nothing else
+                               runs; parse, array framing: [0] record index, [1] set-up between the kernels
+                               (record count read-back, state reset), [2] the tile kernel; write: [0] state
+                               reset and the scan of the string arenas for bytes to escape, [1] the closing
+                               kernel, [2] the tile kernel */
   uint32_t stage_launches[8]; /* kernels launched per stage                                      */
   uint64_t h2d_bytes;       /* bytes copied host->device by the call                            */
   uint64_t d2h_bytes;       /* bytes copied device->host by the call                            */

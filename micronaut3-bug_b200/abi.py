@@ -29,8 +29,6 @@ PJ_INCLUDE_NON_EMPTY, PJ_INCLUDE_NON_NULL, PJ_INCLUDE_ALWAYS = 0, 1, 2
 PJ_GEN_ZIPF_LISTS, PJ_GEN_ESCAPES, PJ_GEN_WHITESPACE, PJ_GEN_MALFORMED, PJ_GEN_ARRAY, PJ_GEN_SPARSE = (
     1, 2, 4, 8, 16, 32)
 
-PJ_OPT_STAGED_PIPELINE = 1
-
 PJ_MAX_COLS = 64
 
 
@@ -120,7 +118,7 @@ class pj_columns(C.Structure):
 
 class pj_options(C.Structure):
     _fields_ = [("device", C.c_int32), ("inclusion", C.c_int32), ("stream", C.c_void_p),
-                ("flags", C.c_uint32), ("host_piece_bytes", C.c_uint32)]
+                ("flags", C.c_uint32), ("host_piece_bytes", C.c_uint32), ("tile_bytes", C.c_uint32), ("spin_limit_us", C.c_uint32)]
 
 
 class pj_call_stats(C.Structure):

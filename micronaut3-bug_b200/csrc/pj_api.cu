@@ -14,6 +14,7 @@
 #include "petjson.h"
 #include "pj_kernels.cuh"
 #include "pj_array_kernels.cuh"
+#include "pj_stream_kernel.cuh"
 
 using namespace pj;
 
@@ -23,6 +24,8 @@ cudaError_t tile_init_1(const Schema*); cudaError_t tile_launch_1(const TileArgs
 cudaError_t tile_init_2(const Schema*); cudaError_t tile_launch_2(const TileArgs*, unsigned, cudaStream_t);
 cudaError_t tile_init_3(const Schema*); cudaError_t tile_launch_3(const TileArgs*, unsigned, cudaStream_t);
 cudaError_t tile_init_4(const Schema*); cudaError_t tile_launch_4(const TileArgs*, unsigned, cudaStream_t);
+cudaError_t stream_launch_1(const StreamArgs*, unsigned, cudaStream_t); cudaError_t stream_launch_2(const StreamArgs*, unsigned, cudaStream_t);
+cudaError_t stream_launch_3(const StreamArgs*, unsigned, cudaStream_t); cudaError_t stream_launch_4(const StreamArgs*, unsigned, cudaStream_t);
 }
 
 namespace {
@@ -81,6 +84,7 @@ struct Buffer {
 
 }  // namespace
 
+enum { PJ_CTX_RESULTS = 16 };
 struct pj_ctx {
   int device = 0;
   int inclusion = PJ_INCLUDE_NON_EMPTY;
@@ -91,14 +95,19 @@ struct pj_ctx {
   Buffer col_stage; /* device copies of host columns */
   Buffer out_stage; /* device copy of a host output (writer) */
   Buffer tiles;     /* look-back state of the tile kernel + its ticket */
-  bool staged = false; /* use the multi-pass pipeline instead of the tile kernel */
-  DevResult* d_res = nullptr;
-  DevResult* h_res = nullptr; /* pinned */
+  DevResult* d_res = nullptr; /* [PJ_CTX_RESULTS]: one per piece of a call; [0] serves every other call */
+  DevResult* h_res = nullptr; /* pinned, same shape */
   cudaEvent_t ev[10] = {};
+  cudaEvent_t ev_k0[16] = {}, ev_k1[16] = {}; /* around the kernel of every piece */
+  cudaEvent_t ev_done[16] = {};               /* the totals of a piece have reached the host */
+  uint32_t tile_bytes_opt = 0;                /* pj_options.tile_bytes */
+  unsigned long long spin_ns = 2000000000ull; /* bound of every device-side wait */
+  double avg_rec_bytes[5] = {0, 0, 0, 0, 0};  /* bytes per record seen per schema (sizes the tiles of the next call) */
   /* host buffers parsed in pieces: copy streams and one "piece is on the device" event per piece */
   cudaStream_t s_in = nullptr, s_out = nullptr;
   cudaEvent_t ev_in[16] = {};
   uint32_t piece_bytes = 0;
+  uint32_t opt_flags = 0;
   Schema schema;
   pj_call_stats stats = {};
   char err[256] = "";
@@ -160,27 +169,12 @@ void collect_times(pj_ctx* c, int stages) {
 }
 
 enum { MAX_PIECES = 16 };
-static constexpr uint64_t DEFAULT_PIECE_BYTES = 64ull << 20;
+static constexpr uint64_t DEFAULT_PIECE_BYTES = 32ull << 20;
 pj_status ensure_pipe_streams(pj_ctx* c) {
   if (c->s_in) return PJ_OK;
   PJ_CUDA(c, cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking));
   PJ_CUDA(c, cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking));
   for (auto& ev : c->ev_in) PJ_CUDA(c, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
-  return PJ_OK;
-}
-
-pj_status run_scan_u32(pj_ctx* c, uint32_t* data, uint64_t stride, uint32_t nslots, uint32_t slot_lo, uint64_t n_cap,
-                       uint32_t* partial, uint32_t nchunks, int stage) {
-  if (!nslots) return PJ_OK;
-  ScanArgs a;
-  a.data = data; a.stride = stride; a.partial = partial; a.nchunks = nchunks; a.slot_lo = slot_lo;
-  a.n_dev = &c->d_res->n_records; a.n_cap = n_cap; a.totals = c->d_res->total;
-  dim3 grid(nchunks, nslots);
-  k_scan_reduce<uint32_t><<<grid, SCAN_THREADS, 0, c->stream>>>(a);
-  k_scan_mid<uint32_t><<<nslots, 1024, 0, c->stream>>>(a);
-  k_scan_apply<uint32_t><<<grid, SCAN_THREADS, 0, c->stream>>>(a);
-  count_launch(c, stage, 3);
-  PJ_CUDA(c, cudaGetLastError());
   return PJ_OK;
 }
 
@@ -193,43 +187,117 @@ int persistent_grid(pj_ctx* c, uint64_t items, int threads) {
   return (int)(want < cap ? want : cap);
 }
 
-pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack,
-                     int is_first, int is_last, uint64_t goff, uint32_t in_kind, pj_columns* out) {
-  if (!c) return PJ_ERR_ARG;
-  if (!out || (!in && len + slack) || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED || in_kind > PJ_MEM_DEVICE ||
-      out->mem_kind > PJ_MEM_DEVICE)
-    return set_err(c, PJ_ERR_ARG, "pj_parse: bad argument");
-  if (framing > PJ_FRAMING_ARRAY) return set_err(c, PJ_ERR_ARG, "pj_parse: unknown framing %u", framing);
-  const bool array = framing == PJ_FRAMING_ARRAY;
-  if (array && (slack || !is_first || !is_last)) return set_err(c, PJ_ERR_ARG, "pj_parse: array framing cannot be sharded");
+/* What a parse call needs to know about the caller's columns. */
+struct ParsePlan {
+  FinalizePlan plan;
+  int rcols[5], nrc;          /* per-record columns */
+  int need[PJ_MAX_COLS], nneed; /* every column the schema fills */
+  uint64_t cap_elems[PJ_MAX_COLS];
+  uint64_t rec_cap;           /* records that fit every per-record and row-indexed buffer */
+  uint64_t slot_cap[NSLOT];   /* largest total of every counter the buffers can take */
+  DevCols dcols;              /* device addresses of the columns (the caller's, or the staging copies) */
+};
+
+pj_status plan_columns(pj_ctx* c, uint32_t schema, pj_columns* out, uint64_t limit, bool array, ParsePlan* pp) {
+  memset(pp, 0, sizeof *pp);
+  build_finalize_plan(c->schema, schema, &pp->plan);
+  pp->nrc = record_cols(schema, pp->rcols);
+  for (int i = 0; i < pp->nrc; ++i) pp->need[pp->nneed++] = pp->rcols[i];
+  for (uint32_t k = 0; k < pp->plan.n; ++k) pp->need[pp->nneed++] = pp->plan.item[k].col;
+  for (int i = 0; i < pp->nneed; ++i)
+    if (!out->col[pp->need[i]].ptr) return set_err(c, PJ_ERR_ARG, "pj_parse: column %s has no buffer", col_info(pp->need[i])->name);
+  const bool host_out = out->mem_kind == PJ_MEM_HOST;
+  if (host_out) {
+    size_t tot = 0;
+    for (int i = 0; i < pp->nneed; ++i) tot += align_up(out->col[pp->need[i]].bytes, 256);
+    pj_status st = ensure(c, &c->col_stage, tot + 256);
+    if (st) return st;
+    size_t at = 0;
+    for (int i = 0; i < pp->nneed; ++i) { pp->dcols.ptr[pp->need[i]] = (uint8_t*)c->col_stage.p + at; at += align_up(out->col[pp->need[i]].bytes, 256); }
+  } else {
+    for (int i = 0; i < pp->nneed; ++i) pp->dcols.ptr[pp->need[i]] = out->col[pp->need[i]].ptr;
+  }
+  for (int i = 0; i < pp->nneed; ++i) pp->cap_elems[pp->need[i]] = out->col[pp->need[i]].bytes / col_info(pp->need[i])->elem;
+  /* records: every per-record column and every column with one row per record (less the closing entry of offsets) */
+  uint64_t cap_all = ~0ull;
+  for (int i = 0; i < pp->nrc; ++i) if (pp->cap_elems[pp->rcols[i]] < cap_all) cap_all = pp->cap_elems[pp->rcols[i]];
+  for (uint32_t k = 0; k < NSLOT; ++k) pp->slot_cap[k] = ~0ull;
+  for (uint32_t k = 0; k < pp->plan.n; ++k) {
+    const FinalizeItem& it = pp->plan.item[k];
+    uint64_t room = pp->cap_elems[it.col];
+    if (it.sentinel_slot != 0xFF) room = room ? room - 1 : 0;
+    if (it.rows_slot == 0xFF) { if (room < cap_all) cap_all = room; }
+    else if (room < pp->slot_cap[it.rows_slot]) pp->slot_cap[it.rows_slot] = room;
+  }
+  if (cap_all > (1ull << 32)) cap_all = 1ull << 32;
+  /* no more records than candidate line starts (NDJSON: a record needs a byte and an LF) or separators (array) */
+  if (!array && cap_all > limit / 2 + 2) cap_all = limit / 2 + 2;
+  if (array && cap_all > limit + 2) cap_all = limit + 2;
+  pp->rec_cap = cap_all;
+  return PJ_OK;
+}
+
+/* What the caller gets back once the totals are known. */
+pj_status finish_columns(pj_ctx* c, uint32_t schema, uint64_t len, const ParsePlan& pp, uint64_t N, uint64_t n_errors, const uint64_t* total, bool over, pj_columns* out) {
+  out->schema = schema;
+  out->n_records = N;
+  out->n_errors = n_errors;
+  for (int t = 0; t < 4; ++t) out->n_rows[t] = 0;
+  if (schema == PJ_SCHEMA_MIXED) { out->n_rows[1] = total[SLOT_ROWS_PET]; out->n_rows[2] = total[SLOT_ROWS_ORD]; out->n_rows[3] = total[SLOT_ROWS_USR]; }
+  else out->n_rows[schema] = N;
+  for (int i = 0; i < pp.nrc; ++i) out->col[pp.rcols[i]].count = N;
+  for (uint32_t k = 0; k < pp.plan.n; ++k) {
+    const FinalizeItem& it = pp.plan.item[k];
+    const uint64_t rows = it.rows_slot == 0xFF ? N : total[it.rows_slot];
+    out->col[it.col].count = rows + (it.sentinel_slot != 0xFF ? 1 : 0);
+  }
+  uint64_t alg = len;
+  for (int i = 0; i < pp.nneed; ++i) alg += out->col[pp.need[i]].count * col_info(pp.need[i])->elem;
+  c->stats.algorithmic_bytes = alg;
+  if (over) return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records need larger output buffers", (unsigned long long)N);
+  return PJ_OK;
+}
+
+/* Tile size of the stream kernel: about 104 records per tile of 128 threads, from the bytes per record the context
+ * saw in its earlier calls on the schema (before the first one: from the benchmark distributions). The result of a
+ * call does not depend on it. */
+uint32_t pick_tile_bytes(const pj_ctx* c, uint32_t schema) {
+  uint64_t tb;
+  if (c->tile_bytes_opt) tb = c->tile_bytes_opt;
+  else {
+    static const double dflt[5] = {0, 300, 125, 190, 220};
+    const double avg = c->avg_rec_bytes[schema] > 0 ? c->avg_rec_bytes[schema] : dflt[schema];
+    tb = (uint64_t)(avg * 104.0);
+  }
+  tb &= ~15ull;
+  if (tb < ST_MIN_TILE_BYTES) tb = ST_MIN_TILE_BYTES;
+  if (tb > ST_MAX_TILE_BYTES) tb = ST_MAX_TILE_BYTES;
+  return (uint32_t)tb;
+}
+
+cudaError_t stream_launch(uint32_t schema, const StreamArgs* a, unsigned grid, cudaStream_t s) {
+  switch (schema) {
+    case PJ_SCHEMA_PET: return stream_launch_1(a, grid, s);
+    case PJ_SCHEMA_ORDER: return stream_launch_2(a, grid, s);
+    case PJ_SCHEMA_USER: return stream_launch_3(a, grid, s);
+    default: return stream_launch_4(a, grid, s);
+  }
+}
+
+/* NDJSON: one launch of k_parse_stream per piece. Host buffers of a whole stream are parsed in pieces cut after line
+ * feeds, so that the copy of piece p+1 to the device, the kernel of piece p and the copy of the columns of piece p-1
+ * back run at the same time on three streams. Every launch is enqueued before the host waits for anything: a piece
+ * starts where the piece before it ended, which it reads from that piece's totals ON THE DEVICE (StreamArgs.prev). */
+pj_status parse_stream(pj_ctx* c, uint32_t schema, const uint8_t* in, uint64_t len, uint64_t slack, int is_first, int is_last,
+                       uint64_t goff, uint32_t in_kind, pj_columns* out) {
   const uint64_t limit = len + slack;
-  if (limit >= (1ull << 32)) return set_err(c, PJ_ERR_TOO_LARGE, "pj_parse: %llu input bytes do not fit 32-bit offsets", (unsigned long long)limit);
-  DeviceGuard guard(c->device);
-  c->stats = pj_call_stats{};
-
-  /* columns of this schema */
-  FinalizeArgs fa;
-  memset(&fa, 0, sizeof fa);
-  build_finalize_plan(c->schema, schema, &fa.plan);
-  int rcols[5];
-  const int nrc = record_cols(schema, rcols);
-  int need[PJ_MAX_COLS], nneed = 0;
-  for (int i = 0; i < nrc; ++i) need[nneed++] = rcols[i];
-  for (uint32_t k = 0; k < fa.plan.n; ++k) need[nneed++] = fa.plan.item[k].col;
-  for (int i = 0; i < nneed; ++i)
-    if (!out->col[need[i]].ptr) return set_err(c, PJ_ERR_ARG, "pj_parse: column %s has no buffer", col_info(need[i])->name);
-
-  /* Pieces. Host buffers of an LF-delimited stream are parsed in pieces cut after line feeds, so that the
-     copy of piece p+1 to the device, the kernels of piece p and the copy of piece p-1's columns back run at
-     the same time on three streams. A piece is a complete input of its own (it starts at a line start and
-     ends with a line feed); what ties the pieces together is where each one starts in the columns: its first
-     row (pointers of the row-indexed columns are advanced) and its first byte / item in every arena and
-     child table (TileArgs.slot_base). */
+  ParsePlan pp;
+  { pj_status st = plan_columns(c, schema, out, limit, false, &pp); if (st) return st; }
   const bool host_in = in_kind == PJ_MEM_HOST, host_out = out->mem_kind == PJ_MEM_HOST;
   uint64_t cut[MAX_PIECES + 1];
   int np = 1;
   cut[0] = 0; cut[1] = len;
-  if (host_in && host_out && !array && !c->staged && slack == 0 && is_first && is_last && c->piece_bytes != 0xFFFFFFFFu) {
+  if (host_in && host_out && slack == 0 && is_first && is_last && c->piece_bytes != 0xFFFFFFFFu) {
     const uint64_t piece = c->piece_bytes ? c->piece_bytes : DEFAULT_PIECE_BYTES;
     uint64_t want = len / piece;
     if (want > MAX_PIECES) want = MAX_PIECES;
@@ -253,7 +321,6 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
     ~Drain() { if (pipe) { cudaStreamSynchronize(c->s_in); cudaStreamSynchronize(c->stream); cudaStreamSynchronize(c->s_out); } }
   } drain{c, pipe};
 
-  /* stage host memory */
   const uint8_t* d_in = in;
   if (host_in && limit) {
     pj_status st = ensure(c, &c->in_stage, limit + 64);
@@ -267,237 +334,77 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
       c->stats.h2d_bytes += nb;
     }
   }
-  DevCols dcols;
-  memset(&dcols, 0, sizeof dcols);
-  if (host_out) {
-    size_t tot = 0;
-    for (int i = 0; i < nneed; ++i) tot += align_up(out->col[need[i]].bytes, 256);
-    pj_status st = ensure(c, &c->col_stage, tot + 256);
-    if (st) return st;
-    size_t at = 0;
-    for (int i = 0; i < nneed; ++i) { dcols.ptr[need[i]] = (uint8_t*)c->col_stage.p + at; at += align_up(out->col[need[i]].bytes, 256); }
-  } else {
-    for (int i = 0; i < nneed; ++i) dcols.ptr[need[i]] = out->col[need[i]].ptr;
-  }
-  uint64_t cap_all = ~0ull;
-  for (int i = 0; i < nneed; ++i) fa.cap_elems[need[i]] = out->col[need[i]].bytes / col_info(need[i])->elem;
-  for (int i = 0; i < nrc; ++i) if (fa.cap_elems[rcols[i]] < cap_all) cap_all = fa.cap_elems[rcols[i]];
-  if (cap_all > (1ull << 32)) cap_all = 1ull << 32;
-  /* no more records than candidate line starts (NDJSON: a record needs a byte and an LF) or separators (array) */
-  if (!array && cap_all > limit / 2 + 2) cap_all = limit / 2 + 2;
-  if (array && cap_all > limit + 2) cap_all = limit + 2;
-  fa.res = c->d_res;
 
-  /* scratch, sized for the whole input (no piece needs more) */
-  uint32_t slot_lo, slot_hi;
-  slot_range(schema, &slot_lo, &slot_hi);
-  const uint32_t nslots = slot_hi - slot_lo;
-  const uint64_t max_index_tiles = (len + 15 + INDEX_TILE) / INDEX_TILE; /* covers the worst misalignment of `in` */
-  const uint64_t stride = align_up(cap_all + 1, 4);
-  const uint32_t nchunks = (uint32_t)((cap_all + 1 + SCAN_CHUNK - 1) / SCAN_CHUNK);
-  size_t off_tile = 0;
-  size_t off_cnt = align_up(off_tile + ((max_index_tiles > (len >> 14) + 2 ? max_index_tiles : (len >> 14) + 2) + 1) * 4, 256);
-  size_t off_part = align_up(off_cnt + (c->staged ? (size_t)nslots * stride * 4 : 0), 256);
-  size_t off_arr = align_up(off_part + (c->staged ? (size_t)nslots * nchunks * 4 : 0), 256);
-  const uint64_t nwords = (len + 63) >> 6;
-  const uint64_t atiles = nwords ? (nwords + ARR_THREADS - 1) / ARR_THREADS : 1;
-  size_t off_fn = off_arr, off_tin = 0, off_sep = 0, off_rend = 0, off_rblank = 0, total_scratch = off_arr + 256;
-  if (array) {
-    off_tin = align_up(off_fn + atiles * sizeof(ArrFn), 256);
-    off_sep = align_up(off_tin + atiles * sizeof(ArrState), 256);
-    off_rend = align_up(off_sep + (nwords + 1) * 8, 256);
-    off_rblank = align_up(off_rend + cap_all * 8, 256);
-    total_scratch = off_rblank + cap_all + 256;
+  const uint32_t tile_bytes = pick_tile_bytes(c, schema);
+  /* look-back states: one buffer per piece, so that no launch waits for the one before it to be read back */
+  uint64_t nt[MAX_PIECES], nt_total = 0;
+  for (int p = 0; p < np; ++p) {
+    const uint8_t* pin = d_in ? d_in + cut[p] : d_in;
+    const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(pin) & 15u);
+    nt[p] = stream_tiles(mis, cut[p + 1] - cut[p], 1u, tile_bytes); /* at least one tile: it closes the offset columns */
+    if (nt[p] >= (1ull << 31)) return set_err(c, PJ_ERR_TOO_LARGE, "pj_parse: too many tiles");
+    nt_total += nt[p];
   }
-  { pj_status st = ensure(c, &c->scratch, total_scratch); if (st) return st; }
-  uint32_t* d_tile = (uint32_t*)((uint8_t*)c->scratch.p + off_tile);
-  uint32_t* d_cnt = (uint32_t*)((uint8_t*)c->scratch.p + off_cnt);
-  uint32_t* d_part = (uint32_t*)((uint8_t*)c->scratch.p + off_part);
+  { pj_status st = ensure(c, &c->tiles, nt_total * sizeof(StreamTile) + (size_t)np * 256 + 256); if (st) return st; }
+  PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, nt_total * sizeof(StreamTile) + (size_t)np * 256, c->stream));
+  PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult) * np, c->stream));
+  c->stats.tile_records = ST_THREADS;
+  uint64_t tiles_at = 0;
+  for (int p = 0; p < np; ++p) {
+    StreamArgs sa;
+    memset(&sa, 0, sizeof sa);
+    const uint64_t plen = cut[p + 1] - cut[p];
+    sa.in = d_in ? d_in + cut[p] : d_in;
+    sa.len = plen; sa.limit = plen + (p == np - 1 ? slack : 0); sa.goff = goff + cut[p];
+    sa.is_first = (uint32_t)is_first; sa.is_last = (uint32_t)is_last;
+    sa.tile_bytes = tile_bytes; sa.ntiles = (uint32_t)nt[p];
+    sa.spin_limit_ns = c->spin_ns;
+    sa.ticket = (uint32_t*)((uint8_t*)c->tiles.p + (size_t)p * 256);
+    sa.tiles = (StreamTile*)((uint8_t*)c->tiles.p + (size_t)np * 256) + tiles_at;
+    tiles_at += nt[p];
+    sa.res = c->d_res + p;
+    sa.prev = p ? c->d_res + p - 1 : nullptr;
+    for (uint32_t k = 0; k < NSLOT; ++k) sa.slot_cap[k] = pp.slot_cap[k];
+    sa.rec_cap = pp.rec_cap;
+    sa.plan = pp.plan;
+    sa.cols = pp.dcols;
+    if (pipe) PJ_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_in[p], 0));
+    PJ_CUDA(c, cudaEventRecord(c->ev_k0[p], c->stream));
+    PJ_CUDA(c, stream_launch(schema, &sa, (unsigned)nt[p], c->stream));
+    PJ_CUDA(c, cudaEventRecord(c->ev_k1[p], c->stream));
+    PJ_CUDA(c, cudaMemcpyAsync(c->h_res + p, c->d_res + p, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+    PJ_CUDA(c, cudaEventRecord(c->ev_done[p], c->stream));
+    count_launch(c, 2);
+    c->stats.tiles += (uint32_t)nt[p];
+  }
 
-  /* what the pieces parsed so far have produced */
+  /* the pieces come back one by one; the columns of each go to the host while the later ones are parsed */
   uint64_t rows_done = 0, n_errors = 0, n_fast = 0;
   uint64_t total[NSLOT];
   for (uint32_t k = 0; k < NSLOT; ++k) total[k] = 0;
-  DevResult last{};
-  int n_stages = 5;
-  /* A call that does not fit the caller's buffers still reports what it needs: once the records do not fit
-     (count_only) the remaining pieces are only indexed; once an arena or child table does not fit (over) they are
-     still sized, but nothing more is emitted or copied back. */
-  bool count_only = false, over = false;
-
+  bool over = false;
   for (int p = 0; p < np; ++p) {
-    const uint64_t poff = cut[p], plen = cut[p + 1] - cut[p], plimit = plen + (p == np - 1 ? slack : 0);
-    const uint8_t* pin = d_in ? d_in + poff : d_in;
-    const uint64_t pgoff = goff + poff;
-    const uint64_t cap_records = count_only ? 0 : cap_all - rows_done;
-    /* this piece's view of the columns: row-indexed ones start at its first row */
-    DevCols pcols = dcols;
-    for (int i = 0; i < nrc; ++i) pcols.ptr[rcols[i]] = (uint8_t*)dcols.ptr[rcols[i]] + rows_done * col_info(rcols[i])->elem;
-    for (uint32_t k = 0; k < fa.plan.n; ++k) {
-      const FinalizeItem& it = fa.plan.item[k];
-      if (it.rows_slot == 0xFF) pcols.ptr[it.col] = (uint8_t*)dcols.ptr[it.col] + rows_done * col_info(it.col)->elem;
-    }
-    fa.cap_records = cap_records;
-    fa.cols = pcols;
-    if (pipe) PJ_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_in[p], 0));
-
-    PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream));
-    Stage stage(c);
-
-    /* stage 0: record index */
-    const uint64_t ntiles_index = (plen + 15 + INDEX_TILE) / INDEX_TILE;
-    uint64_t* d_rec_end = nullptr;
-    uint8_t* d_rec_blank = nullptr;
-    if (!array) {
-      IndexArgs ia;
-      ia.in = pin; ia.len = plen; ia.limit = plimit; ia.is_first = is_first; ia.is_last = is_last;
-      ia.tile = d_tile; ia.rec_start = (uint64_t*)pcols.ptr[PJ_COL_REC_START]; ia.cap = cap_records; ia.goff = pgoff;
-      if (c->staged) {
-        k_nd_index<false><<<(unsigned)ntiles_index, INDEX_THREADS, 0, c->stream>>>(ia);
-        k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, ntiles_index, &c->d_res->n_records);
-        k_nd_index<true><<<(unsigned)ntiles_index, INDEX_THREADS, 0, c->stream>>>(ia);
-        count_launch(c, 0, 3);
-      } else {
-        /* one pass: count, look back, write (the look-back state shares the buffer the tile kernel uses afterwards) */
-        const uint64_t nt = (plen + 15 + INDEX_LB_TILE) / INDEX_LB_TILE;
-        { pj_status st = ensure(c, &c->tiles, 256 + nt * 16 + 256); if (st) return st; }
-        IndexLbArgs la;
-        la.ix = ia;
-        la.ticket = (uint32_t*)c->tiles.p;
-        la.agg = (unsigned long long*)((uint8_t*)c->tiles.p + 256);
-        la.inc = la.agg + nt;
-        la.ntiles = (uint32_t)nt;
-        la.res = c->d_res;
-        PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, 256 + nt * 16, c->stream));
-        k_nd_index_lb<<<(unsigned)nt, INDEX_THREADS, 0, c->stream>>>(la);
-        count_launch(c, 0, 1);
-      }
-    } else {
-      d_rec_end = (uint64_t*)((uint8_t*)c->scratch.p + off_rend);
-      d_rec_blank = (uint8_t*)c->scratch.p + off_rblank;
-      ArrArgs aa;
-      aa.in = pin; aa.len = plen; aa.nwords = nwords;
-      aa.tile_fn = (ArrFn*)((uint8_t*)c->scratch.p + off_fn); aa.tile_in = (ArrState*)((uint8_t*)c->scratch.p + off_tin);
-      aa.sep = (uint64_t*)((uint8_t*)c->scratch.p + off_sep); aa.tile_cnt = d_tile;
-      aa.rec_start = (uint64_t*)pcols.ptr[PJ_COL_REC_START]; aa.rec_end = d_rec_end; aa.rec_blank = d_rec_blank;
-      aa.cap = cap_records; aa.goff = pgoff; aa.ntiles = (uint32_t)atiles; aa.res = c->d_res;
-      /* the two running minima start at "none" */
-      PJ_CUDA(c, cudaMemsetAsync(&c->d_res->doc_err_off, 0xFF, sizeof(unsigned long long), c->stream));
-      PJ_CUDA(c, cudaMemsetAsync(&c->d_res->first_opener, 0xFF, sizeof(unsigned long long), c->stream));
-      k_arr_summary<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
-      k_arr_scan_tiles<<<1, 32, 0, c->stream>>>(aa);
-      k_arr_mark<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
-      k_arr_records<false><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
-      k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, atiles, &c->d_res->n_records);
-      k_arr_records<true><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
-      count_launch(c, 0, 6);
-    }
-    PJ_CUDA(c, cudaGetLastError());
-    stage.next();
-
-    if (c->staged) {
-      /* stage 1: size pass */
-      ParseArgs pa;
-      pa.in = pin; pa.limit = plimit; pa.goff = pgoff; pa.cap_records = cap_records;
-      pa.lf_ws = array ? 1u : 0u; pa.open_end = is_last ? 0u : 1u; pa.schema = schema; pa.slot_lo = slot_lo; pa.slot_hi = slot_hi;
-      pa.cnt = d_cnt - (size_t)slot_lo * stride; /* indexed by absolute slot */
-      pa.stride = stride; pa.rec_end = d_rec_end; pa.rec_blank = d_rec_blank; pa.res = c->d_res; pa.cols = pcols;
-      const int pgrid = persistent_grid(c, cap_records, PARSE_THREADS);
-      k_parse_size<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
-      count_launch(c, 1);
-      PJ_CUDA(c, cudaGetLastError());
-      stage.next();
-
-      /* stage 2: where every record starts in every arena */
-      { pj_status st = run_scan_u32(c, d_cnt, stride, nslots, slot_lo, cap_records, d_part, nchunks, 2); if (st) return st; }
-      k_check<<<1, 32, 0, c->stream>>>(fa);
-      count_launch(c, 2);
-      stage.next();
-
-      /* stage 3: emit pass */
-      k_parse_emit<<<pgrid, PARSE_THREADS, 0, c->stream>>>(pa);
-      count_launch(c, 3);
-      PJ_CUDA(c, cudaGetLastError());
-      stage.next();
-
-      /* stage 4: closing offsets */
-      k_finalize<<<1, 64, 0, c->stream>>>(fa);
-      count_launch(c, 4);
-      stage.next();
-    } else {
-      /* the tile kernel needs the record count to size its grid */
-      PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
-      PJ_CUDA(c, cudaStreamSynchronize(c->stream));
-      const uint64_t N0 = c->h_res->n_records;
-      if (count_only || N0 > cap_records) { count_only = true; rows_done += N0; continue; }
-      TileArgs ta;
-      memset(&ta, 0, sizeof ta);
-      ta.in = pin; ta.limit = plimit; ta.goff = pgoff; ta.n_records = N0;
-      ta.lf_ws = array ? 1u : 0u; ta.open_end = is_last ? 0u : 1u; ta.schema = schema; ta.slot_lo = slot_lo; ta.slot_hi = slot_hi;
-      ta.win_bytes = TILE_WIN_BYTES; ta.tape_cap = TILE_TAPE_CAP;
-      /* A tile is always one record per thread: records that miss the staging window are read where they lie, which
-         costs less than idle threads (measured on long records: 128 per tile beat 16, 32 and 64). */
-      const uint32_t tile_recs = TILE_THREADS;
-      ta.tile_recs = tile_recs;
-      const uint64_t ntiles = N0 ? (N0 + tile_recs - 1) / tile_recs : 1;
-      ta.ntiles = (uint32_t)ntiles;
-      c->stats.tile_records = tile_recs; c->stats.tiles += (uint32_t)ntiles;
-      ta.rec_end = d_rec_end; ta.rec_blank = d_rec_blank;
-      const uint64_t nstates = ntiles; /* one look-back state per block */
-      { pj_status st = ensure(c, &c->tiles, nstates * sizeof(TileState) + 256); if (st) return st; }
-      ta.ticket = (uint32_t*)c->tiles.p;
-      ta.tiles = (TileState*)((uint8_t*)c->tiles.p + 128);
-      ta.res = c->d_res;
-      for (uint32_t k = 0; k < NSLOT; ++k) { ta.slot_cap[k] = ~0ull; ta.slot_base[k] = (uint32_t)total[k]; }
-      for (uint32_t k = 0; k < fa.plan.n; ++k) {
-        const FinalizeItem& it = fa.plan.item[k];
-        if (it.rows_slot == 0xFF) continue;
-        uint64_t room = fa.cap_elems[it.col];
-        if (it.sentinel_slot != 0xFF) room = room ? room - 1 : 0;
-        if (room < ta.slot_cap[it.rows_slot]) ta.slot_cap[it.rows_slot] = room;
-      }
-      ta.plan = fa.plan;
-      ta.cols = pcols;
-      PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, nstates * sizeof(TileState) + 128, c->stream));
-      const uint32_t one = 1;
-      PJ_CUDA(c, cudaMemcpyAsync(&c->d_res->ok, &one, sizeof one, cudaMemcpyHostToDevice, c->stream));
-      stage.next(); /* stage 1: set-up */
-      switch (schema) {
-        case PJ_SCHEMA_PET: PJ_CUDA(c, tile_launch_1(&ta, (unsigned)ntiles, c->stream)); break;
-        case PJ_SCHEMA_ORDER: PJ_CUDA(c, tile_launch_2(&ta, (unsigned)ntiles, c->stream)); break;
-        case PJ_SCHEMA_USER: PJ_CUDA(c, tile_launch_3(&ta, (unsigned)ntiles, c->stream)); break;
-        default: PJ_CUDA(c, tile_launch_4(&ta, (unsigned)ntiles, c->stream)); break;
-      }
-      count_launch(c, 2);
-      stage.next(); /* stage 2: the tile kernel */
-      n_stages = 3;
-    }
-
-    PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
-    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
-    PJ_CUDA(c, cudaGetLastError());
-    collect_times(c, n_stages);
-
-    const DevResult& r = *c->h_res;
-    last = r;
-    n_fast += r.n_fast;
+    PJ_CUDA(c, cudaEventSynchronize(c->ev_done[p]));
+    const DevResult& r = c->h_res[p];
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, c->ev_k0[p], c->ev_k1[p]) == cudaSuccess) { c->stats.stage_ms[2] += ms; c->stats.device_ms += ms; }
+    n_fast += r.n_fast; n_errors += r.n_errors;
     for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] += r.phase_cycles[k];
     c->stats.lookback_polls += r.lookback_polls; c->stats.lookback_rounds += r.lookback_rounds;
     if (r.timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_parse: a bounded device-side wait ran out");
-    const uint64_t rows_new = rows_done + r.n_records;
-    n_errors += r.n_errors;
-    if (!r.ok) over = true;
-    /* this piece's part of every column goes back while the next piece is parsed */
+    if (r.over) over = true;
+    const uint64_t rows_new = r.n_records;
     if (host_out && !over) {
+      if (pipe) PJ_CUDA(c, cudaStreamWaitEvent(s_out, c->ev_done[p], 0));
       auto copy_back = [&](int col, uint64_t from, uint64_t to) -> cudaError_t {
         const size_t e = col_info(col)->elem;
         if (to <= from) return cudaSuccess;
         c->stats.d2h_bytes += (to - from) * e;
-        return cudaMemcpyAsync((uint8_t*)out->col[col].ptr + from * e, (uint8_t*)dcols.ptr[col] + from * e, (to - from) * e, cudaMemcpyDeviceToHost, s_out);
+        return cudaMemcpyAsync((uint8_t*)out->col[col].ptr + from * e, (uint8_t*)pp.dcols.ptr[col] + from * e, (to - from) * e, cudaMemcpyDeviceToHost, s_out);
       };
-      for (int i = 0; i < nrc; ++i) PJ_CUDA(c, copy_back(rcols[i], rows_done, rows_new));
-      for (uint32_t k = 0; k < fa.plan.n; ++k) {
-        const FinalizeItem& it = fa.plan.item[k];
+      for (int i = 0; i < pp.nrc; ++i) PJ_CUDA(c, copy_back(pp.rcols[i], rows_done, rows_new));
+      for (uint32_t k = 0; k < pp.plan.n; ++k) {
+        const FinalizeItem& it = pp.plan.item[k];
         const uint64_t from = it.rows_slot == 0xFF ? rows_done : total[it.rows_slot];
         const uint64_t to = (it.rows_slot == 0xFF ? rows_new : r.total[it.rows_slot]) + (it.sentinel_slot != 0xFF ? 1 : 0);
         PJ_CUDA(c, copy_back(it.col, from, to));
@@ -506,41 +413,153 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
     rows_done = rows_new;
     for (uint32_t k = 0; k < NSLOT; ++k) total[k] = r.total[k];
   }
-  c->stats.main_kernel_ms = c->staged ? c->stats.stage_ms[1] + c->stats.stage_ms[3] : c->stats.stage_ms[2];
+  PJ_CUDA(c, cudaGetLastError());
+  c->stats.main_kernel_ms = c->stats.stage_ms[2];
   c->stats.fast_records = n_fast;
   c->stats.pieces = (uint32_t)np;
-
-  const uint64_t N = rows_done;
-  if (count_only) {
-    out->schema = schema; out->n_records = N; out->n_errors = 0;
-    for (int i = 0; i < nrc; ++i) out->col[rcols[i]].count = N;
-    return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records, per-record buffers hold %llu", (unsigned long long)N, (unsigned long long)cap_all);
-  }
-  out->schema = schema;
-  out->n_records = N;
-  out->n_errors = n_errors;
   out->doc_err_kind = 0; out->doc_err_off = 0;
-  if (array) {
-    if (last.doc_err_off != ~0ull) { out->doc_err_kind = PJ_E_SYNTAX; out->doc_err_off = last.doc_err_off; }
-    else if (last.first_opener == ~0ull || last.arr_final_s || last.arr_final_d != 0) { out->doc_err_kind = PJ_E_EOF; out->doc_err_off = len; }
-  }
-  for (int t = 0; t < 4; ++t) out->n_rows[t] = 0;
-  if (schema == PJ_SCHEMA_MIXED) { out->n_rows[1] = total[SLOT_ROWS_PET]; out->n_rows[2] = total[SLOT_ROWS_ORD]; out->n_rows[3] = total[SLOT_ROWS_USR]; }
-  else out->n_rows[schema] = N;
-  for (int i = 0; i < nrc; ++i) out->col[rcols[i]].count = N;
-  for (uint32_t k = 0; k < fa.plan.n; ++k) {
-    const FinalizeItem& it = fa.plan.item[k];
-    uint64_t rows = it.rows_slot == 0xFF ? N : total[it.rows_slot];
-    out->col[it.col].count = rows + (it.sentinel_slot != 0xFF ? 1 : 0);
-  }
-  uint64_t alg = len;
-  for (int i = 0; i < nneed; ++i) alg += out->col[need[i]].count * col_info(need[i])->elem;
-  c->stats.algorithmic_bytes = alg;
-  if (over) return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records need larger output buffers", (unsigned long long)N);
+  const pj_status st = finish_columns(c, schema, len, pp, rows_done, n_errors, total, over, out);
+  if (st) return st;
+  if (rows_done > 1000 && !c->tile_bytes_opt) c->avg_rec_bytes[schema] = (double)len / (double)rows_done;
   if (host_out) PJ_CUDA(c, cudaStreamSynchronize(s_out));
   return PJ_OK;
 }
 
+/* Array framing: the record index of pj_array_kernels.cuh (extent of every element), then the tile kernel over
+ * tiles of TILE_THREADS records. */
+pj_status parse_array(pj_ctx* c, uint32_t schema, const uint8_t* in, uint64_t len, uint32_t in_kind, pj_columns* out) {
+  ParsePlan pp;
+  { pj_status st = plan_columns(c, schema, out, len, true, &pp); if (st) return st; }
+  const bool host_in = in_kind == PJ_MEM_HOST, host_out = out->mem_kind == PJ_MEM_HOST;
+  const uint8_t* d_in = in;
+  if (host_in && len) {
+    pj_status st = ensure(c, &c->in_stage, len + 64);
+    if (st) return st;
+    d_in = (const uint8_t*)c->in_stage.p;
+    PJ_CUDA(c, cudaMemcpyAsync(c->in_stage.p, in, len, cudaMemcpyHostToDevice, c->stream));
+    c->stats.h2d_bytes += len;
+  }
+  const uint64_t cap_all = pp.rec_cap;
+  const uint64_t nwords = (len + 63) >> 6;
+  const uint64_t atiles = nwords ? (nwords + ARR_THREADS - 1) / ARR_THREADS : 1;
+  const size_t off_fn = align_up((atiles + 1) * 4, 256);
+  const size_t off_tin = align_up(off_fn + atiles * sizeof(ArrFn), 256);
+  const size_t off_sep = align_up(off_tin + atiles * sizeof(ArrState), 256);
+  const size_t off_rend = align_up(off_sep + (nwords + 1) * 8, 256);
+  const size_t off_rblank = align_up(off_rend + cap_all * 8, 256);
+  { pj_status st = ensure(c, &c->scratch, off_rblank + cap_all + 256); if (st) return st; }
+  uint32_t* d_tile = (uint32_t*)c->scratch.p;
+  uint64_t* d_rec_end = (uint64_t*)((uint8_t*)c->scratch.p + off_rend);
+  uint8_t* d_rec_blank = (uint8_t*)c->scratch.p + off_rblank;
+  uint32_t slot_lo, slot_hi;
+  slot_range(schema, &slot_lo, &slot_hi);
+
+  PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream));
+  Stage stage(c);
+  ArrArgs aa;
+  aa.in = d_in; aa.len = len; aa.nwords = nwords;
+  aa.tile_fn = (ArrFn*)((uint8_t*)c->scratch.p + off_fn); aa.tile_in = (ArrState*)((uint8_t*)c->scratch.p + off_tin);
+  aa.sep = (uint64_t*)((uint8_t*)c->scratch.p + off_sep); aa.tile_cnt = d_tile;
+  aa.rec_start = (uint64_t*)pp.dcols.ptr[PJ_COL_REC_START]; aa.rec_end = d_rec_end; aa.rec_blank = d_rec_blank;
+  aa.cap = cap_all; aa.goff = 0; aa.ntiles = (uint32_t)atiles; aa.res = c->d_res;
+  /* the two running minima start at "none" */
+  PJ_CUDA(c, cudaMemsetAsync(&c->d_res->doc_err_off, 0xFF, sizeof(unsigned long long), c->stream));
+  PJ_CUDA(c, cudaMemsetAsync(&c->d_res->first_opener, 0xFF, sizeof(unsigned long long), c->stream));
+  k_arr_summary<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+  k_arr_scan_tiles<<<1, 32, 0, c->stream>>>(aa);
+  k_arr_mark<<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+  k_arr_records<false><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+  k_scan_single<uint32_t><<<1, 1024, 0, c->stream>>>(d_tile, atiles, &c->d_res->n_records);
+  k_arr_records<true><<<(unsigned)atiles, ARR_THREADS, 0, c->stream>>>(aa);
+  count_launch(c, 0, 6);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+
+  /* the tile kernel needs the record count to size its grid */
+  PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+  PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  const uint64_t N0 = c->h_res->n_records;
+  uint64_t total[NSLOT];
+  for (uint32_t k = 0; k < NSLOT; ++k) total[k] = 0;
+  if (N0 > cap_all) {
+    out->schema = schema; out->n_records = N0; out->n_errors = 0;
+    for (int i = 0; i < pp.nrc; ++i) out->col[pp.rcols[i]].count = N0;
+    return set_err(c, PJ_ERR_CAPACITY, "pj_parse: %llu records, per-record buffers hold %llu", (unsigned long long)N0, (unsigned long long)cap_all);
+  }
+  TileArgs ta;
+  memset(&ta, 0, sizeof ta);
+  ta.in = d_in; ta.limit = len; ta.goff = 0; ta.n_records = N0;
+  ta.lf_ws = 1u; ta.open_end = 0u; ta.schema = schema; ta.slot_lo = slot_lo; ta.slot_hi = slot_hi;
+  ta.win_bytes = TILE_WIN_BYTES; ta.tape_cap = TILE_TAPE_CAP;
+  ta.tile_recs = TILE_THREADS;
+  const uint64_t ntiles = N0 ? (N0 + TILE_THREADS - 1) / TILE_THREADS : 1;
+  ta.ntiles = (uint32_t)ntiles;
+  ta.spin_limit_ns = c->spin_ns;
+  c->stats.tile_records = TILE_THREADS; c->stats.tiles += (uint32_t)ntiles;
+  ta.rec_end = d_rec_end; ta.rec_blank = d_rec_blank;
+  { pj_status st = ensure(c, &c->tiles, ntiles * sizeof(TileState) + 256); if (st) return st; }
+  ta.ticket = (uint32_t*)c->tiles.p;
+  ta.tiles = (TileState*)((uint8_t*)c->tiles.p + 128);
+  ta.res = c->d_res;
+  for (uint32_t k = 0; k < NSLOT; ++k) { ta.slot_cap[k] = pp.slot_cap[k]; ta.slot_base[k] = 0; }
+  ta.plan = pp.plan;
+  ta.cols = pp.dcols;
+  PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, ntiles * sizeof(TileState) + 128, c->stream));
+  const uint32_t one = 1;
+  PJ_CUDA(c, cudaMemcpyAsync(&c->d_res->ok, &one, sizeof one, cudaMemcpyHostToDevice, c->stream));
+  stage.next(); /* stage 1: set-up */
+  switch (schema) {
+    case PJ_SCHEMA_PET: PJ_CUDA(c, tile_launch_1(&ta, (unsigned)ntiles, c->stream)); break;
+    case PJ_SCHEMA_ORDER: PJ_CUDA(c, tile_launch_2(&ta, (unsigned)ntiles, c->stream)); break;
+    case PJ_SCHEMA_USER: PJ_CUDA(c, tile_launch_3(&ta, (unsigned)ntiles, c->stream)); break;
+    default: PJ_CUDA(c, tile_launch_4(&ta, (unsigned)ntiles, c->stream)); break;
+  }
+  count_launch(c, 2);
+  stage.next(); /* stage 2: the tile kernel */
+  PJ_CUDA(c, cudaMemcpyAsync(c->h_res, c->d_res, sizeof(DevResult), cudaMemcpyDeviceToHost, c->stream));
+  PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  PJ_CUDA(c, cudaGetLastError());
+  collect_times(c, 3);
+  const DevResult r = *c->h_res;
+  for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] += r.phase_cycles[k];
+  c->stats.lookback_polls += r.lookback_polls; c->stats.lookback_rounds += r.lookback_rounds;
+  c->stats.main_kernel_ms = c->stats.stage_ms[2];
+  c->stats.fast_records = r.n_fast;
+  c->stats.pieces = 1;
+  if (r.timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_parse: a bounded device-side wait ran out");
+  for (uint32_t k = 0; k < NSLOT; ++k) total[k] = r.total[k];
+  out->doc_err_kind = 0; out->doc_err_off = 0;
+  if (r.doc_err_off != ~0ull) { out->doc_err_kind = PJ_E_SYNTAX; out->doc_err_off = r.doc_err_off; }
+  else if (r.first_opener == ~0ull || r.arr_final_s || r.arr_final_d != 0) { out->doc_err_kind = PJ_E_EOF; out->doc_err_off = len; }
+  const pj_status st = finish_columns(c, schema, len, pp, r.n_records, r.n_errors, total, !r.ok, out);
+  if (st) return st;
+  if (host_out) {
+    for (int i = 0; i < pp.nneed; ++i) {
+      const int col = pp.need[i];
+      const size_t nb = (size_t)out->col[col].count * col_info(col)->elem;
+      if (nb) PJ_CUDA(c, cudaMemcpyAsync(out->col[col].ptr, pp.dcols.ptr[col], nb, cudaMemcpyDeviceToHost, c->stream));
+      c->stats.d2h_bytes += nb;
+    }
+    PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  }
+  return PJ_OK;
+}
+
+pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack,
+                     int is_first, int is_last, uint64_t goff, uint32_t in_kind, pj_columns* out) {
+  if (!c) return PJ_ERR_ARG;
+  if (!out || (!in && len + slack) || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED || in_kind > PJ_MEM_DEVICE ||
+      out->mem_kind > PJ_MEM_DEVICE)
+    return set_err(c, PJ_ERR_ARG, "pj_parse: bad argument");
+  if (framing > PJ_FRAMING_ARRAY) return set_err(c, PJ_ERR_ARG, "pj_parse: unknown framing %u", framing);
+  const bool array = framing == PJ_FRAMING_ARRAY;
+  if (array && (slack || !is_first || !is_last)) return set_err(c, PJ_ERR_ARG, "pj_parse: array framing cannot be sharded");
+  const uint64_t limit = len + slack;
+  if (limit >= (1ull << 32)) return set_err(c, PJ_ERR_TOO_LARGE, "pj_parse: %llu input bytes do not fit 32-bit offsets", (unsigned long long)limit);
+  DeviceGuard guard(c->device);
+  c->stats = pj_call_stats{};
+  return array ? parse_array(c, schema, in, len, in_kind, out) : parse_stream(c, schema, in, len, slack, is_first, is_last, goff, in_kind, out);
+}
 }  // namespace
 
 /* ================================================================================================ */
@@ -588,8 +607,10 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   if (!c) return PJ_ERR_NOMEM;
   c->device = dev;
   c->inclusion = opt ? opt->inclusion : PJ_INCLUDE_NON_EMPTY;
-  c->staged = opt && (opt->flags & PJ_OPT_STAGED_PIPELINE);
+  c->opt_flags = opt ? opt->flags : 0;
   c->piece_bytes = opt ? opt->host_piece_bytes : 0;
+  c->tile_bytes_opt = opt ? opt->tile_bytes : 0;
+  if (opt && opt->spin_limit_us) c->spin_ns = (unsigned long long)opt->spin_limit_us * 1000ull;
   DeviceGuard guard(dev);
   auto fail_create = [&](cudaError_t err, const char* what) {
     set_err(nullptr, PJ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
@@ -602,11 +623,14 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
     if (e != cudaSuccess) return fail_create(e, "cudaStreamCreate");
     c->own_stream = true;
   }
-  e = cudaMalloc(&c->d_res, sizeof(DevResult));
+  e = cudaMalloc(&c->d_res, sizeof(DevResult) * PJ_CTX_RESULTS);
   if (e != cudaSuccess) return fail_create(e, "cudaMalloc");
-  e = cudaMallocHost(&c->h_res, sizeof(DevResult));
+  e = cudaMallocHost(&c->h_res, sizeof(DevResult) * PJ_CTX_RESULTS);
   if (e != cudaSuccess) return fail_create(e, "cudaMallocHost");
   for (auto& ev : c->ev) { e = cudaEventCreate(&ev); if (e != cudaSuccess) return fail_create(e, "cudaEventCreate"); }
+  for (auto& ev : c->ev_k0) { e = cudaEventCreate(&ev); if (e != cudaSuccess) return fail_create(e, "cudaEventCreate"); }
+  for (auto& ev : c->ev_k1) { e = cudaEventCreate(&ev); if (e != cudaSuccess) return fail_create(e, "cudaEventCreate"); }
+  for (auto& ev : c->ev_done) { e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming); if (e != cudaSuccess) return fail_create(e, "cudaEventCreate"); }
   build_schema(&c->schema);
   e = tile_init_1(&c->schema);
   if (e == cudaSuccess) e = tile_init_2(&c->schema);
@@ -630,6 +654,9 @@ void pj_destroy(pj_ctx* c) {
   if (c->h_res) cudaFreeHost(c->h_res);
   for (auto& ev : c->ev) if (ev) cudaEventDestroy(ev);
   for (auto& ev : c->ev_in) if (ev) cudaEventDestroy(ev);
+  for (auto& ev : c->ev_k0) if (ev) cudaEventDestroy(ev);
+  for (auto& ev : c->ev_k1) if (ev) cudaEventDestroy(ev);
+  for (auto& ev : c->ev_done) if (ev) cudaEventDestroy(ev);
   if (c->s_in) cudaStreamDestroy(c->s_in);
   if (c->s_out) cudaStreamDestroy(c->s_out);
   if (c->own_stream && c->stream) cudaStreamDestroy(c->stream);
@@ -860,45 +887,16 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
     if (st) return st;
     d_out = (uint8_t*)c->out_stage.p;
   }
-  const uint32_t nchunks = (uint32_t)((n + 1 + SCAN_CHUNK - 1) / SCAN_CHUNK);
-  size_t off_part = align_up((n + 1) * 8, 256);
-  { pj_status st = ensure(c, &c->scratch, off_part + (size_t)nchunks * 8 + 256); if (st) return st; }
-  uint64_t* d_off = (uint64_t*)c->scratch.p;
-  uint64_t* d_part = (uint64_t*)((uint8_t*)c->scratch.p + off_part);
-
   DevResult init;
   memset(&init, 0, sizeof init);
   init.n_records = n;
-  init.ok = c->staged ? 0 : 1;
+  init.ok = 1;
   *c->h_res = init;
   PJ_CUDA(c, cudaMemcpyAsync(c->d_res, c->h_res, sizeof(DevResult), cudaMemcpyHostToDevice, c->stream));
   WriteArgs wa;
   wa.n = n; wa.schema = schema; wa.array = framing == PJ_FRAMING_ARRAY; wa.inclusion = c->inclusion;
-  wa.off = d_off; wa.out = d_out; wa.cap = cap; wa.res = c->d_res; wa.cols = dcols;
-  if (c->staged) {
-    /* the multi-pass writer: size pass, scan of the lengths, emit pass */
-    Stage stage(c);
-    const int grid = persistent_grid(c, n, PARSE_THREADS);
-    k_write_size<<<grid, PARSE_THREADS, 0, c->stream>>>(wa);
-    count_launch(c, 0);
-    PJ_CUDA(c, cudaGetLastError());
-    stage.next();
-    ScanArgs sa;
-    sa.data = d_off; sa.stride = n + 1; sa.partial = d_part; sa.nchunks = nchunks; sa.slot_lo = 0;
-    sa.n_dev = &c->d_res->n_records; sa.n_cap = n; sa.totals = &c->d_res->out_bytes;
-    dim3 sgrid(nchunks, 1);
-    k_scan_reduce<uint64_t><<<sgrid, SCAN_THREADS, 0, c->stream>>>(sa);
-    k_scan_mid<uint64_t><<<1, 1024, 0, c->stream>>>(sa);
-    k_scan_apply<uint64_t><<<sgrid, SCAN_THREADS, 0, c->stream>>>(sa);
-    k_write_check<<<1, 32, 0, c->stream>>>(wa);
-    count_launch(c, 1, 4);
-    PJ_CUDA(c, cudaGetLastError());
-    stage.next();
-    k_write_emit<<<grid, PARSE_THREADS, 0, c->stream>>>(wa);
-    count_launch(c, 2);
-    PJ_CUDA(c, cudaGetLastError());
-    stage.next();
-  } else {
+  wa.out = d_out; wa.cap = cap; wa.res = c->d_res; wa.cols = dcols;
+  {
     /* the single-pass tile writer; stages: [0] state reset and the look at the string arenas, [1] the closing kernel, [2] the tile kernel */
     const uint64_t ntiles = n ? (n + TILE_THREADS - 1) / TILE_THREADS : 1;
     { pj_status st = ensure(c, &c->tiles, 256 + ntiles * 16 + 256); if (st) return st; }
@@ -908,6 +906,7 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
     ta.agg = (unsigned long long*)((uint8_t*)c->tiles.p + 256);
     ta.inc = ta.agg + ntiles;
     ta.ntiles = (uint32_t)ntiles;
+    ta.spin_limit_ns = c->spin_ns;
     /* the string arenas of the schema */
     ArenaArgs aa;
     memset(&aa, 0, sizeof aa);
@@ -943,14 +942,14 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
   PJ_CUDA(c, cudaStreamSynchronize(c->stream));
   PJ_CUDA(c, cudaGetLastError());
   collect_times(c, 3);
-  if (!c->staged) {
+  {
     /* stage 1 covered both kernels: split it with the events around the tile kernel */
     float ms = 0.f;
     if (cudaEventElapsedTime(&ms, c->ev[8], c->ev[9]) == cudaSuccess) { c->stats.stage_ms[2] = ms; c->stats.stage_ms[1] -= ms; }
     c->stats.main_kernel_ms = c->stats.stage_ms[2];
-  } else c->stats.main_kernel_ms = c->stats.stage_ms[0] + c->stats.stage_ms[2];
+  }
   for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] = c->h_res->phase_cycles[k];
-  c->stats.tiles = c->staged ? 0 : (uint32_t)(n ? (n + TILE_THREADS - 1) / TILE_THREADS : 1);
+  c->stats.tiles = (uint32_t)(n ? (n + TILE_THREADS - 1) / TILE_THREADS : 1);
   if (c->h_res->timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_write: a bounded device-side wait ran out");
   *out_len = c->h_res->out_bytes;
   c->stats.algorithmic_bytes = col_bytes + *out_len;

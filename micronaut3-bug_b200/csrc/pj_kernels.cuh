@@ -1,20 +1,17 @@
 /*
- * pj_kernels.cuh — the sm_100a kernels.
+ * pj_kernels.cuh — sm_100a kernels and the device helpers they share.
  *
- * Parse, single pass (the default):
- *   input bytes --k_nd_index_lb--> rec_start[]            one pass, look-back on the record count
- *               --k_parse_tile<SCHEMA>--> every column     128 records per block: bulk-copy staging, one tokenising
- *                                                          pass per record, block scan + decoupled look-back, emission
- * Write, single pass:
- *   columns --k_arena_flags--> "any byte to escape?" --k_write_tile--> text --k_write_close--> brackets, total
- * Array framing gets its record index from pj_array_kernels.cuh.
+ * NDJSON is parsed by k_parse_stream (pj_stream_kernel.cuh), which builds its own line index. This header holds
+ *   - the block scan, the look-back words, the bulk-copy (cp.async.bulk / mbarrier) wrappers that every kernel uses;
+ *   - the NDJSON record index on its own (k_nd_index<false> / k_scan_single / k_nd_index<true>: pj_index_records and
+ *     its allocation-free variant);
+ *   - k_parse_tile<SCHEMA>: the tile kernel over a GIVEN record index, 128 records per block (array framing, whose
+ *     index comes from pj_array_kernels.cuh);
+ *   - the writer: columns --k_arena_flags--> "any byte to escape?" --k_write_tile--> text --k_write_close--> brackets, total.
  *
- * The first, multi-pass pipelines are kept behind PJ_OPT_STAGED_PIPELINE as an independent implementation:
- *   k_nd_index<false> / k_scan_single / k_nd_index<true>, k_parse_size, k_scan_*, k_check, k_parse_emit, k_finalize,
- *   k_write_size, k_write_check, k_write_emit. Nothing in them waits on another thread block.
- *
- * Kernels that do wait on other blocks (the look-backs) take their tile from an atomic ticket, so every block they
- * wait for is running or done, and every wait is bounded (PJ_SPIN_LIMIT_NS -> DevResult.timeout -> PJ_ERR_TIMEOUT).
+ * Kernels that wait on other blocks (the look-backs) take their tile from an atomic ticket, so every block they
+ * wait for is running or done, and every wait is bounded (the spin limit of the kernel's arguments ->
+ * DevResult.timeout -> PJ_ERR_TIMEOUT).
  */
 #ifndef PJ_KERNELS_CUH
 #define PJ_KERNELS_CUH
@@ -41,6 +38,7 @@ struct DevResult {
   unsigned long long doc_err_off;
   uint32_t doc_err_kind;
   uint32_t ok;      /* every output fits its buffer */
+  uint32_t over;    /* stream kernel: some output does not fit its buffer */
   uint32_t timeout; /* a bounded wait ran out */
   uint32_t needs_escape; /* writer: some string byte of the columns has to be escaped (k_arena_flags) */
   unsigned long long n_fast;  /* records decoded by the speculative pass alone */
@@ -165,10 +163,6 @@ __global__ void __launch_bounds__(INDEX_THREADS) k_nd_index(const __grid_constan
 }
 
 /* ---- scans over device-resident lengths -------------------------------------------------------- */
-static constexpr int SCAN_THREADS = 256;
-static constexpr int SCAN_ITEMS = 8;
-static constexpr int SCAN_CHUNK = SCAN_THREADS * SCAN_ITEMS;
-
 /* Single block: exclusive scan of data[0..n) in place, data[n] = total; also *total_out. */
 template <class T>
 __global__ void __launch_bounds__(1024) k_scan_single(T* data, uint64_t n, unsigned long long* total_out) {
@@ -184,214 +178,16 @@ __global__ void __launch_bounds__(1024) k_scan_single(T* data, uint64_t n, unsig
   if (threadIdx.x == 0) { data[n] = carry; if (total_out) *total_out = (unsigned long long)carry; }
 }
 
-struct ScanArgs {
-  void* data;                      /* [nslots][stride] */
-  uint64_t stride;
-  void* partial;                   /* [nslots][nchunks] */
-  uint32_t nchunks, slot_lo;
-  const unsigned long long* n_dev; /* number of valid entries per slot (device resident) */
-  uint64_t n_cap;                  /* entries the buffers can hold (excluding the closing entry) */
-  unsigned long long* totals;      /* [NSLOT] indexed by slot_lo + blockIdx.y */
-};
-template <class T>
-__global__ void __launch_bounds__(SCAN_THREADS) k_scan_reduce(const __grid_constant__ ScanArgs a) {
-  __shared__ T sh[33];
-  uint64_t n = min((uint64_t)*a.n_dev, a.n_cap);
-  uint64_t c0 = (uint64_t)blockIdx.x * SCAN_CHUNK;
-  if (c0 >= n) return;
-  const T* d = (const T*)a.data + (uint64_t)blockIdx.y * a.stride;
-  T s = 0;
-#pragma unroll
-  for (int k = 0; k < SCAN_ITEMS; ++k) {
-    uint64_t i = c0 + (uint64_t)k * SCAN_THREADS + threadIdx.x;
-    if (i < n) s += d[i];
-  }
-  T tot;
-  block_excl_scan(s, &tot, sh);
-  if (threadIdx.x == 0) ((T*)a.partial)[(uint64_t)blockIdx.y * a.nchunks + blockIdx.x] = tot;
-}
-template <class T>
-__global__ void __launch_bounds__(1024) k_scan_mid(const __grid_constant__ ScanArgs a) {
-  __shared__ T sh[33];
-  uint64_t n = min((uint64_t)*a.n_dev, a.n_cap);
-  uint32_t used = (uint32_t)((n + SCAN_CHUNK - 1) / SCAN_CHUNK);
-  T* p = (T*)a.partial + (uint64_t)blockIdx.x * a.nchunks;
-  T carry = 0;
-  for (uint32_t b = 0; b < used; b += blockDim.x) {
-    uint32_t i = b + threadIdx.x;
-    T v = i < used ? p[i] : T(0), tot;
-    T ex = block_excl_scan(v, &tot, sh);
-    if (i < used) p[i] = carry + ex;
-    carry += tot;
-  }
-  if (threadIdx.x == 0) a.totals[a.slot_lo + blockIdx.x] = (unsigned long long)carry;
-}
-/* In-place exclusive scan of each chunk plus its base; entry [n] receives the slot total. */
-template <class T>
-__global__ void __launch_bounds__(SCAN_THREADS) k_scan_apply(const __grid_constant__ ScanArgs a) {
-  __shared__ T sh[33];
-  uint64_t n = min((uint64_t)*a.n_dev, a.n_cap);
-  uint64_t c0 = (uint64_t)blockIdx.x * SCAN_CHUNK;
-  if (c0 > n) return;
-  T* d = (T*)a.data + (uint64_t)blockIdx.y * a.stride;
-  T base = c0 < n ? ((const T*)a.partial)[(uint64_t)blockIdx.y * a.nchunks + blockIdx.x] : (T)a.totals[a.slot_lo + blockIdx.y];
-  /* thread t owns SCAN_ITEMS consecutive entries */
-  uint64_t i0 = c0 + (uint64_t)threadIdx.x * SCAN_ITEMS;
-  T v[SCAN_ITEMS], s = 0;
-#pragma unroll
-  for (int k = 0; k < SCAN_ITEMS; ++k) { v[k] = (i0 + k < n) ? d[i0 + k] : T(0); s += v[k]; }
-  T tot;
-  T ex = base + block_excl_scan(s, &tot, sh);
-#pragma unroll
-  for (int k = 0; k < SCAN_ITEMS; ++k) { if (i0 + k <= n) d[i0 + k] = ex; ex += v[k]; }
-}
-
-/* ---- per-record passes -------------------------------------------------------------------------- */
-struct ParseArgs {
-  const uint8_t* in;
-  uint64_t limit, goff, cap_records;
-  uint32_t lf_ws, open_end, schema, slot_lo, slot_hi;
-  uint32_t* cnt;          /* [NSLOT][stride] */
-  uint64_t stride;
-  const uint64_t* rec_end;   /* array framing: end of every extent, else null */
-  const uint8_t* rec_blank;  /* array framing: extent without a value */
-  DevResult* res;
-  DevCols cols;
-};
-
-static constexpr int PARSE_THREADS = 128;
-
-/* Size pass: one record per thread. */
-static __global__ void __launch_bounds__(PARSE_THREADS) k_parse_size(const __grid_constant__ ParseArgs a) {
-  const uint64_t n = min((uint64_t)a.res->n_records, a.cap_records);
-  const uint64_t* rec_start = colp<uint64_t>(&a.cols, PJ_COL_REC_START);
-  uint32_t nerr = 0;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-    Rd r;
-    r.in = a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end;
-    r.limit = a.rec_end ? a.rec_end[i] : a.limit;
-    PS s;
-    s.p = rec_start[i] - a.goff; s.err = 0; s.err_pos = 0;
-    const uint64_t start = s.p;
-    Out<false> o;
-    o.cols = &a.cols;
-    uint32_t type;
-    if (a.rec_blank && a.rec_blank[i]) { fail(s, PJ_E_SYNTAX, r.limit); type = PJ_TYPE_NONE; for (uint32_t k = 0; k < NSLOT; ++k) o.cnt[k] = 0; }
-    else type = parse_record<false>(c_schema, r, s, a.schema, o, i);
-    if (s.err) { type = PJ_TYPE_NONE; nerr++; }
-    colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i] = (uint8_t)s.err;
-    colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = s.err ? (uint32_t)(s.err_pos - start) : 0u;
-    if (a.schema == PJ_SCHEMA_MIXED) colp<uint8_t>(&a.cols, PJ_COL_REC_TYPE)[i] = (uint8_t)type;
-    for (uint32_t k = a.slot_lo; k < a.slot_hi; ++k) a.cnt[(uint64_t)k * a.stride + i] = s.err ? 0u : o.cnt[k];
-  }
-  /* one atomic per warp */
-  for (int d = 16; d; d >>= 1) nerr += __shfl_down_sync(0xFFFFFFFFu, nerr, d);
-  if ((threadIdx.x & 31) == 0 && nerr) atomicAdd(&a.res->n_errors, (unsigned long long)nerr);
-}
-
-/* Emit pass. */
-static __global__ void __launch_bounds__(PARSE_THREADS) k_parse_emit(const __grid_constant__ ParseArgs a) {
-  if (!a.res->ok) return;
-  const uint64_t n = (uint64_t)a.res->n_records;
-  const uint64_t* rec_start = colp<uint64_t>(&a.cols, PJ_COL_REC_START);
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-    Out<true> o;
-    o.cols = &a.cols;
-    for (uint32_t k = 0; k < NSLOT; ++k) { o.base[k] = 0; o.room[k] = 0; }
-    for (uint32_t k = a.slot_lo; k < a.slot_hi; ++k) {
-      uint32_t b0 = a.cnt[(uint64_t)k * a.stride + i], b1 = a.cnt[(uint64_t)k * a.stride + i + 1];
-      o.base[k] = b0; o.room[k] = b1 - b0;
-    }
-    const uint32_t err = colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i];
-    if (a.schema == PJ_SCHEMA_MIXED) {
-      uint32_t type = colp<uint8_t>(&a.cols, PJ_COL_REC_TYPE)[i];
-      colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = type == PJ_TYPE_NONE ? 0xFFFFFFFFu : o.base[type - 1];
-    }
-    if (err) {
-      if (a.schema != PJ_SCHEMA_MIXED) store_absent<true>(c_schema, a.schema, o, i);
-      continue;
-    }
-    Rd r;
-    r.in = a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end;
-    r.limit = a.rec_end ? a.rec_end[i] : a.limit;
-    PS s;
-    s.p = rec_start[i] - a.goff; s.err = 0; s.err_pos = 0;
-    parse_record<true>(c_schema, r, s, a.schema, o, i);
-  }
-}
-
-/* Capacity check and closing offsets. */
-struct FinalizeArgs {
-  FinalizePlan plan;
-  uint64_t cap_elems[PJ_MAX_COLS];
-  uint64_t cap_records;
-  DevResult* res;
-  DevCols cols;
-};
-static __global__ void k_check(const __grid_constant__ FinalizeArgs a) {
-  if (threadIdx.x || blockIdx.x) return;
-  uint64_t n = a.res->n_records;
-  uint32_t ok = n <= a.cap_records;
-  for (uint32_t k = 0; k < a.plan.n; ++k) {
-    FinalizeItem it = a.plan.item[k];
-    uint64_t rows = it.rows_slot == 0xFF ? n : a.res->total[it.rows_slot];
-    if (rows + (it.sentinel_slot != 0xFF) > a.cap_elems[it.col]) ok = 0;
-  }
-  a.res->ok = ok;
-}
-static __global__ void k_finalize(const __grid_constant__ FinalizeArgs a) {
-  if (!a.res->ok) return;
-  uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
-  if (k >= a.plan.n) return;
-  FinalizeItem it = a.plan.item[k];
-  if (it.sentinel_slot == 0xFF) return;
-  uint64_t rows = it.rows_slot == 0xFF ? a.res->n_records : a.res->total[it.rows_slot];
-  colp<uint32_t>(&a.cols, it.col)[rows] = (uint32_t)a.res->total[it.sentinel_slot];
-}
-
-/* ---- writer ---------------------------------------------------------------------------------- */
+/* ---- writer arguments ------------------------------------------------------------------------- */
 struct WriteArgs {
   uint64_t n;             /* records (mixed) or rows */
   uint32_t schema, array; /* array: wrap as [r,r,...] */
   int inclusion;
-  uint64_t* off;          /* [n + 1] lengths, then exclusive offsets */
   uint8_t* out;
   uint64_t cap;
   DevResult* res;
   DevCols cols;
 };
-static __global__ void __launch_bounds__(PARSE_THREADS) k_write_size(const __grid_constant__ WriteArgs a) {
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
-    uint32_t type; uint64_t row;
-    uint64_t len = 0;
-    if (write_locate(a.schema, &a.cols, i, &type, &row)) {
-      WOut w; w.dst = nullptr; w.n = 0;
-      write_record<false>(c_schema, &a.cols, type, row, a.inclusion, w);
-      len = w.n + 1; /* LF, or the comma / closing bracket that follows the record */
-    }
-    a.off[i] = len;
-  }
-}
-static __global__ void k_write_check(const __grid_constant__ WriteArgs a) {
-  if (threadIdx.x || blockIdx.x) return;
-  uint64_t body = a.res->out_bytes; /* sum of the record lengths, set by the scan */
-  uint64_t total = a.array ? (body ? body + 1 : 2) : body;
-  a.res->out_bytes = total;
-  a.res->ok = total <= a.cap;
-  if (a.array && total <= a.cap) { a.out[0] = '['; if (!body) a.out[1] = ']'; }
-}
-static __global__ void __launch_bounds__(PARSE_THREADS) k_write_emit(const __grid_constant__ WriteArgs a) {
-  if (!a.res->ok) return;
-  const uint64_t total = a.res->out_bytes;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += (uint64_t)gridDim.x * blockDim.x) {
-    uint32_t type; uint64_t row;
-    if (!write_locate(a.schema, &a.cols, i, &type, &row)) continue;
-    uint64_t at = a.off[i] + (a.array ? 1 : 0);
-    WOut w; w.dst = a.out + at; w.n = 0;
-    write_record<true>(c_schema, &a.cols, type, row, a.inclusion, w);
-    a.out[at + w.n] = a.array ? (uint8_t)(at + w.n + 1 == total ? ']' : ',') : (uint8_t)'\n';
-  }
-}
 
 
 /* ================================================================================================
@@ -408,11 +204,10 @@ static __global__ void __launch_bounds__(PARSE_THREADS) k_write_emit(const __gri
  * tile publishes its aggregate as soon as its records are sized and its inclusive prefix once it has
  * found the nearest predecessor whose inclusive prefix is published and added the aggregates in between. Tiles take their
  * index from an atomic ticket, so every predecessor of a running tile is itself running or done and
- * the waits cannot deadlock. Every wait is bounded: after PJ_SPIN_LIMIT_NS it raises res->timeout,
+ * the waits cannot deadlock. Every wait is bounded: after the spin limit it raises res->timeout,
  * which all other waits also watch, and the block finishes without emitting.
  * ================================================================================================ */
 static constexpr int TILE_THREADS = 128;
-static constexpr unsigned long long PJ_SPIN_LIMIT_NS = 2000000000ull; /* 2 s */
 static constexpr uint32_t TILE_WIN_BYTES = 44 * 1024;  /* staged input bytes per tile */
 static constexpr uint32_t TILE_TAPE_CAP = 20;          /* 32-bit tape words per record before the generic parser takes over */
 static constexpr uint32_t TILE_SMEM_BYTES = ((TILE_WIN_BYTES + 64 + 15) & ~15u) + TILE_TAPE_CAP * TILE_THREADS * 4;
@@ -433,6 +228,7 @@ struct TileArgs {
   uint64_t limit, goff, n_records;
   uint32_t lf_ws, open_end, schema, slot_lo, slot_hi;
   uint32_t tile_recs, ntiles, win_bytes, tape_cap;
+  unsigned long long spin_limit_ns; /* bound of every wait on another block or on the staging copy */
   const uint64_t* rec_end;  /* array framing: end of every extent, else null */
   const uint8_t* rec_blank; /* array framing: extent without a value */
   TileState* tiles;
@@ -492,7 +288,7 @@ __device__ __forceinline__ bool tile_lookback(const TileArgs& a, uint32_t tile, 
       if ((ready_mask & need) == need) break;
       ++polls;
       uint32_t give_up = 0;
-      if (lane == 0) give_up = (global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)&a.res->timeout;
+      if (lane == 0) give_up = (global_ns() - t0 > a.spin_limit_ns) || *(volatile uint32_t*)&a.res->timeout;
       give_up = __shfl_sync(0xFFFFFFFFu, give_up, 0);
       if (give_up) { if (lane == 0) atomicExch(&a.res->timeout, 1u); return false; }
       __nanosleep(100);
@@ -536,13 +332,13 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
       : "memory");
   return done != 0;
 }
-/* bounded: false when the copy has not landed after PJ_SPIN_LIMIT_NS */
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint32_t parity) {
+/* bounded: false when the copy has not landed after limit_ns */
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint32_t parity, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (global_ns() - t0 > PJ_SPIN_LIMIT_NS) return false;
+    if (global_ns() - t0 > limit_ns) return false;
     __nanosleep(64);
   }
 }
@@ -674,7 +470,7 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
     if (tid == 0 && nb16) { mbar_expect_tx(&sh_mbar, nb16); bulk_g2s(win, a.in + w0, nb16, &sh_mbar); }
     if (tid < nbytes - nb16) win[nb16 + tid] = a.in[w0 + (int64_t)(nb16 + tid)];
     if (tid < 32) win[nbytes + tid] = '\n';
-    stage_failed = nb16 && !mbar_wait_bounded(&sh_mbar, 0);
+    stage_failed = nb16 && !mbar_wait_bounded(&sh_mbar, 0, a.spin_limit_ns);
   }
   if (__syncthreads_or(stage_failed)) { /* the whole block leaves together */
     if (tid == 0) atomicExch(&a.res->timeout, 1u);
@@ -883,11 +679,12 @@ struct WTileArgs {
   unsigned long long* inc; /* [ntiles] text bytes of all tiles up to and including it | TS_VALID */
   uint32_t* ticket;
   uint32_t ntiles;
+  unsigned long long spin_limit_ns;
 };
 
 /* Exclusive prefix of `tile` over all earlier tiles. Warp 0 only, all lanes; false when the bounded wait ran out. */
-__device__ __forceinline__ bool lookback_u64(const unsigned long long* agg, const unsigned long long* inc, uint32_t* timeout_flag, uint32_t tile,
-                                             uint32_t lane, unsigned long long* excl_out) {
+__device__ __forceinline__ bool lookback_u64(const unsigned long long* agg, const unsigned long long* inc, uint32_t* timeout_flag, unsigned long long limit_ns,
+                                             uint32_t tile, uint32_t lane, unsigned long long* excl_out) {
   unsigned long long excl = 0;
   int64_t j = (int64_t)tile - 1;
   const unsigned long long t0 = global_ns();
@@ -905,7 +702,7 @@ __device__ __forceinline__ bool lookback_u64(const unsigned long long* agg, cons
       const uint32_t need = first_inc >= 31 ? 0xFFFFFFFFu : ((2u << first_inc) - 1u);
       if ((ready_mask & need) == need) break;
       uint32_t give_up = 0;
-      if (lane == 0) give_up = (global_ns() - t0 > PJ_SPIN_LIMIT_NS) || *(volatile uint32_t*)timeout_flag;
+      if (lane == 0) give_up = (global_ns() - t0 > limit_ns) || *(volatile uint32_t*)timeout_flag;
       give_up = __shfl_sync(0xFFFFFFFFu, give_up, 0);
       if (give_up) { if (lane == 0) atomicExch(timeout_flag, 1u); return false; }
       __nanosleep(100);
@@ -919,85 +716,6 @@ __device__ __forceinline__ bool lookback_u64(const unsigned long long* agg, cons
   }
   *excl_out = excl;
   return true;
-}
-
-/* The NDJSON record index in one pass: the candidates of a 16 KiB tile are counted, the tile's first record number
- * comes from a look-back over the tiles before it (the protocol of the tile kernels, one running total), and the
- * record starts are written at once. The input is read once; the last tile leaves the record count. */
-struct IndexLbArgs {
-  IndexArgs ix;            /* ix.tile is not used */
-  unsigned long long* agg; /* [ntiles] */
-  unsigned long long* inc; /* [ntiles] */
-  uint32_t* ticket;
-  uint32_t ntiles;
-  DevResult* res;
-};
-static constexpr int INDEX_LB_CHUNKS = 4;                           /* 64-byte chunks per thread */
-static constexpr int INDEX_LB_TILE = INDEX_TILE * INDEX_LB_CHUNKS; /* 64 KiB per block: fewer, larger tiles keep the look-back cheap */
-static __global__ void __launch_bounds__(INDEX_THREADS) k_nd_index_lb(const __grid_constant__ IndexLbArgs a) {
-  __shared__ uint32_t sh[33];
-  __shared__ uint32_t sh_tile, sh_ok;
-  __shared__ unsigned long long sh_base;
-  const uint32_t tid = threadIdx.x, lane = tid & 31;
-  if (tid == 0) sh_tile = atomicAdd(a.ticket, 1u);
-  __syncthreads();
-  const uint32_t tile = sh_tile;
-  if (tile >= a.ntiles) return;
-  const IndexArgs& x = a.ix;
-  const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(x.in) & 15u);
-  const uint8_t* base = x.in - mis; /* 16-byte aligned */
-  const uint64_t vend = x.len ? x.len + mis : 0;
-  /* a thread owns INDEX_LB_CHUNKS consecutive 64-byte chunks, so its records are consecutive too */
-  const uint64_t t0 = (uint64_t)tile * INDEX_LB_TILE + (uint64_t)tid * (INDEX_BYTES_PER_THREAD * INDEX_LB_CHUNKS); /* offset from base */
-  const bool head_keep = x.is_first && tile == 0 && tid == 0 && nd_is_record(x.in, 0, x.limit, x.is_last);
-  uint64_t keep[INDEX_LB_CHUNKS];
-  uint32_t cnt = head_keep ? 1u : 0u;
-#pragma unroll
-  for (int c = 0; c < INDEX_LB_CHUNKS; ++c) {
-    const uint64_t v0 = t0 + (uint64_t)c * INDEX_BYTES_PER_THREAD;
-    uint64_t m = 0;
-    if (v0 < vend) {
-      m = lf_mask64(base + v0, vend - v0);
-      if (v0 < mis) m &= ~0ull << (mis - v0);
-      if (vend - v0 < 64) m &= ~(~0ull << (vend - v0));
-    }
-    uint64_t k = 0;
-    for (uint64_t t = m; t; t &= t - 1) {
-      const int b = __ffsll((long long)t) - 1;
-      const uint64_t p = v0 + (uint64_t)b - mis + 1;
-      if (nd_is_record(x.in, p, x.limit, x.is_last)) { k |= 1ull << b; cnt++; }
-    }
-    keep[c] = k;
-  }
-  uint32_t total;
-  const uint32_t local = block_excl_scan(cnt, &total, sh);
-  if (tid < 32) {
-    if (lane == 0) {
-      st_relaxed_u64(&a.agg[tile], TS_VALID | total);
-      if (tile == 0) st_relaxed_u64(&a.inc[tile], TS_VALID | total);
-    }
-    unsigned long long excl = 0;
-    const bool ok = lookback_u64(a.agg, a.inc, &a.res->timeout, tile, lane, &excl);
-    if (lane == 0) {
-      if (tile != 0 && ok) st_relaxed_u64(&a.inc[tile], TS_VALID | (excl + total));
-      if (tile == a.ntiles - 1) a.res->n_records = excl + total;
-      sh_base = excl;
-      sh_ok = ok;
-    }
-  }
-  __syncthreads();
-  if (!sh_ok) return;
-  uint64_t at = sh_base + local;
-  if (head_keep) { if (at < x.cap) x.rec_start[at] = x.goff; at++; }
-#pragma unroll
-  for (int c = 0; c < INDEX_LB_CHUNKS; ++c) {
-    const uint64_t v0 = t0 + (uint64_t)c * INDEX_BYTES_PER_THREAD;
-    for (uint64_t t = keep[c]; t; t &= t - 1) {
-      const uint64_t p = v0 + (uint64_t)(__ffsll((long long)t) - 1) - mis + 1;
-      if (at < x.cap) x.rec_start[at] = p + x.goff;
-      at++;
-    }
-  }
 }
 
 /* Does any byte of the string arenas need a JSON escape (below 0x20, '"', '\\')? Text is mostly free of
@@ -1091,7 +809,7 @@ static __global__ void __launch_bounds__(TILE_THREADS, 5) k_write_tile(const __g
       if (tile == 0) st_relaxed_u64(&a.inc[tile], TS_VALID | tile_total);
     }
     unsigned long long excl = 0;
-    const bool ok = lookback_u64(a.agg, a.inc, &a.w.res->timeout, tile, lane, &excl);
+    const bool ok = lookback_u64(a.agg, a.inc, &a.w.res->timeout, a.spin_limit_ns, tile, lane, &excl);
     if (lane == 0) {
       if (tile != 0 && ok) st_relaxed_u64(&a.inc[tile], TS_VALID | (excl + tile_total));
       const bool room = lead + excl + tile_total <= a.w.cap;

@@ -171,8 +171,14 @@ extern "C" int emu_write_fast(uint32_t schema, uint32_t framing, int inclusion, 
 }
 
 #include "pj_fast.cuh"
+#include "pj_lock.cuh"
 static uint64_t g_fail_fast = 0;
 extern "C" uint64_t emu_fail_fast_count() { return g_fail_fast; }
+/* the lockstep tokeniser of pj_lock.cuh as the first attempt at every staged NDJSON record (as in the stream kernel) */
+static int g_use_lock = 0;
+static uint64_t g_lock_accepted = 0;
+extern "C" void emu_use_lock(int on) { g_use_lock = on; g_lock_accepted = 0; }
+extern "C" uint64_t emu_lock_accepted() { return g_lock_accepted; }
 template <int SCHEMA>
 static int emu_fast_t(uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack, int is_first, int is_last, uint64_t goff,
                       pj_columns* out, uint64_t* n_fast, uint32_t tile_recs, uint32_t win_bytes, uint32_t tape_cap,
@@ -226,7 +232,8 @@ static int emu_fast_t(uint32_t framing, const uint8_t* in, uint64_t len, uint64_
       uint32_t fk = 0, fp = 0, st32 = (uint32_t)((int64_t)starts[i] - wr.w0);
       st32v[t] = st32; lim32v[t] = lim32;
       uint32_t verdict = 0;
-      if ((fits || direct) && !blank[i]) {
+      if (g_use_lock && fits && !lf_ws && lock_record<SCHEMA>(wr, true, st32, lim32, !is_last, &type, V[t], CV[t], c, tp)) { verdict = FAST_ACCEPTED; g_lock_accepted++; }
+      else if ((fits || direct) && !blank[i]) {
         if (!direct) verdict = fast_record<SCHEMA>(wr, st32, lim32, lf_ws, lf_ws ? 0 : !is_last, &type, V[t], CV[t], c, tp, &fk, &fp);
         else { verdict = fast_outline<SCHEMA>(wr, st32, lim32, lf_ws, lf_ws ? 0 : !is_last, nullptr, nullptr, i, tp, c, &type, &fk, &fp); tp.n = tp.cap + 1; }
       }
@@ -343,5 +350,73 @@ extern "C" int emu_array_index(const uint8_t* in, uint64_t len, uint64_t* s_out,
   if (doc_min != ~0ull) { *doc_kind = PJ_E_SYNTAX; *doc_off = doc_min; }
   else if (first_opener == ~0ull || st.s || st.d != 0) { *doc_kind = PJ_E_EOF; *doc_off = len; }
   else { *doc_kind = 0; *doc_off = 0; }
+  return 0;
+}
+
+/* ---- the line index of the stream kernel (pj_stream.cuh), tile by tile and "thread" by "thread" ---------------
+ * `mis` bytes of junk are put before the input in a 16-byte aligned copy, as if the caller's buffer started `mis`
+ * bytes into an aligned block. Writes the input offset of every record the tiles find, in order. */
+#include "pj_stream.cuh"
+extern "C" int emu_stream_index(const uint8_t* in, uint64_t len, uint64_t slack, int is_first, int is_last, uint32_t tile_bytes,
+                                uint32_t mis, uint64_t* starts, uint64_t cap, uint64_t* n_out, uint64_t* overflow_tiles, uint64_t* long_lines) {
+  const uint64_t limit = len + slack;
+  std::vector<uint8_t> base(mis + limit + 64, 0xEE);
+  if (limit) memcpy(base.data() + mis, in, limit);
+  const uint8_t* ain = base.data() + mis; /* the "caller's pointer" */
+  std::vector<uint8_t> win(ST_WIN_BYTES + ST_WIN_PAD);
+  uint64_t ntiles = stream_tiles(mis, len, 1u, tile_bytes);
+  uint64_t n = 0;
+  *overflow_tiles = 0; *long_lines = 0;
+  for (uint64_t tile = 0; tile < ntiles; ++tile) {
+    const StreamGeom g = stream_geom(mis, len, limit, tile_bytes, (uint32_t)tile);
+    std::fill(win.begin(), win.end(), 0xDD);
+    if (g.copy_bytes) memcpy(win.data(), base.data() + g.v0, std::min<uint64_t>(g.copy_bytes, base.size() - g.v0));
+    for (uint32_t k = 0; k < ST_WIN_PAD; ++k) win[g.hi_valid + k] = '\n';
+    /* chunk masks, thread by thread */
+    std::vector<uint16_t> lfb(ST_CHUNKS);
+    std::vector<uint32_t> first_idx(ST_THREADS);
+    uint32_t nlf = 0, nown = 0;
+    const bool virtual_first = tile == 0 && is_first && limit > 0;
+    for (uint32_t tid = 0; tid < ST_THREADS; ++tid) {
+      first_idx[tid] = nlf;
+      if (tid == 0 && virtual_first) { nlf++; nown++; }
+      for (uint32_t k = 0; k < ST_CPT; ++k) {
+        const uint32_t c = tid * ST_CPT + k;
+        const uint32_t m = stream_chunk_mask(win.data(), c * 16u, g);
+        lfb[c] = (uint16_t)m;
+        nlf += __builtin_popcount(m); nown += __builtin_popcount(stream_own_bits(m, c * 16u, g));
+      }
+    }
+    if (nown > ST_THREADS) ++*overflow_tiles;
+    for (uint32_t b0 = 0; b0 < nown || b0 == 0; b0 += ST_THREADS) {
+      std::vector<uint16_t> list(ST_LF_CAP, 0xFFFF);
+      for (uint32_t tid = 0; tid < ST_THREADS; ++tid) {
+        uint32_t idx = first_idx[tid];
+        if (tid == 0 && virtual_first) { if (idx - b0 < ST_LF_CAP) list[idx - b0] = (uint16_t)mis; idx++; }
+        for (uint32_t k = 0; k < ST_CPT; ++k) {
+          const uint32_t c = tid * ST_CPT + k;
+          for (uint32_t m = lfb[c]; m; m &= m - 1) {
+            const uint32_t b = (uint32_t)__builtin_ctz(m);
+            if (idx - b0 < ST_LF_CAP) list[idx - b0] = (uint16_t)(c * 16u + b + 1u);
+            idx++;
+          }
+        }
+      }
+      for (uint32_t tid = 0; tid < ST_THREADS; ++tid) {
+        const uint32_t j = b0 + tid;
+        if (j >= nown) break;
+        const uint32_t s = list[tid];
+        const bool fits = (j + 1 < nlf) || g.to_limit;
+        if (tid + 1 < ST_LF_CAP && j + 1 < nlf && list[tid + 1] == 0xFFFF) return -2; /* the next line must be in the list */
+        if (stream_is_record(win.data(), s, g, ain, limit, is_last)) {
+          if (!fits) ++*long_lines;
+          if (n < cap) starts[n] = g.v0 + s - mis;
+          ++n;
+        }
+      }
+      if (nown == 0) break;
+    }
+  }
+  *n_out = n;
   return 0;
 }

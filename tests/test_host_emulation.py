@@ -47,8 +47,10 @@ def extents(oracle, buf):
     return s[:n.value], e[:n.value], b[:n.value]
 
 
-def emu_parse_tiles(emu, oracle, schema, buf, framing=NDJSON, tile=128, win=45056, tape=20):
-    """The tile kernel's per-record work on the host: windows of `win` bytes, tapes of `tape` words, `tile` records a tile."""
+def emu_parse_tiles(emu, oracle, schema, buf, framing=NDJSON, tile=128, win=45056, tape=20, lock=False):
+    """The tile kernel's per-record work on the host: windows of `win` bytes, tapes of `tape` words, `tile` records a tile.
+    lock: the lockstep tokeniser (pj_lock.cuh) gets the first try at every staged NDJSON record, as in the stream kernel."""
+    emu.emu_use_lock(1 if lock else 0)
     buf = as_u8(buf)
     hc = garbage_columns(schema, nrec_bound(buf), buf.size)
     if framing == ARRAY:
@@ -79,14 +81,20 @@ SHAPES = [(128, 45056, 20), (16, 45056, 8), (128, 2048, 20), (7, 45056, 8)]
 
 @pytest.mark.parametrize("schema", [1, 2, 3, 4])
 @pytest.mark.parametrize("flags", FLAG_SETS)
-def test_tile_code_matches_checker_on_generated_text(emu, oracle, schema, flags):
+@pytest.mark.parametrize("lock", [False, True])
+def test_tile_code_matches_checker_on_generated_text(emu, oracle, schema, flags, lock):
+    emu.emu_lock_accepted.restype = C.c_uint64
     text = pj.gen_text(schema, 0xE11, 0, 700, flags)
     want = oracle.parse(schema, text)
     for tile, win, tape in SHAPES:
-        got, nfast = emu_parse_tiles(emu, oracle, schema, text, NDJSON, tile, win, tape)
+        got, nfast = emu_parse_tiles(emu, oracle, schema, text, NDJSON, tile, win, tape, lock)
         assert same_result(want, got) == "", (tile, win, tape)
         if flags == 0:
             assert nfast >= want.n_records - 1  # everything but, at most, the record at the very end of the input
+            if lock and win > 4096:
+                assert emu.emu_lock_accepted() >= want.n_records - 1  # the canonical spelling never needs the second try
+        if lock and flags == G.PJ_GEN_SPARSE and win > 4096:
+            assert emu.emu_lock_accepted() > want.n_records // 20  # records that only omit properties stay on it
 
 
 def test_common_failures_are_found_by_the_word_path(emu, oracle):
@@ -120,8 +128,9 @@ def test_tile_code_matches_checker_on_mutated_text(emu, oracle, seed):
             continue
         want = oracle.parse(schema, body)
         tile, win, tape = rng.choice(SHAPES)
-        got, _ = emu_parse_tiles(emu, oracle, schema, body, NDJSON, tile, win, tape)
-        assert same_result(want, got) == "", (seed, it, schema, flags, tile, win, tape)
+        for lock in (False, True):
+            got, _ = emu_parse_tiles(emu, oracle, schema, body, NDJSON, tile, win, tape, lock)
+            assert same_result(want, got) == "", (seed, it, schema, flags, tile, win, tape, lock)
         # whatever parsed goes back to text through both writers
         for incl in (abi.PJ_INCLUDE_NON_EMPTY, abi.PJ_INCLUDE_NON_NULL, abi.PJ_INCLUDE_ALWAYS):
             text = oracle.write(schema, want, NDJSON, incl)
@@ -154,9 +163,113 @@ def test_integer_text_at_every_digit_count(emu, oracle):
         body = as_u8(b"\n".join(lines) + b"\n")
         cols = oracle.parse(schema, body)
         assert cols.n_errors == 0
-        got, _ = emu_parse_tiles(emu, oracle, schema, body)
-        assert same_result(cols, got) == ""
+        for lock in (False, True):
+            got, _ = emu_parse_tiles(emu, oracle, schema, body, lock=lock)
+            assert same_result(cols, got) == ""
         for framing in (NDJSON, ARRAY):
             for incl in (abi.PJ_INCLUDE_NON_EMPTY, abi.PJ_INCLUDE_NON_NULL, abi.PJ_INCLUDE_ALWAYS):
                 want = oracle.write(schema, cols, framing, incl)
                 assert np.array_equal(want, emu_write(emu, "emu_write_fast", schema, cols, framing, incl, body.size * 4 + 128))
+
+
+# ---- the stream kernel's line index (pj_stream.cuh) ---------------------------------------------------------
+def stream_index(emu, buf, tile_bytes, mis=0, slack=0, is_first=1, is_last=1):
+    buf = as_u8(buf)
+    cap = nrec_bound(buf) + 2
+    starts, n, ov, ll = np.zeros(cap, np.uint64), u64(), u64(), u64()
+    st = emu.emu_stream_index(C.c_void_p(buf.ctypes.data), u64(buf.size - slack), u64(slack), int(is_first), int(is_last), u32(tile_bytes), u32(mis),
+                              C.c_void_p(starts.ctypes.data), u64(cap), C.byref(n), C.byref(ov), C.byref(ll))
+    assert st == 0, st
+    return starts[: n.value], ov.value, ll.value
+
+
+def blank_mutations(rng, text: bytes) -> bytes:
+    """Blank lines, CRLF line ends, lines of blanks and a missing final line feed, sprinkled over an NDJSON text."""
+    out = bytearray()
+    for ln in text.split(b"\n"):
+        r = rng.random()
+        if r < 0.05:
+            out += b"\n"
+        elif r < 0.10:
+            out += b" \t\r\n"
+        elif r < 0.15:
+            out += b"  "
+        out += ln + (b"\r\n" if rng.random() < 0.1 else b"\n")
+    if rng.random() < 0.5:
+        while out.endswith(b"\n"):
+            out.pop()
+    return bytes(out)
+
+
+@pytest.mark.parametrize("tile_bytes", [1024, 4096, 20480, 32768])
+def test_stream_line_index_matches_the_checker(emu, oracle, tile_bytes):
+    rng = random.Random(tile_bytes)
+    for schema, n, flags in ((abi.PJ_SCHEMA_PET, 700, 0), (abi.PJ_SCHEMA_ORDER, 2500, 0), (abi.PJ_SCHEMA_MIXED, 900, G.PJ_GEN_WHITESPACE),
+                             (abi.PJ_SCHEMA_PET, 60, G.PJ_GEN_ZIPF_LISTS)):
+        text = blank_mutations(rng, pj.gen_text(schema, 7 + tile_bytes, 0, n, flags).tobytes())
+        buf = as_u8(text)
+        want = oracle.index(buf)
+        for mis in (0, 1, 7, 15):
+            got, _, _ = stream_index(emu, buf, tile_bytes, mis)
+            assert np.array_equal(got, want), (schema, tile_bytes, mis)
+
+
+def test_stream_line_index_tiny_records_and_long_lines(emu, oracle):
+    """More lines than threads in a tile (the overflow road) and lines that run out of the window."""
+    rng = random.Random(5)
+    tiny = b"".join(rng.choice([b"{}\n", b"\n", b"1\n", b" \n", b"[]\r\n"]) for _ in range(40000))
+    got, ov, _ = stream_index(emu, as_u8(tiny), 32768)
+    assert ov > 0 and np.array_equal(got, oracle.index(as_u8(tiny)))
+    long_line = b'{"name":"' + b"x" * 100000 + b'","photoUrls":[]}\n'
+    text = b'{"id":1}\n' + long_line + b'{"id":2}\n' + b" " * 50000 + b"\n" + b'{"id":3}'
+    got, _, ll = stream_index(emu, as_u8(text), 32768, mis=3)
+    assert ll >= 1 and np.array_equal(got, oracle.index(as_u8(text)))
+    for text in (b"", b"\n", b"{}", b"\n{}", b" ", b"   \n \n"):
+        got, _, _ = stream_index(emu, as_u8(text), 4096)
+        assert np.array_equal(got, oracle.index(as_u8(text))), text
+
+
+def test_stream_line_index_of_shards(emu, oracle):
+    """Shards with slack own the lines the shard rule gives them, whatever the tile size."""
+    rng = random.Random(11)
+    text = as_u8(blank_mutations(rng, pj.gen_text(abi.PJ_SCHEMA_PET, 3, 0, 900, 0).tobytes()))
+    want = oracle.index(text)
+    for parts in (2, 3, 5):
+        cuts = [text.size * k // parts for k in range(parts + 1)]
+        got = []
+        for k in range(parts):
+            lo, hi = cuts[k], cuts[k + 1]
+            slack = min(65536, text.size - hi)
+            s, _, _ = stream_index(emu, text[lo:hi + slack], 8192, mis=k, slack=slack, is_first=k == 0, is_last=hi + slack == text.size)
+            got.append(s + np.uint64(lo))
+        assert np.array_equal(np.concatenate(got), want), parts
+
+
+def test_lockstep_tokeniser_edges(emu, oracle):
+    """What the lockstep tokeniser accepts it decodes as the checker does; what it may not accept it leaves alone."""
+    emu.emu_lock_accepted.restype = C.c_uint64
+    ok = [b'{}', b'{"name":"a","photoUrls":[]}', b'{"id":0,"name":"","photoUrls":[""],"tags":[{}],"status":"sold"}',
+          b'{"id":9223372036854775807,"category":{},"name":"n","photoUrls":["a","b","c","d","e","f","g","h","i","j","k","l","m","n","o","p","q","r","s","t","u","v","w","x"],"tags":[{"id":1},{"name":"x"},{"id":2,"name":"y"}]}',
+          b'{"name":"' + b"x" * 2047 + b'","photoUrls":[]}']
+    refused = [b'{"id":-1,"name":"a","photoUrls":[]}', b'{"id":01,"name":"a","photoUrls":[]}', b'{"id":1.0,"name":"a","photoUrls":[]}',
+               b'{"id":9223372036854775808,"name":"a","photoUrls":[]}', b'{"id":1e3,"name":"a","photoUrls":[]}', b'{"name":"a","photoUrls":[],}',
+               b'{"name":"a","photoUrls":["x",]}', b'{"name":"a","photoUrls":[,]}', b'{"name":"a" ,"photoUrls":[]}', b'{"name":"a","photoUrls":[]} ',
+               b'{"name":"a","photoUrls":[]}\r', b'{"photoUrls":[],"name":"a"}', b'{"name":"a","name":"b","photoUrls":[]}', b'{"name":"a\\n","photoUrls":[]}',
+               b'{"name":"\xc3\xa9","photoUrls":[]}', b'{"name":null,"photoUrls":[]}', b'{"name":"a","photoUrls":[],"status":"gone"}',
+               b'{"name":"a","photoUrls":[],"tags":[{"id":1,}]}', b'{"name":"a","photoUrls":[]', b'{"name":"a","photoUrls":[]}}', b'{"name":"a","photoUrls":[]}x',
+               b'{"name":"' + b"x" * 2048 + b'","photoUrls":[]}', b'{"id":123456789012345678901234567890,"name":"a","photoUrls":[]}', b'[]', b'']
+    for recs, floor in ((ok, len(ok)), (refused, 0)):
+        body = as_u8(b"\n".join(recs) + b"\n")
+        want = oracle.parse(1, body)
+        got, _ = emu_parse_tiles(emu, oracle, 1, body, lock=True)
+        assert same_result(want, got) == ""
+        n = emu.emu_lock_accepted()
+        assert (n >= floor - 1) if floor else (n <= 1), n  # `{}` of the refused set's neighbours aside, nothing of it is accepted
+    for schema, recs in ((2, [b'{"id":1,"petId":2,"quantity":3,"shipDate":"2024-02-29T12:00:01.123Z","status":"placed","complete":true}', b'{"complete":false}', b'{"quantity":2147483648}',
+                              b'{"shipDate":"2023-02-29T12:00:01Z"}', b'{"complete":tru}']),
+                         (3, [b'{"id":5,"username":"u","firstName":"f","lastName":"l","email":"e@x","password":"p","phone":"1234567890","userStatus":3}', b'{"userStatus":-1}']),
+                         (4, [b'{"id":1,"name":"a","photoUrls":[]}', b'{"id":1}', b'{"id":1,"status":"placed","petId":2}', b'{"petId":2,"id":1}', b'{"id":7,"username":"u"}', b'{"id":7,"petId":3}',
+                              b'{"name":"a","photoUrls":[],"id":4}', b'{"phone":"1"}', b'{"photoUrls":[]}', b'{"password":"x"}', b'{}'])):
+        body = as_u8(b"\n".join(recs) + b"\n")
+        got, _ = emu_parse_tiles(emu, oracle, schema, body, lock=True)
+        assert same_result(oracle.parse(schema, body), got) == "", schema
