@@ -187,7 +187,7 @@ template <int SCHEMA>
 struct StreamRec {
   FVals v, cv;
   uint32_t cnt[NSLOT];
-  uint32_t type, err, err_off, fast, direct, start32, lim32, tape_n;
+  uint32_t type, err, err_off, fast, locked, direct, start32, lim32, tape_n;
 };
 
 /* Tokenises the record of line L once (window, or where it lies when it is not staged: `end_known` = input offset of
@@ -214,16 +214,18 @@ __device__ __forceinline__ void stream_tokenise(const StreamArgs& a, const Strea
     r.lim32 = rel > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)rel;
     r.start32 = (uint32_t)((int64_t)L.gstart - wd.w0);
   }
-  const bool locked = lock_record<SCHEMA>(w, is_rec && L.fits, L.s, r.lim32, open_end, &r.type, r.v, r.cv, r.cnt, tp);
-  if (locked) { verdict = FAST_ACCEPTED; r.fast = 1; }
+  uint32_t fpos = 0;
+  verdict = lock_record<SCHEMA>(w, is_rec && L.fits, L.s, r.lim32, open_end, &r.type, r.v, r.cv, r.cnt, tp, &r.err, &fpos);
   if (!is_rec) {
+    r.err = 0; r.locked = 0;
 #pragma unroll
     for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
     r.tape_n = 0;
     return;
   }
-  if (!locked && (L.fits || r.direct)) {
-    uint32_t fpos = 0;
+  r.fast = verdict == FAST_ACCEPTED;
+  r.locked = r.fast; /* accepted in step: its tape is in model order */
+  if (verdict == FAST_REFUSED && (L.fits || r.direct)) {
     if (!r.direct) verdict = fast_record<SCHEMA>(w, r.start32, r.lim32, 0u, open_end, &r.type, r.v, r.cv, r.cnt, tp, &r.err, &fpos);
     else {
       uint32_t cnt_d[NSLOT], type_d = PJ_TYPE_NONE, err_d = 0;
@@ -233,12 +235,12 @@ __device__ __forceinline__ void stream_tokenise(const StreamArgs& a, const Strea
       for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = cnt_d[k];
     }
     r.fast = verdict == FAST_ACCEPTED;
-    if (verdict == FAST_FAILED) {
-      r.type = PJ_TYPE_NONE;
+  }
+  if (verdict == FAST_FAILED) { /* a failure found by one of the two word-at-a-time paths: no row values, no bytes anywhere */
+    r.type = PJ_TYPE_NONE;
 #pragma unroll
-      for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
-      r.err_off = fpos - r.start32;
-    }
+    for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
+    r.err_off = fpos - r.start32;
   }
   if (verdict == FAST_REFUSED) {
     Rd rd;
@@ -270,7 +272,8 @@ __device__ __forceinline__ void stream_emit(const StreamArgs& a, const StreamGeo
     colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = r.type == PJ_TYPE_NONE ? 0xFFFFFFFFu : row;
   }
   if (r.fast) {
-    if (!r.direct && r.tape_n <= tp.cap) fast_emit<SCHEMA>(w, &a.cols, r.type, r.v, r.cv, tp, base, i);
+    if (r.locked && r.tape_n <= tp.cap) lock_emit<SCHEMA>(w, &a.cols, r.type, r.v, r.cv, tp, base, r.cnt, i);
+    else if (!r.direct && r.tape_n <= tp.cap) fast_emit<SCHEMA>(w, &a.cols, r.type, r.v, r.cv, tp, base, i);
     else {
       uint32_t base_copy[NSLOT], t_d, e_d, p_d;
 #pragma unroll
@@ -358,7 +361,7 @@ __device__ __noinline__ void stream_overflow_tile(const StreamArgs& a, const Str
         L.gstart = g.v0 + L.s - g.mis;
         is_rec = stream_is_record(win, L.s, g, a.in, a.limit, (int)a.is_last);
       }
-      r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0; r.direct = 0; r.tape_n = 0;
+      r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0; r.locked = 0; r.direct = 0; r.tape_n = 0;
 #pragma unroll
       for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
       stream_tokenise<SCHEMA>(a, g, win, is_rec, L, ~0ull, tp, r, w, wd); /* a line that leaves the window: exact parser, where it lies */
@@ -488,7 +491,7 @@ __global__ void __launch_bounds__(ST_THREADS, 4) k_parse_stream(const __grid_con
   tp.e = tape + tid; tp.stride = ST_THREADS; tp.cap = ST_TAPE_CAP; tp.n = 0;
   StreamRec<SCHEMA> r;
   Win w, wd;
-  r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0; r.direct = 0; r.tape_n = 0;
+  r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0; r.locked = 0; r.direct = 0; r.tape_n = 0;
 #pragma unroll
   for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
   stream_tokenise<SCHEMA>(a, g, win, is_rec, L, end_known, tp, r, w, wd);

@@ -176,9 +176,10 @@ static uint64_t g_fail_fast = 0;
 extern "C" uint64_t emu_fail_fast_count() { return g_fail_fast; }
 /* the lockstep tokeniser of pj_lock.cuh as the first attempt at every staged NDJSON record (as in the stream kernel) */
 static int g_use_lock = 0;
-static uint64_t g_lock_accepted = 0;
-extern "C" void emu_use_lock(int on) { g_use_lock = on; g_lock_accepted = 0; }
+static uint64_t g_lock_accepted = 0, g_lock_failed = 0;
+extern "C" void emu_use_lock(int on) { g_use_lock = on; g_lock_accepted = 0; g_lock_failed = 0; }
 extern "C" uint64_t emu_lock_accepted() { return g_lock_accepted; }
+extern "C" uint64_t emu_lock_failed() { return g_lock_failed; }
 template <int SCHEMA>
 static int emu_fast_t(uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack, int is_first, int is_last, uint64_t goff,
                       pj_columns* out, uint64_t* n_fast, uint32_t tile_recs, uint32_t win_bytes, uint32_t tape_cap,
@@ -214,7 +215,7 @@ static int emu_fast_t(uint32_t framing, const uint8_t* in, uint64_t len, uint64_
     Win w; w.s = winbuf.data(); w.w0 = w0;
     std::vector<uint32_t> tape((size_t)tape_cap * tile_recs + 1);
     std::vector<FVals> V(nrec), CV(nrec);
-    std::vector<uint32_t> types(nrec), isfast(nrec), ntape(nrec), st32v(nrec), lim32v(nrec);
+    std::vector<uint32_t> types(nrec), isfast(nrec), islock(nrec, 0), ntape(nrec), st32v(nrec), lim32v(nrec);
     std::vector<Win> wins(nrec);
     std::vector<uint32_t> cnt((size_t)nrec * NSLOT, 0);
     for (uint32_t t = 0; t < nrec; ++t) {
@@ -232,7 +233,12 @@ static int emu_fast_t(uint32_t framing, const uint8_t* in, uint64_t len, uint64_
       uint32_t fk = 0, fp = 0, st32 = (uint32_t)((int64_t)starts[i] - wr.w0);
       st32v[t] = st32; lim32v[t] = lim32;
       uint32_t verdict = 0;
-      if (g_use_lock && fits && !lf_ws && lock_record<SCHEMA>(wr, true, st32, lim32, !is_last, &type, V[t], CV[t], c, tp)) { verdict = FAST_ACCEPTED; g_lock_accepted++; }
+      if (g_use_lock && fits && !lf_ws) {
+        verdict = lock_record<SCHEMA>(wr, true, st32, lim32, !is_last, &type, V[t], CV[t], c, tp, &fk, &fp);
+        if (verdict == FAST_ACCEPTED) { g_lock_accepted++; islock[t] = 1; }
+        if (verdict == FAST_FAILED) g_lock_failed++;
+      }
+      if (verdict != FAST_REFUSED) {}
       else if ((fits || direct) && !blank[i]) {
         if (!direct) verdict = fast_record<SCHEMA>(wr, st32, lim32, lf_ws, lf_ws ? 0 : !is_last, &type, V[t], CV[t], c, tp, &fk, &fp);
         else { verdict = fast_outline<SCHEMA>(wr, st32, lim32, lf_ws, lf_ws ? 0 : !is_last, nullptr, nullptr, i, tp, c, &type, &fk, &fp); tp.n = tp.cap + 1; }
@@ -262,7 +268,8 @@ static int emu_fast_t(uint32_t framing, const uint8_t* in, uint64_t len, uint64_
       if (ek[i]) { if (schema != PJ_SCHEMA_MIXED) store_absent<true>(S, schema, o, i); continue; }
       if (isfast[t]) {
         Tape tp; tp.e = tape.data() + t; tp.stride = tile_recs; tp.cap = tape_cap; tp.n = ntape[t];
-        if (tp.n <= tp.cap) fast_emit<SCHEMA>(wins[t], &dc, types[t], V[t], CV[t], tp, o.base, i);
+        if (islock[t] && tp.n <= tp.cap) lock_emit<SCHEMA>(wins[t], &dc, types[t], V[t], CV[t], tp, o.base, o.room, i);
+        else if (tp.n <= tp.cap) fast_emit<SCHEMA>(wins[t], &dc, types[t], V[t], CV[t], tp, o.base, i);
         else { uint32_t a_, b_, c_; fast_outline<SCHEMA>(wins[t], st32v[t], lim32v[t], lf_ws, lf_ws ? 0 : !is_last, &dc, o.base, i, tp, nullptr, &a_, &b_, &c_); }
       } else {
         uint64_t lim = lf_ws ? ends[i] : limit;

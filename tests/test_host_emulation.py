@@ -100,15 +100,20 @@ def test_tile_code_matches_checker_on_generated_text(emu, oracle, schema, flags,
 def test_common_failures_are_found_by_the_word_path(emu, oracle):
     """Wrong type, unknown literal, missing required property, record ending in a string: same kind and offset as the checker."""
     emu.emu_fail_fast_count.restype = C.c_uint64
+    emu.emu_lock_failed.restype = C.c_uint64
     before = emu.emu_fail_fast_count()
-    nerr = 0
+    nerr = nlock = 0
     for schema in (1, 2, 3, 4):
         text = pj.gen_text(schema, 99, 0, 3000, G.PJ_GEN_MALFORMED)
         want = oracle.parse(schema, text)
         got, _ = emu_parse_tiles(emu, oracle, schema, text)
         assert same_result(want, got) == ""
         nerr += want.n_errors
+        got, _ = emu_parse_tiles(emu, oracle, schema, text, lock=True)  # the lockstep tokeniser reports them itself
+        assert same_result(want, got) == ""
+        nlock += emu.emu_lock_failed()
     assert nerr > 60 and emu.emu_fail_fast_count() - before >= nerr * 9 // 10
+    assert nlock >= nerr * 9 // 10
 
 
 @pytest.mark.parametrize("seed", [1, 2, 3])
