@@ -267,7 +267,7 @@ uint32_t pick_tile_bytes(const pj_ctx* c, uint32_t schema) {
   else {
     static const double dflt[5] = {0, 300, 125, 190, 220};
     const double avg = c->avg_rec_bytes[schema] > 0 ? c->avg_rec_bytes[schema] : dflt[schema];
-    tb = (uint64_t)(avg * 104.0);
+    tb = (uint64_t)(avg * (ST_THREADS * 13 / 16));
   }
   tb &= ~15ull;
   if (tb < ST_MIN_TILE_BYTES) tb = ST_MIN_TILE_BYTES;

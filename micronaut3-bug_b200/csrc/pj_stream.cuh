@@ -20,14 +20,14 @@
 
 namespace pj {
 
-static constexpr uint32_t ST_THREADS = 128;
-static constexpr uint32_t ST_CPT = 17; /* 16-byte chunks per thread; odd, so that 128-bit loads at this stride are free of bank conflicts */
+static constexpr uint32_t ST_THREADS = 256;
+static constexpr uint32_t ST_CPT = 15; /* 16-byte chunks per thread; odd, so that 128-bit loads at this stride are free of bank conflicts */
 static constexpr uint32_t ST_CHUNKS = ST_THREADS * ST_CPT;
 static constexpr uint32_t ST_WIN_BYTES = ST_CHUNKS * 16; /* 34816 bytes staged per tile */
 static constexpr uint32_t ST_WIN_PAD = 48;               /* line feeds behind the staged bytes: look-ahead never leaves the window */
-static constexpr uint32_t ST_MAX_TILE_BYTES = 32768;     /* leaves 2 KiB of the window for records that run past the tile */
+static constexpr uint32_t ST_MAX_TILE_BYTES = ST_WIN_BYTES - 2048; /* leaves 2 KiB of the window for records that run past the tile */
 static constexpr uint32_t ST_MIN_TILE_BYTES = 1024;
-static constexpr uint32_t ST_LF_CAP = 192;               /* line starts kept per batch: 128 owned ones and what follows */
+static constexpr uint32_t ST_LF_CAP = ST_THREADS + 64;     /* line starts kept per batch: the owned ones and what follows */
 static constexpr uint32_t ST_NONE = 0xFFFFFFFFu;
 
 /* Where a tile lies. Offsets named v* count from the aligned base (input offset + mis); window offsets count from

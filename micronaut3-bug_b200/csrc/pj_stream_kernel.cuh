@@ -190,15 +190,15 @@ struct StreamRec {
   uint32_t type, err, err_off, fast, locked, direct, start32, lim32, tape_n;
 };
 
-/* Tokenises the record of line L once (window, or where it lies when it is not staged: `end_known` = input offset of
- * its end, or ~0). Every thread of the block calls this, `is_rec` or not: staged records first go through the
- * lockstep tokeniser, which the lanes of a warp walk together; what it refuses goes to fast_record<>() (counts,
- * values and tape as that leaves them), and what that refuses to the exact parser of pj_core.cuh. */
+/* What lock_record<>() did not finish: the word-at-a-time tokeniser (staged record, or where it lies when it is not
+ * staged: `end_known` = input offset of its end, or ~0) and, behind it, the exact parser of pj_core.cuh. Out of
+ * line: it is rare, large and wants more registers than the path in step. */
 template <int SCHEMA>
-__device__ __forceinline__ void stream_tokenise(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, bool is_rec, const StreamLine& L, uint64_t end_known,
-                                                Tape& tp, StreamRec<SCHEMA>& r, Win& w, Win& wd) {
+__device__ __noinline__ void stream_tokenise_rest(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, const StreamLine& L, uint64_t end_known,
+                                                  Tape& tp, StreamRec<SCHEMA>& r, Win& wd) {
   constexpr uint32_t LO = StreamSlots<SCHEMA>::lo, HI = StreamSlots<SCHEMA>::hi;
   const int64_t w0 = (int64_t)g.v0 - (int64_t)g.mis; /* input offset of window byte 0 */
+  Win w;
   w.s = win; w.w0 = w0;
   wd = w;
   const uint32_t open_end = a.is_last ? 0u : 1u;
@@ -207,25 +207,14 @@ __device__ __forceinline__ void stream_tokenise(const StreamArgs& a, const Strea
     const uint32_t mis4 = (uint32_t)(reinterpret_cast<uintptr_t>(a.in + L.gstart) & 3u);
     wd.s = a.in + L.gstart - mis4; wd.w0 = (int64_t)L.gstart - mis4;
   }
-  uint32_t verdict = FAST_REFUSED;
-  r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0; r.start32 = 0; r.lim32 = 0;
   {
     const uint64_t rel = (uint64_t)((int64_t)a.limit - wd.w0);
     r.lim32 = rel > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)rel;
     r.start32 = (uint32_t)((int64_t)L.gstart - wd.w0);
   }
-  uint32_t fpos = 0;
-  verdict = lock_record<SCHEMA>(w, is_rec && L.fits, L.s, r.lim32, open_end, &r.type, r.v, r.cv, r.cnt, tp, &r.err, &fpos);
-  if (!is_rec) {
-    r.err = 0; r.locked = 0;
-#pragma unroll
-    for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
-    r.tape_n = 0;
-    return;
-  }
-  r.fast = verdict == FAST_ACCEPTED;
-  r.locked = r.fast; /* accepted in step: its tape is in model order */
-  if (verdict == FAST_REFUSED && (L.fits || r.direct)) {
+  uint32_t verdict = FAST_REFUSED, fpos = 0;
+  r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0;
+  if (L.fits || r.direct) {
     if (!r.direct) verdict = fast_record<SCHEMA>(w, r.start32, r.lim32, 0u, open_end, &r.type, r.v, r.cv, r.cnt, tp, &r.err, &fpos);
     else {
       uint32_t cnt_d[NSLOT], type_d = PJ_TYPE_NONE, err_d = 0;
@@ -236,7 +225,7 @@ __device__ __forceinline__ void stream_tokenise(const StreamArgs& a, const Strea
     }
     r.fast = verdict == FAST_ACCEPTED;
   }
-  if (verdict == FAST_FAILED) { /* a failure found by one of the two word-at-a-time paths: no row values, no bytes anywhere */
+  if (verdict == FAST_FAILED) { /* a failure found by the word-at-a-time path: no row values, no bytes anywhere */
     r.type = PJ_TYPE_NONE;
 #pragma unroll
     for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
@@ -259,21 +248,51 @@ __device__ __forceinline__ void stream_tokenise(const StreamArgs& a, const Strea
   r.tape_n = tp.n;
 }
 
-/* Emits record number `i` (base[] = its start in every arena / child table / model table). */
+/* Tokenises the record of line L once. Every thread of the block calls this, `is_rec` or not: staged records go
+ * through the lockstep tokeniser, which the lanes of a warp walk together; what it neither accepts nor fails goes
+ * to stream_tokenise_rest<>(). */
 template <int SCHEMA>
-__device__ __forceinline__ void stream_emit(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, const StreamLine& L, const Win& w, const Win& wd,
-                                            Tape& tp, const StreamRec<SCHEMA>& r, const uint32_t* base, uint64_t i) {
-  colp<uint64_t>(&a.cols, PJ_COL_REC_START)[i] = a.goff + L.gstart;
-  colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i] = (uint8_t)r.err;
-  colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = r.err_off;
-  if (SCHEMA == PJ_SCHEMA_MIXED) {
-    colp<uint8_t>(&a.cols, PJ_COL_REC_TYPE)[i] = (uint8_t)r.type;
-    const uint32_t row = r.type == PJ_TYPE_PET ? base[SLOT_ROWS_PET] : (r.type == PJ_TYPE_ORDER ? base[SLOT_ROWS_ORD] : base[SLOT_ROWS_USR]);
-    colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = r.type == PJ_TYPE_NONE ? 0xFFFFFFFFu : row;
+__device__ __forceinline__ void stream_tokenise(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, bool is_rec, const StreamLine& L, uint64_t end_known,
+                                                Tape& tp, StreamRec<SCHEMA>& r, Win& w, Win& wd) {
+  w.s = win; w.w0 = (int64_t)g.v0 - (int64_t)g.mis;
+  wd = w;
+  const uint32_t open_end = a.is_last ? 0u : 1u;
+  r.direct = 0; r.err_off = 0;
+  r.start32 = L.s;
+  r.lim32 = g.vlimit - g.v0 > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)(g.vlimit - g.v0); /* window offset of the first byte that is not input */
+  uint32_t fpos = 0;
+  const uint32_t verdict = lock_record<SCHEMA>(w, is_rec && L.fits, L.s, r.lim32, open_end, &r.type, r.v, r.cv, r.cnt, tp, &r.err, &fpos);
+  r.fast = verdict == FAST_ACCEPTED;
+  r.locked = r.fast; /* accepted in step: its tape is in model order */
+  r.tape_n = tp.n;
+  if (!is_rec || verdict == FAST_FAILED) { /* no record, or a failed one: no row values, no bytes anywhere */
+    if (!is_rec) r.err = 0;
+    r.type = PJ_TYPE_NONE;
+#pragma unroll
+    for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
+    r.err_off = is_rec ? fpos - L.s : 0u;
+    r.tape_n = 0;
+  } else if (verdict == FAST_REFUSED) {
+    /* through copies, so that the addresses of the hot path's own state never leave it (it stays in registers) */
+    StreamRec<SCHEMA> cold;
+    StreamLine lc = L;
+    Tape tc = tp;
+    Win wc;
+    stream_tokenise_rest<SCHEMA>(a, g, win, lc, end_known, tc, cold, wc);
+    r = cold; tp.n = tc.n; wd = wc;
+    r.locked = 0;
   }
+}
+
+/* Emission of the records the path in step did not accept (out of line, like their tokenising). */
+template <int SCHEMA>
+__device__ __noinline__ void stream_emit_rest(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, const StreamLine& L, const Win& wd,
+                                              Tape& tp, const StreamRec<SCHEMA>& r, const uint32_t* base, uint64_t i) {
+  const int64_t w0 = (int64_t)g.v0 - (int64_t)g.mis;
+  Win w;
+  w.s = win; w.w0 = w0;
   if (r.fast) {
-    if (r.locked && r.tape_n <= tp.cap) lock_emit<SCHEMA>(w, &a.cols, r.type, r.v, r.cv, tp, base, r.cnt, i);
-    else if (!r.direct && r.tape_n <= tp.cap) fast_emit<SCHEMA>(w, &a.cols, r.type, r.v, r.cv, tp, base, i);
+    if (!r.direct && r.tape_n <= tp.cap) fast_emit<SCHEMA>(w, &a.cols, r.type, r.v, r.cv, tp, base, i);
     else {
       uint32_t base_copy[NSLOT], t_d, e_d, p_d;
 #pragma unroll
@@ -288,13 +307,37 @@ __device__ __forceinline__ void stream_emit(const StreamArgs& a, const StreamGeo
     if (r.err) {
       if (SCHEMA != PJ_SCHEMA_MIXED) store_absent<true>(c_schema, (uint32_t)SCHEMA, o, i);
     } else {
-      const int64_t w0 = (int64_t)g.v0 - (int64_t)g.mis;
       Rd rd;
       rd.in = L.fits ? win - w0 : a.in; rd.lf_ws = 0; rd.open_end = a.is_last ? 0u : 1u; rd.limit = a.limit;
       PS s;
       s.p = L.gstart; s.err = 0; s.err_pos = 0;
       parse_record<true>(c_schema, rd, s, (uint32_t)SCHEMA, o, i);
     }
+  }
+}
+
+/* Emits record number `i` (base[] = its start in every arena / child table / model table). */
+template <int SCHEMA>
+__device__ __forceinline__ void stream_emit(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, const StreamLine& L, const Win& w, const Win& wd,
+                                            Tape& tp, const StreamRec<SCHEMA>& r, const uint32_t* base, uint64_t i) {
+  colp<uint64_t>(&a.cols, PJ_COL_REC_START)[i] = a.goff + L.gstart;
+  colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i] = (uint8_t)r.err;
+  colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = r.err_off;
+  if (SCHEMA == PJ_SCHEMA_MIXED) {
+    colp<uint8_t>(&a.cols, PJ_COL_REC_TYPE)[i] = (uint8_t)r.type;
+    const uint32_t row = r.type == PJ_TYPE_PET ? base[SLOT_ROWS_PET] : (r.type == PJ_TYPE_ORDER ? base[SLOT_ROWS_ORD] : base[SLOT_ROWS_USR]);
+    colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = r.type == PJ_TYPE_NONE ? 0xFFFFFFFFu : row;
+  }
+  if (r.locked && r.tape_n <= tp.cap) lock_emit<SCHEMA>(w, &a.cols, r.type, r.v, r.cv, tp, base, r.cnt, i);
+  else {
+    StreamRec<SCHEMA> cold = r;
+    StreamLine lc = L;
+    Tape tc = tp;
+    Win wc = wd;
+    uint32_t bc[NSLOT];
+#pragma unroll
+    for (uint32_t k = 0; k < NSLOT; ++k) bc[k] = base[k];
+    stream_emit_rest<SCHEMA>(a, g, win, lc, wc, tc, cold, bc, i);
   }
 }
 
@@ -404,7 +447,7 @@ __device__ __noinline__ void stream_overflow_tile(const StreamArgs& a, const Str
 }
 
 template <int SCHEMA>
-__global__ void __launch_bounds__(ST_THREADS, 4) k_parse_stream(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(ST_THREADS, 512 / ST_THREADS) k_parse_stream(const __grid_constant__ StreamArgs a) {
   constexpr uint32_t LO = StreamSlots<SCHEMA>::lo, HI = StreamSlots<SCHEMA>::hi, MASK = StreamSlots<SCHEMA>::mask;
   constexpr uint32_t NWARPS = ST_THREADS / 32;
   extern __shared__ __align__(16) uint8_t smem[];
