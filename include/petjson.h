@@ -121,7 +121,8 @@ enum {
   PJ_ERR_CUDA = 3,      /* a CUDA call failed (text via pj_last_error)                         */
   PJ_ERR_TIMEOUT = 4,   /* a bounded device-side wait ran out; the context stays usable        */
   PJ_ERR_NOMEM = 5,     /* host or device allocation failed                                    */
-  PJ_ERR_TOO_LARGE = 6  /* input (plus slack) or output does not fit 32-bit offsets (>= 4 GiB) */
+  PJ_ERR_TOO_LARGE = 6, /* input (plus slack) or output does not fit 32-bit offsets (>= 4 GiB) */
+  PJ_ERR_NCCL = 7       /* pj_group_*: an NCCL call failed or the library could not be loaded    */
 };
 
 /* ---- per-record validation result (PJ_COL_ERR_KIND) ------------------------------------- */
@@ -239,11 +240,32 @@ typedef struct pj_columns {
   pj_buf col[PJ_MAX_COLS];
 } pj_columns;
 
+/* pj_options.flags. The first four select the other answer of a rule that rests on behaviour of the reference's
+ * third-party serde which could not be observed (no JVM where this was written); the defaults are the rules R1-R12,
+ * W1-W5 above. tests/golden/EmitGolden.java, run by someone who has the JVM, says which answers are the library's. */
+enum {
+  PJ_OPT_ENUM_UNKNOWN_AS_NULL = 1u << 0,   /* R8: a string that is no literal of the enum leaves the property absent (the
+                                              convention of api/EnumParam.java:32-34) instead of failing with PJ_E_ENUM (the
+                                              convention of config/data/VariantEnum.java:41-46)                              */
+  PJ_OPT_LONE_SURROGATE_REPLACE = 1u << 1, /* R7: a \uD800-\uDFFF escape without its partner is accepted and decoded as
+                                              U+FFFD (EF BF BD) instead of failing with PJ_E_BAD_SURROGATE                 */
+  PJ_OPT_COERCE_SCALARS = 1u << 2,         /* R5: an integer property also takes a JSON string that holds an integer
+                                              (-?(0|[1-9][0-9]*); otherwise PJ_E_TYPE, out of range PJ_E_NUM_RANGE, both at the
+                                              opening quote); a boolean property the strings "true" / "false"; a string
+                                              property of a model, Category or Tag also takes a number, true or false, whose
+                                              text as written becomes the string. List elements, enums and date-times are
+                                              not coerced                                                                  */
+  PJ_OPT_HEX_LOWER = 1u << 3,              /* W3: \u00xx escapes are written with lower-case hex digits                    */
+  PJ_OPT_TEST_STALL_ONCE = 1u << 31 /* test hook for the time-out path: in the context's FIRST NDJSON parse call the first
+                                       tile is never handed out, so every other tile's bounded wait for it runs out
+                                       (after spin_limit_us) and the call answers PJ_ERR_TIMEOUT; later calls are normal */
+};
+
 typedef struct pj_options {
   int32_t device;            /* CUDA device ordinal; -1 = the calling thread's current device   */
   int32_t inclusion;         /* PJ_INCLUDE_* for pj_write                                       */
   void* stream;              /* a cudaStream_t to run on, or NULL for a stream the context owns */
-  uint32_t flags;            /* PJ_OPT_* bits (none defined: must be 0)                         */
+  uint32_t flags;            /* PJ_OPT_* bits                                                   */
   uint32_t host_piece_bytes; /* pj_parse with host input and host columns (NDJSON): the input is cut after
                                 line feeds into pieces of about this many bytes (at most 16), and the copy of
                                 one piece to the device, the kernel of the previous one and the copy of the
@@ -368,6 +390,79 @@ pj_status pj_index_records_static(const uint8_t* in, uint64_t len, uint64_t* rec
  * PJ_ERR_CAPACITY. Columns live in cols->mem_kind memory. */
 pj_status pj_write(pj_ctx* ctx, uint32_t schema, uint32_t framing, const pj_columns* cols,
                    uint8_t* out, uint64_t cap, uint32_t out_kind, uint64_t* out_len);
+
+/* One 64-bit checksum per column of a device-resident column set, computed on the GPU: for checking results at sizes
+ * where copying every column to the host for a comparison is not wanted. sums[col] is 0 for columns the schema does
+ * not have. The checksum of a column is over its first count * element_width bytes b[0..n): with w_j the little-endian
+ * 64-bit word of bytes [8j, 8j+8) (zero padded at the end),
+ *     sum = SUM_j mix(w_j + 0x9E3779B97F4A7C15 * (j + 1))  (mod 2^64),
+ *     mix(x): x ^= x >> 30; x *= 0xBF58476D1CE4E5B9; x ^= x >> 27; x *= 0x94D049BB133111EB; x ^= x >> 31.
+ * The terms commute, so any number of threads may add them in any order; the CPU checker computes the same sums
+ * from its own columns. No counterpart in the reference (it has no columns). */
+pj_status pj_columns_checksum(pj_ctx* ctx, uint32_t schema, const pj_columns* cols, uint64_t* sums /*[PJ_MAX_COLS]*/);
+
+/* ---- several GPUs of one machine ------------------------------------------------------------------------
+ * The reference reaches its mapper as ONE in-process bean (MyEntityConfig.java:24,34): a caller that wants all the
+ * GPUs of a box therefore needs them behind one handle in one process. A group holds one context per device and
+ * runs one host thread and one stream per device inside its calls. An NDJSON stream is split by the caller into
+ * contiguous byte ranges ("shards"), shard g resident on device g; a shard owns the records whose preceding line
+ * feed lies in its range (pj_parse_shard's rule). The library copies the head of the following shard(s) into the
+ * room behind shard g (device to device, peer copy; no kernel reads another GPU's memory), parses every shard on
+ * its own GPU, and exchanges one small table of counters with ncclAllGather, which is left on every device. */
+typedef struct pj_group pj_group;
+
+/* words per shard of the gathered table (uint64 each) */
+enum {
+  PJ_GC_RECORDS = 0, PJ_GC_ERRORS = 1, PJ_GC_BYTES = 2,   /* parse: owned input bytes; write: text bytes produced */
+  PJ_GC_ROWS_PET = 3, PJ_GC_ROWS_ORDER = 4, PJ_GC_ROWS_USER = 5,
+  PJ_GC_COUNTER0 = 8,                                     /* 15 totals: arena bytes and child-table rows, library order */
+  PJ_GROUP_NCOUNT = 24
+};
+
+/* What a group call reports per shard. */
+typedef struct pj_group_shard {
+  uint64_t global_offset;  /* parse: byte offset of the shard in the stream (added to PJ_COL_REC_START);
+                              write: byte offset of the shard's text in the concatenation of all outputs */
+  uint64_t first_record;   /* number, in the whole stream, of the shard's first record                    */
+  uint64_t first_row[4];   /* rows of the model tables that precede the shard's, indexed by PJ_TYPE_*     */
+  uint64_t bytes;          /* parse: input bytes the shard owns; write: text bytes it produced             */
+  uint64_t slack_bytes;    /* parse: bytes of the following shards that were copied behind this one        */
+  const uint64_t* table_dev; /* DEVICE memory of the shard's GPU: the gathered table [ndev][PJ_GROUP_NCOUNT],
+                                valid until the next call on the group                                   */
+  pj_status status;        /* this shard's own status (the call returns the first one that is not PJ_OK)   */
+  float slack_copy_ms;     /* parse: CUDA-event time of the device-to-device copy of the slack bytes        */
+  float gather_ms;         /* host time from "this shard's kernels are done" to "the table is back": the
+                              counter kernel, the all-gather (which waits for the slowest shard) and the read-back */
+  uint32_t reserved;
+} pj_group_shard;
+
+/* `devs` may name a device more than once (several shards per GPU, e.g. to try a group on one GPU): such a group
+ * exchanges its table through the host instead of NCCL. Otherwise NCCL (libnccl.so.2, found with the dynamic
+ * loader's search rules) is initialised with ncclCommInitAll; PJ_ERR_NCCL if that fails. `opt` applies to every
+ * context (device and stream are ignored). */
+pj_status pj_group_create(int32_t ndev, const int32_t* devs, const pj_options* opt, pj_group** out);
+void pj_group_destroy(pj_group* grp);
+int32_t pj_group_size(const pj_group* grp);
+/* the context of shard i (pj_last_stats, pj_last_error); not for concurrent use with a group call */
+pj_ctx* pj_group_ctx(pj_group* grp, int32_t i);
+const char* pj_group_last_error(const pj_group* grp);
+/* 1 when the group exchanges its table with NCCL, 0 when it goes through the host */
+int32_t pj_group_uses_nccl(const pj_group* grp);
+
+/* Replaces ObjectMapper#readValue (MyEntityConfig.java:34) for a stream spread over the group's GPUs.
+ * in[g]: shard g's bytes in device g's memory, len[g] of them, followed by room[g] writable bytes (at least
+ * `slack` for every shard but the last, or a record that straddles the boundary fails with PJ_E_TOO_LONG);
+ * out[g]: shard g's columns, buffers in device g's memory (mem_kind PJ_MEM_DEVICE). Offsets in the columns are
+ * local to the shard; PJ_COL_REC_START is global. shards[g] receives where shard g lies in the whole. */
+pj_status pj_group_parse(pj_group* grp, uint32_t schema, uint8_t* const* in, const uint64_t* len, const uint64_t* room,
+                         uint64_t slack, pj_columns* out, pj_group_shard* shards);
+
+/* Replaces ObjectMapper#writeValueAsBytes (MyEntityController.java:48-51) for tables spread over the group's GPUs:
+ * device g serialises cols[g] (as pj_write, NDJSON framing) into out[g] (cap[g] bytes, device g's memory). The
+ * text of the whole is the concatenation of the outputs in shard order; shards[g].global_offset says where shard
+ * g's text starts in it, shards[g].bytes how long it is. */
+pj_status pj_group_write(pj_group* grp, uint32_t schema, const pj_columns* cols, uint8_t* const* out, const uint64_t* cap,
+                         pj_group_shard* shards);
 
 #ifdef __cplusplus
 }

@@ -57,6 +57,19 @@ def lib() -> C.CDLL:
         L.pj_index_records.argtypes = [C.c_void_p, u32, C.c_void_p, u64, u32, C.c_void_p, u64, C.POINTER(u64)]
         L.pj_index_records_static.argtypes = [C.c_void_p, u64, C.c_void_p, u64, C.c_void_p, C.c_void_p]
         L.pj_write.argtypes = [C.c_void_p, u32, u32, C.POINTER(abi.pj_columns), C.c_void_p, u64, u32, C.POINTER(u64)]
+        L.pj_columns_checksum.argtypes = [C.c_void_p, u32, C.POINTER(abi.pj_columns), C.POINTER(u64)]
+        L.pj_group_create.argtypes = [i32, C.POINTER(i32), C.POINTER(abi.pj_options), C.POINTER(C.c_void_p)]
+        L.pj_group_destroy.argtypes = [C.c_void_p]
+        L.pj_group_destroy.restype = None
+        L.pj_group_size.argtypes = [C.c_void_p]
+        L.pj_group_ctx.argtypes = [C.c_void_p, i32]
+        L.pj_group_ctx.restype = C.c_void_p
+        L.pj_group_last_error.argtypes = [C.c_void_p]
+        L.pj_group_last_error.restype = C.c_char_p
+        L.pj_group_uses_nccl.argtypes = [C.c_void_p]
+        L.pj_group_parse.argtypes = [C.c_void_p, u32, C.POINTER(C.c_void_p), C.POINTER(u64), C.POINTER(u64), u64, C.POINTER(abi.pj_columns),
+                                     C.POINTER(abi.pj_group_shard)]
+        L.pj_group_write.argtypes = [C.c_void_p, u32, C.POINTER(abi.pj_columns), C.POINTER(C.c_void_p), C.POINTER(u64), C.POINTER(abi.pj_group_shard)]
         _lib = L
     return _lib
 
@@ -266,6 +279,12 @@ class Context:
         self._check(st, "pj_index_records", (abi.PJ_ERR_CAPACITY,) if allow_capacity else ())
         return int(cnt.value)
 
+    def checksums(self, schema: int, cols) -> dict:
+        """{column name: 64-bit checksum} of a device-resident column set (pj_columns_checksum)."""
+        sums = (u64 * abi.PJ_MAX_COLS)()
+        self._check(lib().pj_columns_checksum(self._h, schema, C.byref(cols.raw), sums), "pj_columns_checksum")
+        return {c.name: int(sums[c.id]) for c in abi.schema_columns(schema)}
+
     def write(self, schema: int, cols, out, framing: int = abi.PJ_FRAMING_NDJSON, allow_capacity: bool = False) -> int:
         """pj_write of `cols` into `out` (numpy / torch uint8); returns the JSON length in bytes."""
         p, cap, kind = self._ptr_len_kind(out)
@@ -283,3 +302,83 @@ def index_records_static(buf, rec_start, n_out, stream: int | None = None) -> No
     st = lib().pj_index_records_static(buf.data_ptr(), buf.numel(), rec_start.data_ptr(), rec_start.numel(), n_out.data_ptr(), stream)
     if st != abi.PJ_OK:
         raise PetJsonError(st, "pj_index_records_static", (lib().pj_last_error(None) or b"").decode())
+
+
+class Group:
+    """Several GPUs of one machine behind one handle (pj_group_*): one context, stream and host thread per shard inside
+    the library. `devices` may repeat a device (several shards on one GPU; the counter table then goes through the
+    host instead of NCCL)."""
+
+    def __init__(self, devices, inclusion: int = abi.PJ_INCLUDE_NON_EMPTY, tile_bytes: int = 0, spin_limit_us: int = 0):
+        self.devices = [int(d) for d in devices]
+        self._h = C.c_void_p()
+        opt = abi.pj_options()
+        opt.device = -1
+        opt.inclusion = inclusion
+        opt.tile_bytes = tile_bytes
+        opt.spin_limit_us = spin_limit_us
+        devs = (i32 * len(self.devices))(*self.devices)
+        st = lib().pj_group_create(len(self.devices), devs, C.byref(opt), C.byref(self._h))
+        if st != abi.PJ_OK:
+            raise PetJsonError(st, "pj_group_create", (lib().pj_last_error(None) or b"").decode())
+
+    def close(self) -> None:
+        if self._h:
+            lib().pj_group_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def uses_nccl(self) -> bool:
+        return bool(lib().pj_group_uses_nccl(self._h))
+
+    def stats(self, i: int) -> abi.pj_call_stats:
+        s = abi.pj_call_stats()
+        lib().pj_last_stats(lib().pj_group_ctx(self._h, i), C.byref(s))
+        return s
+
+    def _cols_array(self, cols):
+        arr = (abi.pj_columns * len(cols))()
+        for k, c in enumerate(cols):
+            C.memmove(C.byref(arr[k]), C.byref(c.raw), C.sizeof(abi.pj_columns))
+        return arr
+
+    def parse(self, schema: int, bufs, lengths, cols, slack: int = 65536, allow_capacity: bool = False):
+        """bufs[g]: a uint8 CUDA tensor on device g holding lengths[g] bytes of shard g and writable room behind them;
+        cols[g]: DeviceColumns on device g. Returns the list of pj_group_shard."""
+        n = len(self.devices)
+        ptrs = (C.c_void_p * n)(*[int(b.data_ptr()) for b in bufs])
+        lens = (u64 * n)(*[int(x) for x in lengths])
+        room = (u64 * n)(*[int(b.numel()) - int(x) for b, x in zip(bufs, lengths)])
+        arr = self._cols_array(cols)
+        shards = (abi.pj_group_shard * n)()
+        st = lib().pj_group_parse(self._h, schema, ptrs, lens, room, slack, arr, shards)
+        for k, c in enumerate(cols):
+            C.memmove(C.byref(c.raw), C.byref(arr[k]), C.sizeof(abi.pj_columns))
+        if st != abi.PJ_OK and not (allow_capacity and st == abi.PJ_ERR_CAPACITY):
+            raise PetJsonError(st, "pj_group_parse", (lib().pj_group_last_error(self._h) or b"").decode())
+        return list(shards)
+
+    def write(self, schema: int, cols, outs, allow_capacity: bool = False):
+        """cols[g]: DeviceColumns on device g; outs[g]: a uint8 CUDA tensor on device g. Returns the list of pj_group_shard
+        (bytes = text length of shard g, global_offset = where it starts in the concatenated text)."""
+        n = len(self.devices)
+        ptrs = (C.c_void_p * n)(*[int(o.data_ptr()) for o in outs])
+        caps = (u64 * n)(*[int(o.numel()) for o in outs])
+        arr = self._cols_array(cols)
+        shards = (abi.pj_group_shard * n)()
+        st = lib().pj_group_write(self._h, schema, arr, ptrs, caps, shards)
+        if st != abi.PJ_OK and not (allow_capacity and st == abi.PJ_ERR_CAPACITY):
+            raise PetJsonError(st, "pj_group_write", (lib().pj_group_last_error(self._h) or b"").decode())
+        return list(shards)

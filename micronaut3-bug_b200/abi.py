@@ -20,6 +20,8 @@ PJ_OK, PJ_ERR_ARG, PJ_ERR_CAPACITY, PJ_ERR_CUDA, PJ_ERR_TIMEOUT, PJ_ERR_NOMEM, P
 ERROR_KIND_NAMES = ["NONE", "SYNTAX", "EOF", "CTRL_CHAR", "BAD_ESCAPE", "BAD_SURROGATE", "UTF8", "TYPE",
                     "NUM_RANGE", "ENUM", "REQUIRED", "DATETIME", "DEPTH", "AMBIGUOUS", "TOO_LONG"]
 
+PJ_ERR_TIMEOUT = 4
+PJ_ERR_NCCL = 7
 PJ_MEM_HOST, PJ_MEM_DEVICE = 0, 1
 PJ_SCHEMA_PET, PJ_SCHEMA_ORDER, PJ_SCHEMA_USER, PJ_SCHEMA_MIXED = 1, 2, 3, 4
 PJ_TYPE_NONE, PJ_TYPE_PET, PJ_TYPE_ORDER, PJ_TYPE_USER = 0, 1, 2, 3
@@ -28,6 +30,9 @@ PJ_INCLUDE_NON_EMPTY, PJ_INCLUDE_NON_NULL, PJ_INCLUDE_ALWAYS = 0, 1, 2
 
 PJ_GEN_ZIPF_LISTS, PJ_GEN_ESCAPES, PJ_GEN_WHITESPACE, PJ_GEN_MALFORMED, PJ_GEN_ARRAY, PJ_GEN_SPARSE = (
     1, 2, 4, 8, 16, 32)
+
+PJ_OPT_ENUM_UNKNOWN_AS_NULL, PJ_OPT_LONE_SURROGATE_REPLACE, PJ_OPT_COERCE_SCALARS, PJ_OPT_HEX_LOWER = 1, 2, 4, 8
+PJ_OPT_TEST_STALL_ONCE = 1 << 31
 
 PJ_MAX_COLS = 64
 
@@ -119,6 +124,15 @@ class pj_columns(C.Structure):
 class pj_options(C.Structure):
     _fields_ = [("device", C.c_int32), ("inclusion", C.c_int32), ("stream", C.c_void_p),
                 ("flags", C.c_uint32), ("host_piece_bytes", C.c_uint32), ("tile_bytes", C.c_uint32), ("spin_limit_us", C.c_uint32)]
+
+
+PJ_GROUP_NCOUNT = 24
+PJ_GC_RECORDS, PJ_GC_ERRORS, PJ_GC_BYTES, PJ_GC_ROWS_PET, PJ_GC_ROWS_ORDER, PJ_GC_ROWS_USER, PJ_GC_COUNTER0 = 0, 1, 2, 3, 4, 5, 8
+
+
+class pj_group_shard(C.Structure):
+    _fields_ = [("global_offset", C.c_uint64), ("first_record", C.c_uint64), ("first_row", C.c_uint64 * 4), ("bytes", C.c_uint64),
+                ("slack_bytes", C.c_uint64), ("table_dev", C.c_void_p), ("status", C.c_int32), ("slack_copy_ms", C.c_float), ("gather_ms", C.c_float), ("reserved", C.c_uint32)]
 
 
 class pj_call_stats(C.Structure):

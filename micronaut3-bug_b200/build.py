@@ -59,7 +59,7 @@ def build_library(force: bool = False, verbose_ptxas: bool = False) -> str:
         jobs.append([nvcc, *NVCC_FLAGS, *extra, f"-DPJ_TILE_SCHEMA={schema}", "-c", os.path.join(CSRC, "pj_tile_inst.cu"), "-o", obj])
     with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
         list(pool.map(_run, jobs))
-    _run([nvcc, "-shared", "-o", LIB, api_o, *tile_objs])
+    _run([nvcc, "-shared", "-o", LIB, api_o, *tile_objs, "-ldl", "-lpthread"])
     return LIB
 
 

@@ -9,6 +9,13 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <chrono>
+#include <condition_variable>
+#include <functional>
+#include <mutex>
+#include <thread>
+#include <vector>
+#include <dlfcn.h>
 #include <new>
 
 #include "petjson.h"
@@ -108,6 +115,7 @@ struct pj_ctx {
   cudaEvent_t ev_in[16] = {};
   uint32_t piece_bytes = 0;
   uint32_t opt_flags = 0;
+  bool stall_once = false; /* PJ_OPT_TEST_STALL_ONCE, not yet used up */
   Schema schema;
   pj_call_stats stats = {};
   char err[256] = "";
@@ -348,6 +356,10 @@ pj_status parse_stream(pj_ctx* c, uint32_t schema, const uint8_t* in, uint64_t l
   { pj_status st = ensure(c, &c->tiles, nt_total * sizeof(StreamTile) + (size_t)np * 256 + 256); if (st) return st; }
   PJ_CUDA(c, cudaMemsetAsync(c->tiles.p, 0, nt_total * sizeof(StreamTile) + (size_t)np * 256, c->stream));
   PJ_CUDA(c, cudaMemsetAsync(c->d_res, 0, sizeof(DevResult) * np, c->stream));
+  if (c->stall_once) { /* test hook: tickets start at 1, tile 0 is never processed, the waits for it run out */
+    c->stall_once = false;
+    for (int p = 0; p < np; ++p) PJ_CUDA(c, cudaMemsetAsync((uint8_t*)c->tiles.p + (size_t)p * 256, 1, 1, c->stream));
+  }
   c->stats.tile_records = ST_THREADS;
   uint64_t tiles_at = 0;
   for (int p = 0; p < np; ++p) {
@@ -359,6 +371,7 @@ pj_status parse_stream(pj_ctx* c, uint32_t schema, const uint8_t* in, uint64_t l
     sa.is_first = (uint32_t)is_first; sa.is_last = (uint32_t)is_last;
     sa.tile_bytes = tile_bytes; sa.ntiles = (uint32_t)nt[p];
     sa.spin_limit_ns = c->spin_ns;
+    sa.opts = c->opt_flags;
     sa.ticket = (uint32_t*)((uint8_t*)c->tiles.p + (size_t)p * 256);
     sa.tiles = (StreamTile*)((uint8_t*)c->tiles.p + (size_t)np * 256) + tiles_at;
     tiles_at += nt[p];
@@ -495,6 +508,7 @@ pj_status parse_array(pj_ctx* c, uint32_t schema, const uint8_t* in, uint64_t le
   const uint64_t ntiles = N0 ? (N0 + TILE_THREADS - 1) / TILE_THREADS : 1;
   ta.ntiles = (uint32_t)ntiles;
   ta.spin_limit_ns = c->spin_ns;
+  ta.opts = c->opt_flags;
   c->stats.tile_records = TILE_THREADS; c->stats.tiles += (uint32_t)ntiles;
   ta.rec_end = d_rec_end; ta.rec_blank = d_rec_blank;
   { pj_status st = ensure(c, &c->tiles, ntiles * sizeof(TileState) + 256); if (st) return st; }
@@ -608,6 +622,7 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   c->device = dev;
   c->inclusion = opt ? opt->inclusion : PJ_INCLUDE_NON_EMPTY;
   c->opt_flags = opt ? opt->flags : 0;
+  c->stall_once = (c->opt_flags & PJ_OPT_TEST_STALL_ONCE) != 0;
   c->piece_bytes = opt ? opt->host_piece_bytes : 0;
   c->tile_bytes_opt = opt ? opt->tile_bytes : 0;
   if (opt && opt->spin_limit_us) c->spin_ns = (unsigned long long)opt->spin_limit_us * 1000ull;
@@ -895,6 +910,7 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
   PJ_CUDA(c, cudaMemcpyAsync(c->d_res, c->h_res, sizeof(DevResult), cudaMemcpyHostToDevice, c->stream));
   WriteArgs wa;
   wa.n = n; wa.schema = schema; wa.array = framing == PJ_FRAMING_ARRAY; wa.inclusion = c->inclusion;
+  wa.hexa = (c->opt_flags & PJ_OPT_HEX_LOWER) ? 'a' : 'A';
   wa.out = d_out; wa.cap = cap; wa.res = c->d_res; wa.cols = dcols;
   {
     /* the single-pass tile writer; stages: [0] state reset and the look at the string arenas, [1] the closing kernel, [2] the tile kernel */
@@ -960,6 +976,370 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
     c->stats.d2h_bytes += *out_len;
   }
   return PJ_OK;
+}
+
+pj_status pj_columns_checksum(pj_ctx* c, uint32_t schema, const pj_columns* cols, uint64_t* sums) {
+  if (!c) return PJ_ERR_ARG;
+  if (!cols || !sums || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED || cols->mem_kind != PJ_MEM_DEVICE) return set_err(c, PJ_ERR_ARG, "pj_columns_checksum: bad argument");
+  DeviceGuard guard(c->device);
+  c->stats = pj_call_stats{};
+  FinalizePlan plan;
+  build_finalize_plan(c->schema, schema, &plan);
+  int rcols[5];
+  const int nrc = record_cols(schema, rcols);
+  ChecksumArgs a;
+  memset(&a, 0, sizeof a);
+  uint64_t most = 0, bytes = 0;
+  auto add = [&](int col) {
+    const uint64_t nb = cols->col[col].count * col_info(col)->elem;
+    a.p[col] = (const uint8_t*)cols->col[col].ptr; a.n[col] = a.p[col] ? nb : 0;
+    if (a.n[col] > most) most = a.n[col];
+    bytes += a.n[col];
+  };
+  for (int i = 0; i < nrc; ++i) add(rcols[i]);
+  for (uint32_t k = 0; k < plan.n; ++k) add(plan.item[k].col);
+  { pj_status st = ensure(c, &c->scratch, sizeof(unsigned long long) * PJ_MAX_COLS + 256); if (st) return st; }
+  a.out = (unsigned long long*)c->scratch.p;
+  PJ_CUDA(c, cudaMemsetAsync(a.out, 0, sizeof(unsigned long long) * PJ_MAX_COLS, c->stream));
+  Stage stage(c);
+  dim3 grid((unsigned)persistent_grid(c, most / 8 + 1, 256), PJ_MAX_COLS);
+  k_checksum<<<grid, 256, 0, c->stream>>>(a);
+  count_launch(c, 0);
+  PJ_CUDA(c, cudaGetLastError());
+  stage.next();
+  PJ_CUDA(c, cudaMemcpyAsync(sums, a.out, sizeof(uint64_t) * PJ_MAX_COLS, cudaMemcpyDeviceToHost, c->stream));
+  PJ_CUDA(c, cudaStreamSynchronize(c->stream));
+  collect_times(c, 1);
+  c->stats.main_kernel_ms = c->stats.stage_ms[0];
+  c->stats.algorithmic_bytes = bytes;
+  c->stats.d2h_bytes = sizeof(uint64_t) * PJ_MAX_COLS;
+  return PJ_OK;
+}
+
+}  // extern "C"
+
+/* ================================================================================================
+ * Several GPUs of one machine: pj_group_*
+ *
+ * One process, one pj_ctx, one stream and one host thread per shard. The threads are started once (pj_group_create)
+ * and sleep between calls. NCCL is bound at run time (dlopen), so the library loads on machines without it; only
+ * ncclCommInitAll / ncclAllGather / ncclCommDestroy / ncclGetErrorString are used.
+ * ================================================================================================ */
+namespace {
+
+typedef struct ncclComm* pj_nccl_comm;
+struct NcclApi {
+  void* handle = nullptr;
+  int (*CommInitAll)(pj_nccl_comm*, int, const int*) = nullptr;
+  int (*CommDestroy)(pj_nccl_comm) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, pj_nccl_comm, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  bool load() {
+    if (handle) return true;
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) { handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL); if (handle) break; }
+    if (!handle) return false;
+    CommInitAll = (int (*)(pj_nccl_comm*, int, const int*))dlsym(handle, "ncclCommInitAll");
+    CommDestroy = (int (*)(pj_nccl_comm))dlsym(handle, "ncclCommDestroy");
+    AllGather = (int (*)(const void*, void*, size_t, int, pj_nccl_comm, cudaStream_t))dlsym(handle, "ncclAllGather");
+    GetErrorString = (const char* (*)(int))dlsym(handle, "ncclGetErrorString");
+    return CommInitAll && CommDestroy && AllGather && GetErrorString;
+  }
+};
+constexpr int PJ_NCCL_UINT64 = 5; /* ncclUint64 */
+
+/* a host thread that runs one job at a time */
+struct Worker {
+  std::thread th;
+  std::mutex m;
+  std::condition_variable cv;
+  std::function<void()> job;
+  bool has_job = false, stop = false, done = true;
+  void start() {
+    th = std::thread([this] {
+      std::unique_lock<std::mutex> lk(m);
+      for (;;) {
+        cv.wait(lk, [this] { return has_job || stop; });
+        if (stop) return;
+        std::function<void()> j = std::move(job);
+        has_job = false;
+        lk.unlock();
+        j();
+        lk.lock();
+        done = true;
+        cv.notify_all();
+      }
+    });
+  }
+  void submit(std::function<void()> j) {
+    std::lock_guard<std::mutex> lk(m);
+    job = std::move(j); has_job = true; done = false;
+    cv.notify_all();
+  }
+  void wait() {
+    std::unique_lock<std::mutex> lk(m);
+    cv.wait(lk, [this] { return done; });
+  }
+  void finish() {
+    { std::lock_guard<std::mutex> lk(m); stop = true; cv.notify_all(); }
+    if (th.joinable()) th.join();
+  }
+};
+
+/* the counters of one shard, as the gathered table holds them, from the result block of its last launch */
+__global__ void k_group_counters(const DevResult* res, uint64_t bytes, unsigned long long* out /*[PJ_GROUP_NCOUNT]*/) {
+  const uint32_t k = threadIdx.x;
+  if (k >= PJ_GROUP_NCOUNT) return;
+  unsigned long long v = 0;
+  if (k == PJ_GC_RECORDS) v = res->n_records;
+  else if (k == PJ_GC_ERRORS) v = res->n_errors;
+  else if (k == PJ_GC_BYTES) v = bytes ? bytes : res->out_bytes;
+  else if (k == PJ_GC_ROWS_PET) v = res->total[SLOT_ROWS_PET];
+  else if (k == PJ_GC_ROWS_ORDER) v = res->total[SLOT_ROWS_ORD];
+  else if (k == PJ_GC_ROWS_USER) v = res->total[SLOT_ROWS_USR];
+  else if (k >= PJ_GC_COUNTER0 && k < PJ_GC_COUNTER0 + NSLOT) v = res->total[k - PJ_GC_COUNTER0];
+  out[k] = v;
+}
+
+}  // namespace
+
+struct pj_group {
+  int ndev = 0;
+  std::vector<int> devs;
+  std::vector<pj_ctx*> ctx;
+  std::vector<Worker*> workers;
+  std::vector<pj_nccl_comm> comms;
+  std::vector<unsigned long long*> d_mine;  /* [PJ_GROUP_NCOUNT] on the shard's device */
+  std::vector<unsigned long long*> d_table; /* [ndev][PJ_GROUP_NCOUNT] on the shard's device */
+  std::vector<unsigned long long*> h_table; /* pinned copy per shard */
+  bool nccl = false;
+  NcclApi api;
+  char err[256] = "";
+};
+
+namespace {
+
+pj_status group_err(pj_group* g, pj_status st, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g ? g->err : g_create_error, 256, fmt, ap);
+  va_end(ap);
+  return st;
+}
+
+template <class F>
+void group_run(pj_group* g, F&& fn) {
+  for (int i = 0; i < g->ndev; ++i) g->workers[i]->submit([&fn, i] { fn(i); });
+  for (int i = 0; i < g->ndev; ++i) g->workers[i]->wait();
+}
+
+/* After every shard's kernels are enqueued: its counters go into the table that every device ends up with.
+ * `res_index`: which result block of the context holds the call's last totals; `bytes`: PJ_GC_BYTES (0: the
+ * writer's byte count from the result block). Called on the shard's thread, its device current. */
+pj_status group_gather(pj_group* g, int i, int res_index, uint64_t bytes) {
+  pj_ctx* c = g->ctx[i];
+  k_group_counters<<<1, 32, 0, c->stream>>>(c->d_res + res_index, bytes, g->d_mine[i]);
+  if (cudaGetLastError() != cudaSuccess) return PJ_ERR_CUDA;
+  if (g->nccl) {
+    const int r = g->api.AllGather(g->d_mine[i], g->d_table[i], PJ_GROUP_NCOUNT, PJ_NCCL_UINT64, g->comms[i], c->stream);
+    if (r != 0) return set_err(c, PJ_ERR_NCCL, "ncclAllGather: %s", g->api.GetErrorString(r));
+    if (cudaMemcpyAsync(g->h_table[i], g->d_table[i], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess) return PJ_ERR_CUDA;
+  } else {
+    /* through the host: own counters down now, the assembled table up once every shard has delivered (group_spread) */
+    if (cudaMemcpyAsync(g->h_table[i] + (size_t)i * PJ_GROUP_NCOUNT, g->d_mine[i], sizeof(unsigned long long) * PJ_GROUP_NCOUNT, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess) return PJ_ERR_CUDA;
+  }
+  if (cudaStreamSynchronize(c->stream) != cudaSuccess) return PJ_ERR_CUDA;
+  return PJ_OK;
+}
+/* host exchange, second half: every shard's row of the table to every device */
+pj_status group_spread(pj_group* g) {
+  if (g->nccl) return PJ_OK;
+  for (int i = 1; i < g->ndev; ++i) memcpy(g->h_table[0] + (size_t)i * PJ_GROUP_NCOUNT, g->h_table[i] + (size_t)i * PJ_GROUP_NCOUNT, sizeof(unsigned long long) * PJ_GROUP_NCOUNT);
+  for (int i = 1; i < g->ndev; ++i) memcpy(g->h_table[i], g->h_table[0], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev);
+  pj_status st = PJ_OK;
+  group_run(g, [&](int i) {
+    DeviceGuard guard(g->devs[i]);
+    pj_ctx* c = g->ctx[i];
+    if (cudaMemcpyAsync(g->d_table[i], g->h_table[i], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev, cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+        cudaStreamSynchronize(c->stream) != cudaSuccess)
+      st = PJ_ERR_CUDA;
+  });
+  return st;
+}
+void group_fill(pj_group* g, pj_group_shard* shards, bool offsets_from_bytes) {
+  uint64_t off = 0, rec = 0, rows[4] = {0, 0, 0, 0};
+  for (int i = 0; i < g->ndev; ++i) {
+    const unsigned long long* t = g->h_table[0] + (size_t)i * PJ_GROUP_NCOUNT;
+    if (offsets_from_bytes) shards[i].global_offset = off;
+    shards[i].first_record = rec;
+    shards[i].first_row[0] = 0;
+    for (int k = 1; k < 4; ++k) shards[i].first_row[k] = rows[k];
+    shards[i].bytes = t[PJ_GC_BYTES];
+    shards[i].table_dev = (const uint64_t*)g->d_table[i];
+    off += t[PJ_GC_BYTES]; rec += t[PJ_GC_RECORDS];
+    rows[1] += t[PJ_GC_ROWS_PET]; rows[2] += t[PJ_GC_ROWS_ORDER]; rows[3] += t[PJ_GC_ROWS_USER];
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+pj_status pj_group_create(int32_t ndev, const int32_t* devs, const pj_options* opt, pj_group** out) {
+  if (!out || ndev < 1 || ndev > 64 || !devs) return PJ_ERR_ARG;
+  *out = nullptr;
+  pj_group* g = new (std::nothrow) pj_group();
+  if (!g) return PJ_ERR_NOMEM;
+  g->ndev = ndev;
+  bool distinct = true;
+  for (int i = 0; i < ndev; ++i) {
+    for (int k = 0; k < i; ++k) if (devs[k] == devs[i]) distinct = false;
+    g->devs.push_back(devs[i]);
+  }
+  pj_status st = PJ_OK;
+  for (int i = 0; i < ndev && st == PJ_OK; ++i) {
+    pj_options o;
+    memset(&o, 0, sizeof o);
+    if (opt) o = *opt;
+    o.device = devs[i]; o.stream = nullptr;
+    pj_ctx* c = nullptr;
+    st = pj_create(&o, &c);
+    if (st != PJ_OK) break;
+    g->ctx.push_back(c);
+    DeviceGuard guard(devs[i]);
+    unsigned long long *mine = nullptr, *table = nullptr, *host = nullptr;
+    if (cudaMalloc(&mine, sizeof(unsigned long long) * PJ_GROUP_NCOUNT) != cudaSuccess ||
+        cudaMalloc(&table, sizeof(unsigned long long) * PJ_GROUP_NCOUNT * ndev) != cudaSuccess ||
+        cudaMallocHost(&host, sizeof(unsigned long long) * PJ_GROUP_NCOUNT * ndev) != cudaSuccess) {
+      (void)cudaGetLastError();
+      st = set_err(nullptr, PJ_ERR_NOMEM, "pj_group_create: allocation failed on device %d", devs[i]);
+    }
+    g->d_mine.push_back(mine); g->d_table.push_back(table); g->h_table.push_back(host);
+    /* every device may read its neighbours' input buffers (the slack copy) */
+    for (int k = 0; k < ndev && st == PJ_OK; ++k) {
+      if (devs[k] == devs[i]) continue;
+      int can = 0;
+      cudaDeviceCanAccessPeer(&can, devs[i], devs[k]);
+      if (can) { cudaError_t e = cudaDeviceEnablePeerAccess(devs[k], 0); if (e != cudaSuccess) (void)cudaGetLastError(); /* already enabled is fine; without it the copy is staged by the driver */ }
+    }
+  }
+  if (st == PJ_OK && distinct) {
+    if (!g->api.load()) st = set_err(nullptr, PJ_ERR_NCCL, "pj_group_create: libnccl.so.2 could not be loaded (%s)", dlerror() ? dlerror() : "symbols missing");
+    else {
+      g->comms.resize(ndev);
+      const int r = g->api.CommInitAll(g->comms.data(), ndev, g->devs.data());
+      if (r != 0) { g->comms.clear(); st = set_err(nullptr, PJ_ERR_NCCL, "ncclCommInitAll: %s", g->api.GetErrorString(r)); }
+      else g->nccl = true;
+    }
+  }
+  if (st != PJ_OK) { pj_group_destroy(g); return st; }
+  for (int i = 0; i < ndev; ++i) { Worker* w = new Worker(); w->start(); g->workers.push_back(w); }
+  *out = g;
+  return PJ_OK;
+}
+
+void pj_group_destroy(pj_group* g) {
+  if (!g) return;
+  for (Worker* w : g->workers) { w->finish(); delete w; }
+  for (size_t i = 0; i < g->comms.size(); ++i) if (g->comms[i]) g->api.CommDestroy(g->comms[i]);
+  for (size_t i = 0; i < g->d_mine.size(); ++i) {
+    DeviceGuard guard(g->devs[i]);
+    if (g->d_mine[i]) cudaFree(g->d_mine[i]);
+    if (g->d_table[i]) cudaFree(g->d_table[i]);
+    if (g->h_table[i]) cudaFreeHost(g->h_table[i]);
+  }
+  for (pj_ctx* c : g->ctx) pj_destroy(c);
+  delete g;
+}
+
+int32_t pj_group_size(const pj_group* g) { return g ? g->ndev : 0; }
+pj_ctx* pj_group_ctx(pj_group* g, int32_t i) { return g && i >= 0 && i < g->ndev ? g->ctx[i] : nullptr; }
+const char* pj_group_last_error(const pj_group* g) { return g ? g->err : g_create_error; }
+int32_t pj_group_uses_nccl(const pj_group* g) { return g && g->nccl ? 1 : 0; }
+
+pj_status pj_group_parse(pj_group* g, uint32_t schema, uint8_t* const* in, const uint64_t* len, const uint64_t* room, uint64_t slack,
+                         pj_columns* out, pj_group_shard* shards) {
+  if (!g) return PJ_ERR_ARG;
+  if (!in || !len || !room || !out || !shards || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED) return group_err(g, PJ_ERR_ARG, "pj_group_parse: bad argument");
+  const int n = g->ndev;
+  std::vector<uint64_t> goff(n + 1, 0);
+  for (int i = 0; i < n; ++i) {
+    if (!in[i] && (len[i] || room[i])) return group_err(g, PJ_ERR_ARG, "pj_group_parse: shard %d has no buffer", i);
+    if (out[i].mem_kind != PJ_MEM_DEVICE) return group_err(g, PJ_ERR_ARG, "pj_group_parse: columns of shard %d are not device memory", i);
+    goff[i + 1] = goff[i] + len[i];
+  }
+  group_run(g, [&](int i) {
+    DeviceGuard guard(g->devs[i]);
+    pj_ctx* c = g->ctx[i];
+    pj_group_shard& S = shards[i];
+    memset(&S, 0, sizeof S);
+    S.global_offset = goff[i];
+    /* the head of what follows becomes this shard's slack: from as many following shards as it takes */
+    uint64_t want = slack < room[i] ? slack : room[i], got = 0;
+    cudaEventRecord(c->ev[6], c->stream);
+    for (int h = i + 1; h < n && got < want; ++h) {
+      const uint64_t take = len[h] < want - got ? len[h] : want - got;
+      if (take) {
+        const cudaError_t e = cudaMemcpyPeerAsync(in[i] + len[i] + got, g->devs[i], in[h], g->devs[h], take, c->stream);
+        if (e != cudaSuccess) { S.status = set_err(c, PJ_ERR_CUDA, "cudaMemcpyPeerAsync: %s", cudaGetErrorString(e)); return; }
+      }
+      got += take;
+    }
+    cudaEventRecord(c->ev[7], c->stream);
+    S.slack_bytes = got;
+    const bool is_last = goff[i] + len[i] + got == goff[n]; /* the readable bytes reach the end of the stream */
+    const bool is_first = goff[i] == 0;                     /* nothing precedes: the line at byte 0 is this shard's */
+    S.status = parse_impl(c, schema, PJ_FRAMING_NDJSON, in[i], len[i], got, is_first, is_last, goff[i], PJ_MEM_DEVICE, &out[i]);
+    if (S.status != PJ_OK && S.status != PJ_ERR_CAPACITY) {
+      /* the table must still be exchanged by every shard (a collective): deliver zeros */
+      cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream);
+    }
+    if (cudaEventElapsedTime(&S.slack_copy_ms, c->ev[6], c->ev[7]) != cudaSuccess) { S.slack_copy_ms = 0.f; (void)cudaGetLastError(); }
+  });
+  /* The exchange starts only when EVERY shard is through its parse: an all-gather kernel waits on its device for the
+     other devices' kernels, and a cudaMalloc on one of those (a parse growing its scratch) waits for the first device
+     to go idle, because new memory is mapped into the peers: together they would never finish. Nothing allocates
+     from here on. */
+  group_run(g, [&](int i) {
+    DeviceGuard guard(g->devs[i]);
+    pj_group_shard& S = shards[i];
+    const auto t0 = std::chrono::steady_clock::now();
+    const pj_status gs = group_gather(g, i, 0, len[i] ? len[i] : ~0ull);
+    S.gather_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (S.status == PJ_OK) S.status = gs;
+  });
+  pj_status st = group_spread(g);
+  group_fill(g, shards, false);
+  for (int i = 0; i < n; ++i) if (shards[i].bytes == ~0ull) shards[i].bytes = 0;
+  for (int i = 0; i < n && st == PJ_OK; ++i) if (shards[i].status != PJ_OK) { st = shards[i].status; group_err(g, st, "shard %d: %s", i, pj_last_error(g->ctx[i])); }
+  return st;
+}
+
+pj_status pj_group_write(pj_group* g, uint32_t schema, const pj_columns* cols, uint8_t* const* out, const uint64_t* cap, pj_group_shard* shards) {
+  if (!g) return PJ_ERR_ARG;
+  if (!cols || !out || !cap || !shards || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED) return group_err(g, PJ_ERR_ARG, "pj_group_write: bad argument");
+  const int n = g->ndev;
+  group_run(g, [&](int i) {
+    DeviceGuard guard(g->devs[i]);
+    pj_ctx* c = g->ctx[i];
+    pj_group_shard& S = shards[i];
+    memset(&S, 0, sizeof S);
+    uint64_t out_len = 0;
+    S.status = pj_write(c, schema, PJ_FRAMING_NDJSON, &cols[i], out[i], cap[i], PJ_MEM_DEVICE, &out_len);
+    if (S.status != PJ_OK && S.status != PJ_ERR_CAPACITY) cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream);
+  });
+  group_run(g, [&](int i) { /* the exchange, once no shard allocates any more (see pj_group_parse) */
+    DeviceGuard guard(g->devs[i]);
+    pj_group_shard& S = shards[i];
+    const auto t0 = std::chrono::steady_clock::now();
+    const pj_status gs = group_gather(g, i, 0, 0);
+    S.gather_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (S.status == PJ_OK) S.status = gs;
+  });
+  pj_status st = group_spread(g);
+  group_fill(g, shards, true);
+  for (int i = 0; i < n && st == PJ_OK; ++i) if (shards[i].status != PJ_OK) { st = shards[i].status; group_err(g, st, "shard %d: %s", i, pj_last_error(g->ctx[i])); }
+  return st;
 }
 
 }  // extern "C"

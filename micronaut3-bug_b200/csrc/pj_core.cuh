@@ -34,6 +34,7 @@ struct Rd {
   uint64_t limit;    /* first unreadable offset */
   uint32_t lf_ws;    /* array framing: LF is whitespace; otherwise LF ends the record */
   uint32_t open_end; /* the stream continues past `limit` (a shard's slack ran out) */
+  uint32_t opts;     /* PJ_OPT_* bits that change a rule (enum, surrogate, coercion) */
 };
 
 struct PS {
@@ -130,6 +131,17 @@ PJ_HD_NOINLINE bool lex_string(const Rd& r, PS& s, Sink& k) {
         case 't': cp = 9; break;
         case 'u': {
           if (!hex4(r, s, p + 2, &cp)) return false;
+          if (r.opts & PJ_OPT_LONE_SURROGATE_REPLACE) {
+            /* a high surrogate takes the low one that follows it at once; whatever is left alone becomes U+FFFD */
+            if (cp - 0xD800u < 0x400u && rd_get(r, p + 6) == '\\' && rd_get(r, p + 7) == 'u') {
+              uint32_t lo;
+              if (!hex4(r, s, p + 8, &lo)) return false;
+              if (lo - 0xDC00u < 0x400u) { cp = 0x10000u + ((cp - 0xD800u) << 10) + (lo - 0xDC00u); p += 6; }
+            }
+            if (cp - 0xD800u < 0x800u) cp = 0xFFFDu;
+            p += 4;
+            break;
+          }
           if (cp - 0xDC00u < 0x400u) return fail(s, PJ_E_BAD_SURROGATE, p);
           if (cp - 0xD800u < 0x400u) {
             if (rd_get(r, p + 6) != '\\') return fail_byte(r, s, p + 6, PJ_E_BAD_SURROGATE, p);
@@ -382,8 +394,37 @@ PJ_HD void store_object(const ObjDesc& O, const ObjVals& v, uint64_t row, const 
   }
 }
 
+/* PJ_OPT_COERCE_SCALARS: the integer held by a decoded string (k: SINK_PACK). 0 = ok, else the failure kind. */
+PJ_HD uint32_t sink_to_int(const Sink& k, bool is64, int64_t* out) {
+  if (k.n == 0 || k.n > 20) return PJ_E_TYPE;
+  uint32_t i = 0;
+  const bool neg = sink_byte(k, 0) == '-';
+  if (neg) i = 1;
+  if (i >= k.n) return PJ_E_TYPE;
+  if (sink_byte(k, i) == '0' && i + 1 < k.n) return PJ_E_TYPE;
+  uint64_t mag = 0;
+  bool over = false;
+  for (; i < k.n; ++i) {
+    const uint32_t d = sink_byte(k, i) - '0';
+    if (d > 9u) return PJ_E_TYPE;
+    if (mag > (0xFFFFFFFFFFFFFFFFull - d) / 10) over = true; else mag = mag * 10 + d;
+  }
+  const uint64_t lim = is64 ? (neg ? 0x8000000000000000ull : 0x7FFFFFFFFFFFFFFFull) : (neg ? 0x80000000ull : 0x7FFFFFFFull);
+  if (over || mag > lim) return PJ_E_NUM_RANGE;
+  *out = neg ? (int64_t)(0 - mag) : (int64_t)mag;
+  return 0;
+}
+
 /* R5 / R6 for an integer property: x is the byte at s.p (not 'n'). */
 PJ_HD bool read_int(const Rd& r, PS& s, uint32_t x, bool is64, int64_t* out) {
+  if (x == '"' && (r.opts & PJ_OPT_COERCE_SCALARS)) {
+    const uint64_t q = s.p;
+    Sink k;
+    sink_init(k, SINK_PACK);
+    if (!lex_string(r, s, k)) return false;
+    const uint32_t e = sink_to_int(k, is64, out);
+    return e ? fail(s, e, q) : true;
+  }
   if (!(x == '-' || x - '0' <= 9u)) return fail_first(r, s, x);
   Num n;
   if (!lex_number(r, s, n)) return false;
@@ -420,12 +461,22 @@ PJ_HD bool read_scalar(const Schema& S, const Rd& r, PS& s, const FieldDesc& F, 
     case K_BOOL: {
       if (x == 't') { if (!lex_literal(r, s, PJ_LIT_RUE, 3)) return false; v.v[i] = 1; }
       else if (x == 'f') { if (!lex_literal(r, s, PJ_LIT_ALSE, 4)) return false; v.v[i] = 0; }
+      else if (x == '"' && (r.opts & PJ_OPT_COERCE_SCALARS)) {
+        const uint64_t q = s.p;
+        Sink k;
+        sink_init(k, SINK_PACK);
+        if (!lex_string(r, s, k)) return false;
+        if (k.n == 4 && k.w[0] == 0x65757274ull) v.v[i] = 1;
+        else if (k.n == 5 && k.w[0] == 0x65736C6166ull) v.v[i] = 0;
+        else return fail(s, PJ_E_TYPE, q);
+      }
       else return fail_first(r, s, x);
       v.present |= bit;
       return true;
     }
     case K_STR: {
-      if (x != '"') return fail_first(r, s, x);
+      const bool coerce = (r.opts & PJ_OPT_COERCE_SCALARS) && (x == '-' || x - '0' <= 9u || x == 't' || x == 'f');
+      if (x != '"' && !coerce) return fail_first(r, s, x);
       Sink k;
       sink_init(k, (W && live) ? SINK_WRITE : SINK_COUNT);
       if (W && live) {
@@ -433,6 +484,13 @@ PJ_HD bool read_scalar(const Schema& S, const Rd& r, PS& s, const FieldDesc& F, 
         k.room = rm > start ? rm - start : 0;
         k.dst = colp<uint8_t>(o.cols, F.col + 1) + o.base[F.cnt] + start;
       }
+      if (coerce) { /* the token's text, as written, becomes the string */
+        const uint64_t t0 = s.p;
+        if (x == 't') { if (!lex_literal(r, s, PJ_LIT_RUE, 3)) return false; }
+        else if (x == 'f') { if (!lex_literal(r, s, PJ_LIT_ALSE, 4)) return false; }
+        else { Num n; if (!lex_number(r, s, n)) return false; }
+        for (uint64_t q = t0; q < s.p; ++q) sink_put(k, rd_get(r, q));
+      } else
       if (!lex_string(r, s, k)) return false;
       o.cnt[F.cnt] = start + k.n;
       v.present |= bit;
@@ -445,7 +503,11 @@ PJ_HD bool read_scalar(const Schema& S, const Rd& r, PS& s, const FieldDesc& F, 
       sink_init(k, SINK_PACK);
       if (!lex_string(r, s, k)) return false;
       int e = sink_small(k) ? find_enum(S.en[F.child], k.n, k.w[0], k.w[1]) : -1;
-      if (e < 0) return fail(s, PJ_E_ENUM, q);
+      if (e < 0) {
+        if (!(r.opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL)) return fail(s, PJ_E_ENUM, q);
+        v.present &= ~bit; v.v[i] = 0; /* unknown literal: the property stays absent */
+        return true;
+      }
       v.v[i] = e; v.present |= bit;
       return true;
     }
@@ -553,9 +615,9 @@ PJ_HD uint32_t parse_record(const Schema& S, const Rd& r, PS& s, uint32_t schema
         if (have_id) { v.v[0] = early_id; v.present |= 1; }
         if (have_status && type != PJ_TYPE_USER) {
           int e = type == PJ_TYPE_PET ? st_pet : st_ord;
-          if (e < 0) { fail(s, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; }
           int fi = type == PJ_TYPE_PET ? 5 : 4;
-          v.v[fi] = e; v.present |= 1u << fi;
+          if (e >= 0) { v.v[fi] = e; v.present |= 1u << fi; }
+          else if (!(r.opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL)) { fail(s, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; }
         }
       } else if (owners == 3) { /* `id`, int64 in every model */
         uint32_t y = rd_get(r, s.p);
@@ -574,7 +636,7 @@ PJ_HD uint32_t parse_record(const Schema& S, const Rd& r, PS& s, uint32_t schema
         bool sm = sink_small(e);
         st_pet = sm ? find_enum(S.en[0], e.n, e.w[0], e.w[1]) : -1;
         st_ord = sm ? find_enum(S.en[1], e.n, e.w[0], e.w[1]) : -1;
-        if (st_pet < 0 && st_ord < 0) { fail(s, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; }
+        if (st_pet < 0 && st_ord < 0 && !(r.opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL)) { fail(s, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; }
         have_status = true;
         continue;
       } else {

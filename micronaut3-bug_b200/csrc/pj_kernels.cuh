@@ -53,6 +53,13 @@ static constexpr int INDEX_THREADS = 256;
 static constexpr int INDEX_BYTES_PER_THREAD = 64;
 static constexpr int INDEX_TILE = INDEX_THREADS * INDEX_BYTES_PER_THREAD; /* 16 KiB */
 
+/* A failure the word-at-a-time paths report that an option turns into something else (an unknown enum literal into an
+ * absent property, a value of another JSON type into a coerced one): such records go to the exact parser, which
+ * knows the options. */
+__device__ __forceinline__ bool opt_decides(uint32_t opts, uint32_t kind) {
+  return ((opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL) && kind == PJ_E_ENUM) || ((opts & PJ_OPT_COERCE_SCALARS) && kind == PJ_E_TYPE);
+}
+
 /* ---- block-wide exclusive scan ---------------------------------------------------------------- */
 template <class T>
 __device__ __forceinline__ T warp_incl_scan(T v) {
@@ -183,6 +190,7 @@ struct WriteArgs {
   uint64_t n;             /* records (mixed) or rows */
   uint32_t schema, array; /* array: wrap as [r,r,...] */
   int inclusion;
+  uint32_t hexa;          /* 'A' or 'a': hex letters of \u00xx escapes */
   uint8_t* out;
   uint64_t cap;
   DevResult* res;
@@ -229,6 +237,7 @@ struct TileArgs {
   uint32_t lf_ws, open_end, schema, slot_lo, slot_hi;
   uint32_t tile_recs, ntiles, win_bytes, tape_cap;
   unsigned long long spin_limit_ns; /* bound of every wait on another block or on the staging copy */
+  uint32_t opts;                    /* PJ_OPT_* bits that change a rule */
   const uint64_t* rec_end;  /* array framing: end of every extent, else null */
   const uint8_t* rec_blank; /* array framing: extent without a value */
   TileState* tiles;
@@ -521,6 +530,7 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
         for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = cnt_d[k];
       }
       fast = verdict == FAST_ACCEPTED;
+      if (verdict == FAST_FAILED && opt_decides(a.opts, err)) { verdict = FAST_REFUSED; err = 0; } /* the exact parser knows the options */
       if (verdict == FAST_FAILED) {
         /* a validation failure found by the word-at-a-time path: no row values, no bytes anywhere */
         type = PJ_TYPE_NONE;
@@ -531,7 +541,7 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
     }
     if (verdict == FAST_REFUSED) {
       Rd r;
-      r.in = fits ? win - w0 : a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end; r.limit = my_limit;
+      r.in = fits ? win - w0 : a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end; r.limit = my_limit; r.opts = a.opts;
       PS s;
       s.p = start; s.err = 0; s.err_pos = 0;
       Out<false> so;
@@ -635,7 +645,7 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
         if (SCHEMA != PJ_SCHEMA_MIXED) store_absent<true>(c_schema, a.schema, o, i);
       } else {
         Rd r;
-        r.in = fits ? win - w0 : a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end; r.limit = my_limit;
+        r.in = fits ? win - w0 : a.in; r.lf_ws = a.lf_ws; r.open_end = a.open_end; r.limit = my_limit; r.opts = a.opts;
         PS s;
         s.p = start; s.err = 0; s.err_pos = 0;
         parse_record<true>(c_schema, r, s, a.schema, o, i);
@@ -790,7 +800,7 @@ static __global__ void __launch_bounds__(TILE_THREADS, 5) k_write_tile(const __g
     if (type == PJ_TYPE_PET) prefetch_row<OBJ_PET>(&a.w.cols, row);
     else if (type == PJ_TYPE_ORDER) prefetch_row<OBJ_ORDER>(&a.w.cols, row);
     else prefetch_row<OBJ_USER>(&a.w.cols, row);
-    WOut w; w.dst = nullptr; w.n = 0;
+    WOut w; w.dst = nullptr; w.n = 0; w.hexa = a.w.hexa;
     if (plain) fwrite_record<false, true>(&a.w.cols, type, row, a.w.inclusion, w); else fwrite_record<false, false>(&a.w.cols, type, row, a.w.inclusion, w);
     len = (uint32_t)w.n + 1; /* LF, or the comma / closing bracket that follows the record */
   }
@@ -829,7 +839,7 @@ static __global__ void __launch_bounds__(TILE_THREADS, 5) k_write_tile(const __g
     /* the window mirrors the output's alignment: window byte k goes to (dst0 - pad)[k] */
     const uint32_t pad = (uint32_t)(reinterpret_cast<uintptr_t>(dst0) & 15u);
     if (located) {
-      WOut w; w.dst = smem + pad + loc; w.n = 0;
+      WOut w; w.dst = smem + pad + loc; w.n = 0; w.hexa = a.w.hexa;
       if (plain) fwrite_record<true, true>(&a.w.cols, type, row, a.w.inclusion, w); else fwrite_record<true, false>(&a.w.cols, type, row, a.w.inclusion, w);
       smem[pad + loc + w.n] = sep;
     }
@@ -849,7 +859,7 @@ static __global__ void __launch_bounds__(TILE_THREADS, 5) k_write_tile(const __g
       for (uint32_t b = pad + tid; b < end; b += TILE_THREADS) gbase[b] = smem[b];
     }
   } else if (located) {
-    WOut w; w.dst = dst0 + loc; w.n = 0;
+    WOut w; w.dst = dst0 + loc; w.n = 0; w.hexa = a.w.hexa;
     if (plain) fwrite_record<true, true>(&a.w.cols, type, row, a.w.inclusion, w); else fwrite_record<true, false>(&a.w.cols, type, row, a.w.inclusion, w);
     dst0[loc + w.n] = sep;
   }
@@ -871,6 +881,37 @@ static __global__ void k_write_close(const __grid_constant__ WriteArgs a) {
   const bool ok = a.res->ok && total <= a.cap;
   a.res->ok = ok;
   if (a.array && ok) { a.out[0] = '['; a.out[total - 1] = ']'; }
+}
+
+/* ---- column checksums --------------------------------------------------------------------------------- */
+PJ_HD uint64_t checksum_mix(uint64_t x) {
+  x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+  x ^= x >> 27; x *= 0x94D049BB133111EBull;
+  x ^= x >> 31;
+  return x;
+}
+PJ_HD uint64_t checksum_term(uint64_t word, uint64_t j) { return checksum_mix(word + 0x9E3779B97F4A7C15ull * (j + 1)); }
+struct ChecksumArgs {
+  const uint8_t* p[PJ_MAX_COLS];
+  uint64_t n[PJ_MAX_COLS]; /* bytes */
+  unsigned long long* out; /* [PJ_MAX_COLS], zeroed */
+};
+/* blockIdx.y = column; the blocks of a column stride over its 8-byte words */
+static __global__ void __launch_bounds__(256) k_checksum(const __grid_constant__ ChecksumArgs a) {
+  const uint32_t col = blockIdx.y;
+  const uint8_t* p = a.p[col];
+  const uint64_t n = a.n[col];
+  const uint64_t nwords = (n + 7) / 8;
+  const bool aligned = (reinterpret_cast<uintptr_t>(p) & 7u) == 0;
+  unsigned long long s = 0;
+  for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < nwords; j += (uint64_t)gridDim.x * blockDim.x) {
+    uint64_t w = 0;
+    if (aligned && 8 * j + 8 <= n) w = *reinterpret_cast<const uint64_t*>(p + 8 * j);
+    else for (uint32_t b = 0; b < 8 && 8 * j + b < n; ++b) w |= (uint64_t)p[8 * j + b] << (8 * b);
+    s += checksum_term(w, j);
+  }
+  for (int d = 16; d; d >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, d);
+  if ((threadIdx.x & 31) == 0 && s) atomicAdd(&a.out[col], s);
 }
 
 }  // namespace pj

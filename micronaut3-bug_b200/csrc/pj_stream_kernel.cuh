@@ -47,6 +47,7 @@ struct StreamArgs {
   uint64_t len, limit, goff;
   uint32_t is_first, is_last;
   uint32_t tile_bytes, ntiles;
+  uint32_t opts; /* PJ_OPT_* bits that change a rule */
   unsigned long long spin_limit_ns;
   StreamTile* tiles;
   uint32_t* ticket;
@@ -224,6 +225,7 @@ __device__ __noinline__ void stream_tokenise_rest(const StreamArgs& a, const Str
       for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = cnt_d[k];
     }
     r.fast = verdict == FAST_ACCEPTED;
+    if (verdict == FAST_FAILED && opt_decides(a.opts, r.err)) { verdict = FAST_REFUSED; r.err = 0; } /* the exact parser knows the options */
   }
   if (verdict == FAST_FAILED) { /* a failure found by the word-at-a-time path: no row values, no bytes anywhere */
     r.type = PJ_TYPE_NONE;
@@ -233,7 +235,7 @@ __device__ __noinline__ void stream_tokenise_rest(const StreamArgs& a, const Str
   }
   if (verdict == FAST_REFUSED) {
     Rd rd;
-    rd.in = L.fits ? win - w0 : a.in; rd.lf_ws = 0; rd.open_end = open_end; rd.limit = a.limit;
+    rd.in = L.fits ? win - w0 : a.in; rd.lf_ws = 0; rd.open_end = open_end; rd.limit = a.limit; rd.opts = a.opts;
     PS s;
     s.p = L.gstart; s.err = 0; s.err_pos = 0;
     Out<false> so;
@@ -261,7 +263,8 @@ __device__ __forceinline__ void stream_tokenise(const StreamArgs& a, const Strea
   r.start32 = L.s;
   r.lim32 = g.vlimit - g.v0 > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)(g.vlimit - g.v0); /* window offset of the first byte that is not input */
   uint32_t fpos = 0;
-  const uint32_t verdict = lock_record<SCHEMA>(w, is_rec && L.fits, L.s, r.lim32, open_end, &r.type, r.v, r.cv, r.cnt, tp, &r.err, &fpos);
+  uint32_t verdict = lock_record<SCHEMA>(w, is_rec && L.fits, L.s, r.lim32, open_end, &r.type, r.v, r.cv, r.cnt, tp, &r.err, &fpos);
+  if (verdict == FAST_FAILED && opt_decides(a.opts, r.err)) verdict = FAST_REFUSED; /* the exact parser knows the options */
   r.fast = verdict == FAST_ACCEPTED;
   r.locked = r.fast; /* accepted in step: its tape is in model order */
   r.tape_n = tp.n;
@@ -308,7 +311,7 @@ __device__ __noinline__ void stream_emit_rest(const StreamArgs& a, const StreamG
       if (SCHEMA != PJ_SCHEMA_MIXED) store_absent<true>(c_schema, (uint32_t)SCHEMA, o, i);
     } else {
       Rd rd;
-      rd.in = L.fits ? win - w0 : a.in; rd.lf_ws = 0; rd.open_end = a.is_last ? 0u : 1u; rd.limit = a.limit;
+      rd.in = L.fits ? win - w0 : a.in; rd.lf_ws = 0; rd.open_end = a.is_last ? 0u : 1u; rd.limit = a.limit; rd.opts = a.opts;
       PS s;
       s.p = L.gstart; s.err = 0; s.err_pos = 0;
       parse_record<true>(c_schema, rd, s, (uint32_t)SCHEMA, o, i);

@@ -11,6 +11,7 @@ namespace pj {
 
 struct WOut {
   uint8_t* dst;
+  uint32_t hexa = 'A'; /* first letter of the hex digits of \u00xx escapes: 'A', or 'a' with PJ_OPT_HEX_LOWER */
   uint64_t n;
 };
 template <bool WR>
@@ -80,7 +81,7 @@ PJ_HD void wput_str(WOut& w, const uint8_t* s, uint32_t n) {
       default:
         wput<WR>(w, 'u'); wput<WR>(w, '0'); wput<WR>(w, '0');
         wput<WR>(w, '0' + (c >> 4));
-        wput<WR>(w, (c & 15) < 10 ? '0' + (c & 15) : 'A' + (c & 15) - 10);
+        wput<WR>(w, (c & 15) < 10 ? '0' + (c & 15) : w.hexa + (c & 15) - 10);
         break;
     }
   }

@@ -161,7 +161,7 @@ PJ_HD void fput_str(WOut& w, const uint8_t* s, uint32_t n) {
         default:
           wput<WR>(w, 'u'); wput<WR>(w, '0'); wput<WR>(w, '0');
           wput<WR>(w, '0' + (c >> 4));
-          wput<WR>(w, (c & 15) < 10 ? '0' + (c & 15) : 'A' + (c & 15) - 10);
+          wput<WR>(w, (c & 15) < 10 ? '0' + (c & 15) : w.hexa + (c & 15) - 10);
           break;
       }
     }

@@ -38,13 +38,16 @@ class ShardedParser:
         self._plan = None
 
     def plan(self, nbytes: int, device) -> dict:
-        """Exchanges the shard sizes (one small all-gather) and derives what every later parse of shards of
-        these sizes needs: global byte offset, how much of the next shard to fetch, whether the stream ends in
-        this shard's view. Cached while `nbytes` stays the same, so steady-state steps skip it."""
-        if self._plan is not None and self._plan["nbytes"] == nbytes:
-            return self._plan
+        """Exchanges the shard sizes (one small all-gather) and derives what the parse needs: global byte offset, how
+        much of the next shard to fetch, whether the stream ends in this shard's view. Every rank runs this on every
+        call: whether to exchange is never decided from one rank's own size, because a collective that only some ranks
+        enter hangs the others. A shard other than the last must hold at least `slack` bytes: the slack of its
+        predecessor is taken from it alone (pj_group_parse of the C ABI has no such limit)."""
         r, w = self.rank, self.world
         sizes_h = self._all_gather(torch.tensor([nbytes], dtype=torch.int64, device=device)).view(-1).tolist()
+        for k in range(1, w - 1):
+            if sizes_h[k] < self.slack:
+                raise ValueError(f"shard {k} holds {sizes_h[k]} bytes, fewer than the slack of {self.slack}: records of shard {k - 1} could run through it")
         self._plan = {"nbytes": nbytes, "sizes": sizes_h, "goff": int(sum(sizes_h[:r])),
                       "recv_n": min(self.slack, sizes_h[r + 1]) if r + 1 < w else 0,
                       "send_n": min(self.slack, nbytes) if r > 0 else 0,

@@ -54,6 +54,7 @@ typedef struct {
   int lf_ws;        /* LF counts as whitespace (array framing) */
   int open_end;     /* extent end not observed (ran out of shard slack): reaching e is TOO_LONG */
   int err; uint64_t err_pos;
+  uint32_t opts;    /* PJ_OPT_* bits that select the other answer of a rule */
 } cur;
 
 static int fail(cur* c, int kind, uint64_t pos) {
@@ -134,6 +135,20 @@ static int lex_string(cur* c, sbuf* o) {
         case 'u': {
           c->p++;
           if (!hex4(c, &cp)) return 0;
+          if (c->opts & PJ_OPT_LONE_SURROGATE_REPLACE) {
+            /* a high surrogate takes the low one that follows it at once; whatever is left alone becomes U+FFFD */
+            if (cp >= 0xD800 && cp <= 0xDBFF && c->p + 1 < c->e && c->b[c->p] == '\\' && c->b[c->p + 1] == 'u') {
+              uint64_t keep = c->p;
+              uint32_t lo;
+              c->p += 2;
+              if (!hex4(c, &lo)) return 0;
+              if (lo >= 0xDC00 && lo <= 0xDFFF) cp = 0x10000 + ((cp - 0xD800) << 10) + (lo - 0xDC00);
+              else c->p = keep; /* not its partner: read again as an escape of its own */
+            }
+            if (cp >= 0xD800 && cp <= 0xDFFF) cp = 0xFFFD;
+            put_utf8(o, cp);
+            continue;
+          }
           if (cp >= 0xDC00 && cp <= 0xDFFF) return fail(c, PJ_E_BAD_SURROGATE, bs);
           if (cp >= 0xD800 && cp <= 0xDBFF) {
             if (c->p >= c->e) return fail_end(c);
@@ -277,6 +292,28 @@ static int read_int(cur* c, int bits, int64_t* out) {
   if (c->p >= c->e) return fail_end(c);
   if (at_null(c)) return lex_literal(c, "null") ? 2 : 0;
   uint8_t x = c->b[c->p];
+  if (x == '"' && (c->opts & PJ_OPT_COERCE_SCALARS)) {
+    /* a string that holds an integer: -?(0|[1-9][0-9]*), nothing else */
+    uint64_t q = c->p;
+    sbuf t; memset(&t, 0, sizeof t);
+    if (!lex_string(c, &t)) { sb_free(&t); return 0; }
+    size_t i = 0, n = t.n;
+    int neg = n && t.b[0] == '-';
+    if (neg) i = 1;
+    int ok = i < n && !(t.b[i] == '0' && i + 1 < n);
+    uint64_t mag = 0; int over = 0;
+    for (; ok && i < n; ++i) {
+      if (t.b[i] < '0' || t.b[i] > '9') { ok = 0; break; }
+      uint64_t d = (uint64_t)(t.b[i] - '0');
+      if (mag > (0xFFFFFFFFFFFFFFFFull - d) / 10) over = 1; else mag = mag * 10 + d;
+    }
+    sb_free(&t);
+    if (!ok) return fail(c, PJ_E_TYPE, q);
+    uint64_t lim = bits == 64 ? (neg ? 0x8000000000000000ull : 0x7FFFFFFFFFFFFFFFull) : (neg ? 0x80000000ull : 0x7FFFFFFFull);
+    if (over || mag > lim) return fail(c, PJ_E_NUM_RANGE, q);
+    *out = neg ? (int64_t)(0 - mag) : (int64_t)mag;
+    return 1;
+  }
   if (!(x == '-' || (x >= '0' && x <= '9'))) return fail_first_byte(c);
   num r;
   if (!lex_number(c, &r)) return 0;
@@ -293,13 +330,36 @@ static int read_bool(cur* c, uint8_t* out) {
   if (at_null(c)) return lex_literal(c, "null") ? 2 : 0;
   if (c->b[c->p] == 't') { *out = 1; return lex_literal(c, "true"); }
   if (c->b[c->p] == 'f') { *out = 0; return lex_literal(c, "false"); }
+  if (c->b[c->p] == '"' && (c->opts & PJ_OPT_COERCE_SCALARS)) {
+    uint64_t q = c->p;
+    sbuf t; memset(&t, 0, sizeof t);
+    if (!lex_string(c, &t)) { sb_free(&t); return 0; }
+    int v = sb_eq(&t, "true") ? 1 : (sb_eq(&t, "false") ? 0 : -1);
+    sb_free(&t);
+    if (v < 0) return fail(c, PJ_E_TYPE, q);
+    *out = (uint8_t)v;
+    return 1;
+  }
   return fail_first_byte(c);
 }
 static int read_str(cur* c, sbuf* o, uint64_t* quote_pos) {
   skip_ws(c);
   if (c->p >= c->e) return fail_end(c);
   if (at_null(c)) return lex_literal(c, "null") ? 2 : 0;
-  if (c->b[c->p] != '"') return fail_first_byte(c);
+  if (c->b[c->p] != '"') {
+    /* a plain string property (the callers that ask for no quote position; enums and date-times do ask) also takes a
+       number, true or false under PJ_OPT_COERCE_SCALARS: the token's text, as written, becomes the string */
+    uint8_t x = c->b[c->p];
+    if (!quote_pos && (c->opts & PJ_OPT_COERCE_SCALARS) && (x == '-' || (x >= '0' && x <= '9') || x == 't' || x == 'f')) {
+      uint64_t t0 = c->p;
+      if (x == 't') { if (!lex_literal(c, "true")) return 0; }
+      else if (x == 'f') { if (!lex_literal(c, "false")) return 0; }
+      else { num r; if (!lex_number(c, &r)) return 0; }
+      if (o) { o->n = 0; for (uint64_t q = t0; q < c->p; ++q) sb_put(o, c->b[q]); }
+      return 1;
+    }
+    return fail_first_byte(c);
+  }
   if (quote_pos) *quote_pos = c->p;
   return lex_string(c, o);
 }
@@ -523,7 +583,11 @@ static int pet_field(cur* c, scratch* w, int field) {
       r = read_str(c, &w->tmp, &q); if (!r) return 0;
       if (r == 2) { v->present &= ~32u; v->status = 255; return 1; }
       int k = enum_index(&w->tmp, PET_STATUS, 3);
-      if (k < 0) return fail(c, PJ_E_ENUM, q);
+      if (k < 0) {
+        if (!(c->opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL)) return fail(c, PJ_E_ENUM, q);
+        v->present &= ~32u; v->status = 255; /* unknown literal: the property stays absent */
+        return 1;
+      }
       v->present |= 32; v->status = k;
       return 1;
     }
@@ -562,7 +626,11 @@ static int ord_field(cur* c, scratch* w, int field) {
       r = read_str(c, &w->tmp, &q); if (!r) return 0;
       if (r == 2) { v->present &= ~bit; v->status = 255; return 1; }
       int k = enum_index(&w->tmp, ORD_STATUS, 3);
-      if (k < 0) return fail(c, PJ_E_ENUM, q);
+      if (k < 0) {
+        if (!(c->opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL)) return fail(c, PJ_E_ENUM, q);
+        v->present &= ~bit; v->status = 255;
+        return 1;
+      }
       v->present |= bit; v->status = k;
       return 1;
     }
@@ -616,8 +684,14 @@ static int parse_record(cur* c, scratch* w, uint32_t schema) {
           else { w->usr.id = early_id; w->usr.present |= 1; }
         }
         if (have_status) {
-          if (type == PJ_TYPE_PET) { if (status_pet < 0) { fail(c, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; } w->pet.status = status_pet; w->pet.present |= 32; }
-          else if (type == PJ_TYPE_ORDER) { if (status_ord < 0) { fail(c, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; } w->ord.status = status_ord; w->ord.present |= 16; }
+          const int lenient = (c->opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL) != 0;
+          if (type == PJ_TYPE_PET) {
+            if (status_pet >= 0) { w->pet.status = status_pet; w->pet.present |= 32; }
+            else if (!lenient) { fail(c, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; }
+          } else if (type == PJ_TYPE_ORDER) {
+            if (status_ord >= 0) { w->ord.status = status_ord; w->ord.present |= 16; }
+            else if (!lenient) { fail(c, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; }
+          }
           /* User has no `status`: the early value was an unknown key, already validated as a string */
         }
       } else if (owners == 3) { /* id */
@@ -632,7 +706,7 @@ static int parse_record(cur* c, scratch* w, uint32_t schema) {
         if (have_status) {
           status_pet = enum_index(&w->tmp, PET_STATUS, 3);
           status_ord = enum_index(&w->tmp, ORD_STATUS, 3);
-          if (status_pet < 0 && status_ord < 0) { fail(c, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; }
+          if (status_pet < 0 && status_ord < 0 && !(c->opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL)) { fail(c, PJ_E_ENUM, status_q); return PJ_TYPE_NONE; }
         }
         continue;
       } else {
@@ -803,8 +877,15 @@ static void extents_array(const uint8_t* in, uint64_t len, extlist* out, uint32_
 /* ------------------------------------------------------------------------------------------ */
 /* public checker entry points                                                                 */
 /* ------------------------------------------------------------------------------------------ */
+int pjo_parse_opt(uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack,
+                  int is_first, int is_last, uint64_t global_offset, uint32_t opts, pj_columns* out);
 int pjo_parse(uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack,
               int is_first, int is_last, uint64_t global_offset, pj_columns* out) {
+  return pjo_parse_opt(schema, framing, in, len, slack, is_first, is_last, global_offset, 0, out);
+}
+/* the same with pj_options.flags (the PJ_OPT_* bits that select the other answer of a rule) */
+int pjo_parse_opt(uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack,
+                  int is_first, int is_last, uint64_t global_offset, uint32_t opts, pj_columns* out) {
   if (!out || (!in && len + slack) || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED) return PJ_ERR_ARG;
   extlist xl; memset(&xl, 0, sizeof xl);
   uint32_t doc_kind = 0; uint64_t doc_off = 0;
@@ -820,7 +901,7 @@ int pjo_parse(uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len
   uint64_t rows[4] = {0, 0, 0, 0}, n_err = 0;
   for (size_t i = 0; i < xl.n; ++i) {
     cur c; memset(&c, 0, sizeof c);
-    c.b = in; c.s = c.p = xl.x[i].s; c.e = xl.x[i].e; c.lf_ws = framing == PJ_FRAMING_ARRAY; c.open_end = xl.x[i].open_end;
+    c.b = in; c.s = c.p = xl.x[i].s; c.e = xl.x[i].e; c.lf_ws = framing == PJ_FRAMING_ARRAY; c.open_end = xl.x[i].open_end; c.opts = opts;
     int type;
     if (xl.x[i].blank_err) { fail(&c, PJ_E_SYNTAX, c.e); type = PJ_TYPE_NONE; }
     else type = parse_record(&c, &sc, schema);
@@ -882,7 +963,7 @@ int pjo_extents(uint32_t framing, const uint8_t* in, uint64_t len, uint64_t* s, 
 /* ------------------------------------------------------------------------------------------ */
 /* writer (W1-W5)                                                                              */
 /* ------------------------------------------------------------------------------------------ */
-typedef struct { uint8_t* p; uint64_t cap, n; int incl; } wout;
+typedef struct { uint8_t* p; uint64_t cap, n; int incl; int hex_lower; } wout;
 static void o_put(wout* o, uint8_t c) { if (o->n < o->cap) o->p[o->n] = c; o->n++; }
 static void o_lit(wout* o, const char* s) { while (*s) o_put(o, (uint8_t)*s++); }
 static void o_i64(wout* o, int64_t v) {
@@ -893,7 +974,7 @@ static void o_i64(wout* o, int64_t v) {
   while (n) o_put(o, (uint8_t)b[--n]);
 }
 static void o_str(wout* o, const uint8_t* s, size_t n) {
-  static const char HEX[] = "0123456789ABCDEF";
+  const char* HEX = o->hex_lower ? "0123456789abcdef" : "0123456789ABCDEF";
   o_put(o, '"');
   for (size_t i = 0; i < n; ++i) {
     uint8_t c = s[i];
@@ -1042,10 +1123,16 @@ static void write_user(wout* o, const pj_columns* cols, uint64_t r) {
   o_put(o, '}');
 }
 
+int pjo_write_opt(uint32_t schema, uint32_t framing, int inclusion, uint32_t opts, const pj_columns* cols, uint8_t* out,
+                  uint64_t cap, uint64_t* out_len);
 int pjo_write(uint32_t schema, uint32_t framing, int inclusion, const pj_columns* cols, uint8_t* out,
               uint64_t cap, uint64_t* out_len) {
+  return pjo_write_opt(schema, framing, inclusion, 0, cols, out, cap, out_len);
+}
+int pjo_write_opt(uint32_t schema, uint32_t framing, int inclusion, uint32_t opts, const pj_columns* cols, uint8_t* out,
+                  uint64_t cap, uint64_t* out_len) {
   if (!cols || !out_len || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED) return PJ_ERR_ARG;
-  wout o; o.p = out; o.cap = out ? cap : 0; o.n = 0; o.incl = inclusion;
+  wout o; o.p = out; o.cap = out ? cap : 0; o.n = 0; o.incl = inclusion; o.hex_lower = (opts & PJ_OPT_HEX_LOWER) != 0;
   int arr = framing == PJ_FRAMING_ARRAY;
   uint64_t n = schema == PJ_SCHEMA_MIXED ? cols->n_records : cols->n_rows[schema];
   uint64_t written = 0;
@@ -1067,4 +1154,22 @@ int pjo_write(uint32_t schema, uint32_t framing, int inclusion, const pj_columns
   if (arr) o_put(&o, ']');
   *out_len = o.n;
   return o.n > cap ? PJ_ERR_CAPACITY : PJ_OK;
+}
+
+/* ---- column checksums: the definition in include/petjson.h (pj_columns_checksum), for host columns ---------- */
+static uint64_t cs_mix(uint64_t x) {
+  x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+  x ^= x >> 27; x *= 0x94D049BB133111EBull;
+  x ^= x >> 31;
+  return x;
+}
+/* sum over the 8-byte words of p[0..n) */
+uint64_t pjo_checksum_bytes(const uint8_t* p, uint64_t n) {
+  uint64_t s = 0;
+  for (uint64_t j = 0; 8 * j < n; ++j) {
+    uint64_t w = 0;
+    for (uint32_t b = 0; b < 8 && 8 * j + b < n; ++b) w |= (uint64_t)p[8 * j + b] << (8 * b);
+    s += cs_mix(w + 0x9E3779B97F4A7C15ull * (j + 1));
+  }
+  return s;
 }

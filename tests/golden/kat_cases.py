@@ -275,3 +275,50 @@ s = b''; case("array: empty input", "pet", s, [{"doc": ("EOF", 0)}], A)
 # commas at depth 1 separate even without an opening bracket, so the tail of the object is an extent
 s = b'{' + MIN + b'}'; case("array: not an array", "pet", s, [("TYPE", 0), {"doc": ("SYNTAX", 0)}], A)
 case("array: mixed models", "mixed", b'[{"petId":1},{' + MIN + b'},{"username":"abcdef"}]', [{"petId": 1}, MIN_D, {"username": "abcdef"}], A)
+
+
+# ---- the other answers of the rules that rest on unobserved behaviour (pj_options.flags) ---------------------
+# OPTION_CASES = (name, schema, option bits, input bytes, expected); the same inputs under the default rules are
+# covered above (they fail with PJ_E_ENUM / PJ_E_BAD_SURROGATE / PJ_E_TYPE).
+ENUM_NULL, LONE_REPLACE, COERCE, HEX_LOWER = 1, 2, 4, 8
+OPTION_CASES = []
+
+
+def ocase(name, schema, opts, data, expected):
+    OPTION_CASES.append((name, schema, opts, data, expected))
+
+
+ocase("enum: unknown literal leaves the property absent", "pet", ENUM_NULL, b'{' + MIN + b',"status":"gone"}\n', [MIN_D])
+ocase("enum: known literal still read", "pet", ENUM_NULL, b'{' + MIN + b',"status":"sold"}\n', [dict(MIN_D, status="sold")])
+ocase("enum: repeated key, the unknown one last", "pet", ENUM_NULL, b'{' + MIN + b',"status":"sold","status":"Sold"}\n', [MIN_D])
+ocase("enum: order", "order", ENUM_NULL, b'{"status":"x","quantity":1}\n{"status":"placed"}\n', [{"quantity": 1}, {"status": "placed"}])
+ocase("enum: mixed stream, status before the deciding key", "mixed", ENUM_NULL,
+      b'{"id":1,"status":"zzz","petId":2}\n{"status":"sold","petId":2}\n{"status":"sold","name":"a","photoUrls":[]}\n',
+      [{"id": 1, "petId": 2}, {"petId": 2}, dict(MIN_D, status="sold")])
+ocase("enum: other failures stay failures", "pet", ENUM_NULL, b'{' + MIN + b',"status":5}\n{"status":"gone"}\n',
+      [("TYPE", at(b'{' + MIN + b',"status":5}', b'5')), ("REQUIRED", len(b'{"status":"gone"') )])
+
+ocase("surrogate: lone high and lone low become U+FFFD", "pet", LONE_REPLACE,
+      b'{"name":"\\ud800","photoUrls":["\\udc00x","\\ud83d\\u0041","\\ud83d\\ud83d\\ude00","a\\udfffb"]}\n',
+      [{"name": "�", "photoUrls": ["�x", "�A", "�\U0001F600", "a�b"]}])
+ocase("surrogate: pairs still pair", "pet", LONE_REPLACE, b'{"name":"\\ud83d\\ude00","photoUrls":[]}\n', [{"name": "\U0001F600", "photoUrls": []}])
+ocase("surrogate: a bad escape after a lone high is still a bad escape", "pet", LONE_REPLACE, b'{"name":"\\ud800\\u12","photoUrls":[]}\n',
+      [("BAD_ESCAPE", at(b'{"name":"\\ud800\\u12"', b'"', 3))])
+
+ocase("coerce: integers from strings, strings from numbers and booleans", "pet", COERCE,
+      b'{"id":"12","category":{"id":"-3","name":true},"name":5,"photoUrls":[]}\n{"name":-1.5e3,"photoUrls":[],"tags":[{"id":"0","name":0}]}\n',
+      [{"id": 12, "category": {"id": -3, "name": "true"}, "name": "5", "photoUrls": []},
+       {"name": "-1.5e3", "photoUrls": [], "tags": [{"id": 0, "name": "0"}]}])
+ocase("coerce: a string that is no integer", "pet", COERCE, b'{"id":"1.0",' + MIN + b'}\n{"id":"",' + MIN + b'}\n{"id":"01",' + MIN + b'}\n{"id":" 1",' + MIN + b'}\n',
+      [("TYPE", 6), ("TYPE", 6), ("TYPE", 6), ("TYPE", 6)])
+ocase("coerce: range of the integer in the string", "pet", COERCE,
+      b'{"id":"9223372036854775807",' + MIN + b'}\n{"id":"9223372036854775808",' + MIN + b'}\n{"id":"-9223372036854775808",' + MIN + b'}\n',
+      [dict(MIN_D, id=9223372036854775807), ("NUM_RANGE", 6), dict(MIN_D, id=-9223372036854775808)])
+ocase("coerce: order", "order", COERCE, b'{"complete":"true","quantity":"7","petId":"8"}\n{"complete":"yes"}\n{"quantity":"2147483648"}\n',
+      [{"petId": 8, "quantity": 7, "complete": True}, ("TYPE", 12), ("NUM_RANGE", 12)])
+ocase("coerce: user", "user", COERCE, b'{"phone":5551234,"userStatus":"2","email":false}\n', [{"email": "false", "phone": "5551234", "userStatus": 2}])
+ocase("coerce: mixed stream, id before the deciding key", "mixed", COERCE, b'{"id":"7","username":1}\n', [{"id": 7, "username": "1"}])
+ocase("coerce: list elements, enums and date-times are not coerced", "pet", COERCE,
+      b'{"name":"a","photoUrls":[1]}\n{' + MIN + b',"status":1}\n{"name":[],"photoUrls":[]}\n',
+      [("TYPE", at(b'{"name":"a","photoUrls":[1', b'1')), ("TYPE", at(b'{' + MIN + b',"status":1', b'1')), ("TYPE", at(b'{"name":[', b'['))])
+ocase("coerce: a malformed number is still a syntax failure", "pet", COERCE, b'{"name":01,"photoUrls":[]}\n', [("SYNTAX", at(b'{"name":01', b'1'))])

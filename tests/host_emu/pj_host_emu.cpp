@@ -18,6 +18,10 @@
 
 using namespace pj;
 
+/* PJ_OPT_* bits for the exact parser (tests set them before a call) */
+static uint32_t g_opts = 0;
+extern "C" void emu_set_options(uint32_t opts) { g_opts = opts; }
+
 
 extern "C" int emu_parse(uint32_t schema, uint32_t framing, const uint8_t* in, uint64_t len, uint64_t slack,
                          int is_first, int is_last, uint64_t goff, pj_columns* out,
@@ -41,7 +45,7 @@ extern "C" int emu_parse(uint32_t schema, uint32_t framing, const uint8_t* in, u
   uint64_t* rs = (uint64_t*)out->col[PJ_COL_REC_START].ptr;
   uint64_t nerr = 0;
   for (uint64_t i = 0; i < N; ++i) {
-    Rd r; r.in = in; r.lf_ws = framing == PJ_FRAMING_ARRAY; r.limit = r.lf_ws ? ends[i] : limit; r.open_end = r.lf_ws ? 0 : !is_last;
+    Rd r; r.in = in; r.lf_ws = framing == PJ_FRAMING_ARRAY; r.limit = r.lf_ws ? ends[i] : limit; r.open_end = r.lf_ws ? 0 : !is_last; r.opts = g_opts;
     PS s; s.p = starts[i]; s.err = 0; s.err_pos = 0;
     Out<false> o; o.cols = &dc;
     uint32_t t;
@@ -65,7 +69,7 @@ extern "C" int emu_parse(uint32_t schema, uint32_t framing, const uint8_t* in, u
     for (uint32_t k = 0; k < NSLOT; ++k) { o.base[k] = cnt[(size_t)k * (N + 1) + i]; o.room[k] = cnt[(size_t)k * (N + 1) + i + 1] - o.base[k]; }
     if (schema == PJ_SCHEMA_MIXED) ((uint32_t*)out->col[PJ_COL_REC_ROW].ptr)[i] = ek[i] ? 0xFFFFFFFFu : o.base[types[i] - 1];
     if (ek[i]) { if (schema != PJ_SCHEMA_MIXED) store_absent<true>(S, schema, o, i); continue; }
-    Rd r; r.in = in; r.lf_ws = framing == PJ_FRAMING_ARRAY; r.limit = r.lf_ws ? ends[i] : limit; r.open_end = r.lf_ws ? 0 : !is_last;
+    Rd r; r.in = in; r.lf_ws = framing == PJ_FRAMING_ARRAY; r.limit = r.lf_ws ? ends[i] : limit; r.open_end = r.lf_ws ? 0 : !is_last; r.opts = g_opts;
     PS s; s.p = starts[i]; s.err = 0; s.err_pos = 0;
     uint32_t t = parse_record<true>(S, r, s, schema, o, i);
     if (s.err || t != types[i]) { fprintf(stderr, "emit pass disagrees at record %llu\n", (unsigned long long)i); return -1; }
@@ -238,17 +242,19 @@ static int emu_fast_t(uint32_t framing, const uint8_t* in, uint64_t len, uint64_
         if (verdict == FAST_ACCEPTED) { g_lock_accepted++; islock[t] = 1; }
         if (verdict == FAST_FAILED) g_lock_failed++;
       }
+      if (verdict == FAST_FAILED && (((g_opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL) && fk == PJ_E_ENUM) || ((g_opts & PJ_OPT_COERCE_SCALARS) && fk == PJ_E_TYPE))) verdict = FAST_REFUSED;
       if (verdict != FAST_REFUSED) {}
       else if ((fits || direct) && !blank[i]) {
         if (!direct) verdict = fast_record<SCHEMA>(wr, st32, lim32, lf_ws, lf_ws ? 0 : !is_last, &type, V[t], CV[t], c, tp, &fk, &fp);
         else { verdict = fast_outline<SCHEMA>(wr, st32, lim32, lf_ws, lf_ws ? 0 : !is_last, nullptr, nullptr, i, tp, c, &type, &fk, &fp); tp.n = tp.cap + 1; }
       }
+      if (verdict == FAST_FAILED && (((g_opts & PJ_OPT_ENUM_UNKNOWN_AS_NULL) && fk == PJ_E_ENUM) || ((g_opts & PJ_OPT_COERCE_SCALARS) && fk == PJ_E_TYPE))) verdict = FAST_REFUSED;
       bool ok = verdict == FAST_ACCEPTED;
       PS s; s.p = starts[i]; s.err = 0; s.err_pos = 0;
       if (verdict == FAST_FAILED) { nfail_fast++; s.err = fk; s.err_pos = starts[i] + (fp - st32); type = 0; for (uint32_t k = 0; k < NSLOT; ++k) cnt[(size_t)t * NSLOT + k] = 0; }
       else if (ok) { nfast++; for (uint32_t k = 0; k < NSLOT; ++k) cnt[(size_t)t * NSLOT + k] = c[k]; ntape[t] = tp.n; }
       else {
-        Rd r; r.in = fits ? winbuf.data() - w0 : in; r.lf_ws = lf_ws; r.limit = lim; r.open_end = lf_ws ? 0 : !is_last;
+        Rd r; r.in = fits ? winbuf.data() - w0 : in; r.lf_ws = lf_ws; r.limit = lim; r.open_end = lf_ws ? 0 : !is_last; r.opts = g_opts;
         Out<false> o; o.cols = &dc;
         if (blank[i]) { fail(s, PJ_E_SYNTAX, ends[i]); type = 0; }
         else type = parse_record<false>(S, r, s, schema, o, i);
@@ -273,7 +279,7 @@ static int emu_fast_t(uint32_t framing, const uint8_t* in, uint64_t len, uint64_
         else { uint32_t a_, b_, c_; fast_outline<SCHEMA>(wins[t], st32v[t], lim32v[t], lf_ws, lf_ws ? 0 : !is_last, &dc, o.base, i, tp, nullptr, &a_, &b_, &c_); }
       } else {
         uint64_t lim = lf_ws ? ends[i] : limit;
-        Rd r; r.in = fits ? winbuf.data() - w0 : in; r.lf_ws = lf_ws; r.limit = lim; r.open_end = lf_ws ? 0 : !is_last;
+        Rd r; r.in = fits ? winbuf.data() - w0 : in; r.lf_ws = lf_ws; r.limit = lim; r.open_end = lf_ws ? 0 : !is_last; r.opts = g_opts;
         PS s; s.p = starts[i]; s.err = 0; s.err_pos = 0;
         uint32_t ty = parse_record<true>(S, r, s, schema, o, i);
         if (s.err || ty != types[t]) { fprintf(stderr, "emit pass disagrees at record %llu\n", (unsigned long long)i); return -1; }

@@ -38,24 +38,34 @@ class Oracle:
         path = build.build_oracle()
         self.lib = C.CDLL(path)
 
-    def parse(self, schema, buf, framing=0, slack=0, is_first=1, is_last=1, goff=0) -> "abi.HostColumns":
+    def parse(self, schema, buf, framing=0, slack=0, is_first=1, is_last=1, goff=0, opts=0) -> "abi.HostColumns":
         buf = np.ascontiguousarray(buf, dtype=np.uint8)
         hc = abi.HostColumns(schema, abi.default_caps(schema, nrec_bound(buf), buf.size))
-        st = self.lib.pjo_parse(u32(schema), u32(framing), C.c_void_p(buf.ctypes.data), u64(buf.size - slack), u64(slack),
-                                int(is_first), int(is_last), u64(goff), C.byref(hc.raw))
+        st = self.lib.pjo_parse_opt(u32(schema), u32(framing), C.c_void_p(buf.ctypes.data), u64(buf.size - slack), u64(slack),
+                                    int(is_first), int(is_last), u64(goff), u32(opts), C.byref(hc.raw))
         assert st == 0, st
         return hc
 
-    def write(self, schema, cols, framing=0, inclusion=0, cap=None) -> np.ndarray:
+    def write(self, schema, cols, framing=0, inclusion=0, cap=None, opts=0) -> np.ndarray:
         if cap is None:
             ln = u64()
-            self.lib.pjo_write(u32(schema), u32(framing), int(inclusion), C.byref(cols.raw), None, u64(0), C.byref(ln))
+            self.lib.pjo_write_opt(u32(schema), u32(framing), int(inclusion), u32(opts), C.byref(cols.raw), None, u64(0), C.byref(ln))
             cap = ln.value
         out = np.zeros(max(cap, 1), np.uint8)
         ln = u64()
-        st = self.lib.pjo_write(u32(schema), u32(framing), int(inclusion), C.byref(cols.raw), C.c_void_p(out.ctypes.data), u64(cap), C.byref(ln))
+        st = self.lib.pjo_write_opt(u32(schema), u32(framing), int(inclusion), u32(opts), C.byref(cols.raw), C.c_void_p(out.ctypes.data), u64(cap), C.byref(ln))
         assert st == 0, st
         return out[: ln.value]
+
+    def checksums(self, cols) -> dict:
+        """{column name: 64-bit checksum} of a host column set, by the definition of pj_columns_checksum."""
+        self.lib.pjo_checksum_bytes.restype = C.c_uint64
+        self.lib.pjo_checksum_bytes.argtypes = [C.c_void_p, C.c_uint64]
+        out = {}
+        for c in abi.schema_columns(cols.schema):
+            a = cols.get(c.id)
+            out[c.name] = int(self.lib.pjo_checksum_bytes(a.ctypes.data, a.nbytes)) if a.size else 0
+        return out
 
     def index(self, buf, framing=0) -> np.ndarray:
         buf = np.ascontiguousarray(buf, dtype=np.uint8)

@@ -4,7 +4,7 @@ import random
 import numpy as np
 import pytest
 
-from golden.kat_cases import CASES
+from golden.kat_cases import CASES, HEX_LOWER, OPTION_CASES
 from pj_testlib import SCHEMA_BY_NAME, abi, as_u8, nrec_bound, pj, same_result
 from test_oracle_crosscheck import mutate
 from test_oracle_kat import check_case
@@ -435,3 +435,66 @@ def test_tile_size_follows_the_records(native, oracle):
             for _ in range(2):
                 assert same_result(want, gpu_parse_device(c, schema, text)) == ""
                 assert c.stats().tiles >= 1
+
+
+def test_a_bounded_wait_that_runs_out(native, oracle):
+    """Tile 0 of the first call is never handed out (test hook), so the other tiles' waits for it run out after 2 ms:
+    the call answers PJ_ERR_TIMEOUT instead of hanging, nothing faults, and the same context parses correctly
+    afterwards."""
+    import time
+
+    text = pj.gen_text(1, 8, 0, 50000, 0)
+    want = oracle.parse(1, text)
+    with native.Context(device=0, flags=abi.PJ_OPT_TEST_STALL_ONCE, spin_limit_us=2000) as c:
+        t0 = time.perf_counter()
+        with pytest.raises(native.PetJsonError) as e:
+            gpu_parse_device(c, 1, text)
+        assert e.value.status == abi.PJ_ERR_TIMEOUT
+        assert time.perf_counter() - t0 < 5.0
+        assert same_result(want, gpu_parse_device(c, 1, text)) == ""
+        assert same_result(want, gpu_parse_host(c, 1, text)) == ""
+
+
+# ---- the option switches (pj_options.flags) --------------------------------------------------------------
+@pytest.mark.parametrize("case", OPTION_CASES, ids=[c[0] for c in OPTION_CASES])
+def test_option_known_answers_on_gpu(native, case):
+    name, schema, opts, data, expected = case
+    with native.Context(device=0, flags=opts) as c:
+        check_case(lambda sch, buf, fr: gpu_parse_host(c, sch, buf, fr), name, schema, "ndjson", data, expected)
+        check_case(lambda sch, buf, fr: gpu_parse_device(c, sch, buf, fr), name, schema, "ndjson", data, expected)
+
+
+@pytest.mark.parametrize("opts", [1, 2, 4, 7])
+def test_option_switches_on_corpora(native, oracle, opts):
+    """Corpora in which the switches matter (quoted numbers, bare words, unknown literals, lone surrogates) with every
+    switch and all of them together, NDJSON and array framing."""
+    import re
+
+    rng = random.Random(opts)
+    with native.Context(device=0, flags=opts) as c:
+        for schema in (1, 2, 3, 4):
+            lines = bytes(pj.gen_text(schema, 500 + opts, 0, 3000, abi.PJ_GEN_ESCAPES | abi.PJ_GEN_MALFORMED)).split(b"\n")[:-1]
+            out = []
+            for ln in lines:
+                r = rng.random()
+                if r < 0.4:
+                    ln = rng.choice([re.sub(rb':(\d+)', rb':"\1"', ln, count=1), re.sub(rb':"([A-Za-z]{1,6})"', rb':\1', ln, count=1),
+                                     ln.replace(b'"status":"', b'"status":"x', 1), re.sub(rb'":"', rb'":"\\ud83d', ln, count=1),
+                                     re.sub(rb':"([a-z]+)"', rb':12.5', ln, count=1), ln.replace(b"true", b'"true"').replace(b"false", b'"false"')])
+                out.append(ln)
+            body = as_u8(b"\n".join(out) + b"\n")
+            want = oracle.parse(schema, body, opts=opts)
+            assert same_result(want, gpu_parse_device(c, schema, body)) == "", schema
+            arr = as_u8(b"[" + b",".join(out) + b"]")
+            assert same_result(oracle.parse(schema, arr, ARRAY, opts=opts), gpu_parse_device(c, schema, arr, ARRAY)) == "", schema
+
+
+def test_writer_hex_case(native, oracle):
+    cols = oracle.parse(1, as_u8(b'{"name":"a\\u001fb\\u000b\\n\\u0000","photoUrls":["\\u001e"]}\n'))
+    for opts in (0, HEX_LOWER):
+        want = oracle.write(1, cols, opts=opts)
+        with native.Context(device=0, flags=opts) as c:
+            out = np.zeros(want.size + 8, np.uint8)
+            n = c.write(1, cols, out)
+            assert n == want.size and np.array_equal(out[:n], want)
+    assert b"\\u001F" in bytes(oracle.write(1, cols)) and b"\\u001f" in bytes(oracle.write(1, cols, opts=HEX_LOWER))

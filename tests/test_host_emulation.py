@@ -6,6 +6,7 @@ another; what is compared is bit-exact: every column, error kind and offset, and
 import ctypes as C
 import os
 import random
+import re
 import subprocess
 
 import numpy as np
@@ -47,10 +48,11 @@ def extents(oracle, buf):
     return s[:n.value], e[:n.value], b[:n.value]
 
 
-def emu_parse_tiles(emu, oracle, schema, buf, framing=NDJSON, tile=128, win=45056, tape=20, lock=False):
+def emu_parse_tiles(emu, oracle, schema, buf, framing=NDJSON, tile=128, win=45056, tape=20, lock=False, opts=0):
     """The tile kernel's per-record work on the host: windows of `win` bytes, tapes of `tape` words, `tile` records a tile.
     lock: the lockstep tokeniser (pj_lock.cuh) gets the first try at every staged NDJSON record, as in the stream kernel."""
     emu.emu_use_lock(1 if lock else 0)
+    emu.emu_set_options(u32(opts))
     buf = as_u8(buf)
     hc = garbage_columns(schema, nrec_bound(buf), buf.size)
     if framing == ARRAY:
@@ -278,3 +280,41 @@ def test_lockstep_tokeniser_edges(emu, oracle):
         body = as_u8(b"\n".join(recs) + b"\n")
         got, _ = emu_parse_tiles(emu, oracle, schema, body, lock=True)
         assert same_result(oracle.parse(schema, body), got) == "", schema
+
+
+# ---- the option switches (pj_options.flags) in the device-side parsers ---------------------------------------
+def test_option_switches_known_answers(emu, oracle):
+    from golden.kat_cases import OPTION_CASES
+    from pj_testlib import SCHEMA_BY_NAME, records
+
+    for name, schema, opts, data, expected in OPTION_CASES:
+        sch = SCHEMA_BY_NAME[schema]
+        for lock in (False, True):
+            got, _ = emu_parse_tiles(emu, oracle, sch, as_u8(data), lock=lock, opts=opts)
+            assert records(got.as_dict(), sch) == expected, (name, lock)
+    emu.emu_set_options(u32(0))
+
+
+@pytest.mark.parametrize("opts", [1, 2, 4, 7])
+def test_option_switches_on_mutated_text(emu, oracle, opts):
+    """Every combination of the three parse switches against the checker with the same switches."""
+    rng = random.Random(opts)
+    for it in range(25):
+        schema = rng.choice([1, 2, 3, 4])
+        lines = bytes(pj.gen_text(schema, rng.randrange(1 << 30), 0, 40, rng.choice([0, G.PJ_GEN_ESCAPES, G.PJ_GEN_MALFORMED | G.PJ_GEN_SPARSE]))).split(b"\n")[:-1]
+        out = []
+        for ln in lines:
+            r = rng.random()
+            if r < 0.25:
+                ln = mutate(rng, ln)
+            elif r < 0.45:  # quote a number, unquote a short string, break an enum, plant a lone surrogate
+                ln = rng.choice([re.sub(rb':(\d+)', rb':"\1"', ln, count=1), re.sub(rb':"([A-Za-z]{1,6})"', rb':\1', ln, count=1),
+                                 ln.replace(b'"status":"', b'"status":"x', 1), re.sub(rb'":"', rb'":"\\ud83d', ln, count=1),
+                                 re.sub(rb':"([a-z]+)"', rb':12.5', ln, count=1), ln.replace(b"true", b'"true"').replace(b"false", b'"false"')])
+            out.append(ln)
+        body = as_u8(b"\n".join(out) + b"\n")
+        want = oracle.parse(schema, body, opts=opts)
+        for lock in (False, True):
+            got, _ = emu_parse_tiles(emu, oracle, schema, body, lock=lock, opts=opts)
+            assert same_result(want, got) == "", (opts, it, schema, lock)
+    emu.emu_set_options(u32(0))

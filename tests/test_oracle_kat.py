@@ -8,7 +8,7 @@ import os
 import numpy as np
 import pytest
 
-from golden.kat_cases import CASES
+from golden.kat_cases import CASES, HEX_LOWER, OPTION_CASES
 from pj_testlib import KIND_BY_NAME, SCHEMA_BY_NAME, abi, as_u8, records
 
 
@@ -43,6 +43,21 @@ def check_case(parse, name, schema, framing, data, expected):
 @pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
 def test_kat(oracle, case):
     check_case(lambda sch, buf, fr: oracle.parse(sch, buf, fr), *case)
+
+
+@pytest.mark.parametrize("case", OPTION_CASES, ids=[c[0] for c in OPTION_CASES])
+def test_option_kat(oracle, case):
+    """The other answer of a rule (pj_options.flags), and the default answer for the same input: a failure."""
+    name, schema, opts, data, expected = case
+    check_case(lambda sch, buf, fr: oracle.parse(sch, buf, fr, opts=opts), name, schema, "ndjson", data, expected)
+    default = oracle.parse(SCHEMA_BY_NAME[schema], as_u8(data))
+    assert default.n_errors >= sum(1 for e in expected if isinstance(e, tuple)), name
+
+
+def test_hex_case_of_the_writer(oracle):
+    cols = oracle.parse(1, as_u8(b'{"name":"a\\u001fb\\u000b\\n","photoUrls":[]}\n'))
+    assert bytes(oracle.write(1, cols)) == b'{"name":"a\\u001Fb\\u000B\\n"}\n'
+    assert bytes(oracle.write(1, cols, opts=HEX_LOWER)) == b'{"name":"a\\u001fb\\u000b\\n"}\n'
 
 
 def test_case_names_unique():

@@ -40,8 +40,19 @@ def _rank_main(rank, world, port, tmp):
     buf = torch.zeros(hi - lo + SLACK, dtype=torch.uint8)
     buf[: hi - lo] = torch.from_numpy(text[lo:hi])
     out = abi.HostColumns(SCHEMA, abi.default_caps(SCHEMA, nrec_bound(text), text.size))
-    info = sharded.ShardedParser(CheckerEngine(), SCHEMA, SLACK).parse(buf, hi - lo, out)
+    parser = sharded.ShardedParser(CheckerEngine(), SCHEMA, SLACK)
+    info = parser.parse(buf, hi - lo, out)
     np.savez(os.path.join(tmp, f"rank{rank}.npz"), **out.as_dict())
+    # a second call on the same parser with other shard sizes (rank 0 takes 50 000 bytes more, the last rank fewer):
+    # every rank must enter the size exchange again, whatever its own size did
+    bounds = [b[0] for b in sharded.split_even(text.size, world)] + [text.size]
+    bounds[1] += 50000
+    lo2, hi2 = bounds[rank], bounds[rank + 1]
+    buf2 = torch.zeros(hi2 - lo2 + SLACK, dtype=torch.uint8)
+    buf2[: hi2 - lo2] = torch.from_numpy(text[lo2:hi2])
+    out2 = abi.HostColumns(SCHEMA, abi.default_caps(SCHEMA, nrec_bound(text), text.size))
+    info2 = parser.parse(buf2, hi2 - lo2, out2)
+    info["second_call"] = (info2["total_records"], info2["first_record"], out2.n_records, info2["global_offset"] == lo2)
     torch.save(info, os.path.join(tmp, f"info{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
@@ -58,6 +69,9 @@ def test_shards_stitch_to_the_whole_stream(oracle, native, world):
         infos = [torch.load(os.path.join(tmp, f"info{r}.pt"), weights_only=False) for r in range(world)]
     assert sum(len(p["err_kind"]) for p in parts) == len(whole["err_kind"]) == infos[0]["total_records"]
     assert [i["first_record"] for i in infos] == list(np.cumsum([0] + [len(p["err_kind"]) for p in parts[:-1]]))
+    # the second call, with other shard sizes, found the same stream
+    assert all(i["second_call"][0] == len(whole["err_kind"]) and i["second_call"][3] for i in infos)
+    assert sum(i["second_call"][2] for i in infos) == len(whole["err_kind"])
     # every shard used the exchanged head of its successor
     assert all(i["slack_used"] > 0 for i in infos[:-1]) and infos[-1]["slack_used"] == 0
     # re-assemble every column from the shards with the bases the stitch reported
