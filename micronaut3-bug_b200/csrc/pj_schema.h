@@ -117,46 +117,10 @@ constexpr CF cf(const char* name, Kind kind, int col, int cnt = 0, int child = 0
 }
 
 template <int OBJ> struct CObj;
-/* Pet — petstore.json:872-922, required name + photoUrls (:873-876) */
-template <> struct CObj<OBJ_PET> {
-  static constexpr int N = 6, present_col = PJ_COL_PET_PRESENT, required = (1 << 2) | (1 << 3), type = PJ_TYPE_PET;
-  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_PET_ID), cf("category", K_OBJ, 0, 0, OBJ_CATEGORY),
-                              cf("name", K_STR, PJ_COL_PET_NAME_OFF, SLOT_PET_NAME),
-                              cf("photoUrls", K_LIST_STR, PJ_COL_PET_PHOTO_OFF, SLOT_PET_PHOTO_CNT),
-                              cf("tags", K_LIST_OBJ, PJ_COL_PET_TAGS_OFF, SLOT_PET_TAG_CNT, OBJ_TAG),
-                              cf("status", K_ENUM, PJ_COL_PET_STATUS, 0, 0)};
-};
-/* Category — petstore.json:858-871 */
-template <> struct CObj<OBJ_CATEGORY> {
-  static constexpr int N = 2, present_col = PJ_COL_PET_CAT_PRESENT, required = 0, type = 0;
-  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_PET_CAT_ID), cf("name", K_STR, PJ_COL_PET_CAT_NAME_OFF, SLOT_PET_CAT_NAME)};
-};
-/* Tag — petstore.json:923-936 */
-template <> struct CObj<OBJ_TAG> {
-  static constexpr int N = 2, present_col = PJ_COL_PET_TAG_PRESENT, required = 0, type = 0;
-  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_PET_TAG_ID), cf("name", K_STR, PJ_COL_PET_TAG_NAME_OFF, SLOT_PET_TAG_NAME)};
-};
-/* Order — petstore.json:937-971 */
-template <> struct CObj<OBJ_ORDER> {
-  static constexpr int N = 6, present_col = PJ_COL_ORD_PRESENT, required = 0, type = PJ_TYPE_ORDER;
-  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_ORD_ID), cf("petId", K_I64, PJ_COL_ORD_PET_ID), cf("quantity", K_I32, PJ_COL_ORD_QUANTITY),
-                              cf("shipDate", K_DATETIME, PJ_COL_ORD_SHIP_EPOCH), cf("status", K_ENUM, PJ_COL_ORD_STATUS, 0, 1),
-                              cf("complete", K_BOOL, PJ_COL_ORD_COMPLETE)};
-};
-/* User — petstore.json:824-857 */
-template <> struct CObj<OBJ_USER> {
-  static constexpr int N = 8, present_col = PJ_COL_USR_PRESENT, required = 0, type = PJ_TYPE_USER;
-  static constexpr CF f[N] = {cf("id", K_I64, PJ_COL_USR_ID), cf("username", K_STR, PJ_COL_USR_USERNAME_OFF, SLOT_USR_STR0 + 0),
-                              cf("firstName", K_STR, PJ_COL_USR_FIRSTNAME_OFF, SLOT_USR_STR0 + 1),
-                              cf("lastName", K_STR, PJ_COL_USR_LASTNAME_OFF, SLOT_USR_STR0 + 2),
-                              cf("email", K_STR, PJ_COL_USR_EMAIL_OFF, SLOT_USR_STR0 + 3),
-                              cf("password", K_STR, PJ_COL_USR_PASSWORD_OFF, SLOT_USR_STR0 + 4),
-                              cf("phone", K_STR, PJ_COL_USR_PHONE_OFF, SLOT_USR_STR0 + 5), cf("userStatus", K_I32, PJ_COL_USR_STATUS)};
-};
-/* enum literals: 0 Pet.status (petstore.json:912-916), 1 Order.status (:958-962) */
 template <int E> struct CEnum;
-template <> struct CEnum<0> { static constexpr int N = 3; static constexpr CF lit[N] = {cf("available", K_ENUM, 0), cf("pending", K_ENUM, 0), cf("sold", K_ENUM, 0)}; };
-template <> struct CEnum<1> { static constexpr int N = 3; static constexpr CF lit[N] = {cf("placed", K_ENUM, 0), cf("approved", K_ENUM, 0), cf("delivered", K_ENUM, 0)}; };
+/* The model tables themselves are GENERATED from the OpenAPI definitions (petstore.json:823-972) by the schema
+ * compiler, `python -m micronaut3-bug_b200.schemac`; a test regenerates the file and compares it byte for byte. */
+#include "pj_schema_models.inc"
 
 template <int OBJ>
 inline void copy_obj(Schema* s) {

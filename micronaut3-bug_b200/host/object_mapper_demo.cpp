@@ -31,7 +31,7 @@ int main() {
   try { om.readValue<Pet>("{\"id\":1,\"photoUrls\":[]}"); CHECK(false); }
   catch (const SerdeException& e) { CHECK(e.kind == PJ_E_REQUIRED && e.offset == 22); }
   try { om.readValue<Pet>("{\"name\":\"a\",\"photoUrls\":[],\"status\":\"lost\"}"); CHECK(false); }
-  catch (const SerdeException& e) { CHECK(e.kind == PJ_E_ENUM && e.offset == 37); }
+  catch (const SerdeException& e) { CHECK(e.kind == PJ_E_ENUM && e.offset == 36); }
   try { om.readValue<Order>("{\"quantity\":\"3\"}"); CHECK(false); }
   catch (const SerdeException& e) { CHECK(e.kind == PJ_E_TYPE && e.offset == 12); }
 

@@ -38,9 +38,9 @@ class Oracle:
         path = build.build_oracle()
         self.lib = C.CDLL(path)
 
-    def parse(self, schema, buf, framing=0, slack=0, is_first=1, is_last=1, goff=0, opts=0) -> "abi.HostColumns":
+    def parse(self, schema, buf, framing=0, slack=0, is_first=1, is_last=1, goff=0, opts=0, caps=None) -> "abi.HostColumns":
         buf = np.ascontiguousarray(buf, dtype=np.uint8)
-        hc = abi.HostColumns(schema, abi.default_caps(schema, nrec_bound(buf), buf.size))
+        hc = abi.HostColumns(schema, caps if caps is not None else abi.default_caps(schema, nrec_bound(buf), buf.size))
         st = self.lib.pjo_parse_opt(u32(schema), u32(framing), C.c_void_p(buf.ctypes.data), u64(buf.size - slack), u64(slack),
                                     int(is_first), int(is_last), u64(goff), u32(opts), C.byref(hc.raw))
         assert st == 0, st

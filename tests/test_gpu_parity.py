@@ -498,3 +498,15 @@ def test_writer_hex_case(native, oracle):
             n = c.write(1, cols, out)
             assert n == want.size and np.array_equal(out[:n], want)
     assert b"\\u001F" in bytes(oracle.write(1, cols)) and b"\\u001f" in bytes(oracle.write(1, cols, opts=HEX_LOWER))
+
+
+def test_cpp_object_mapper_mirror(native):
+    """The C++ mirror of the ObjectMapper surface (host/object_mapper.hpp): its self-checking program runs the calls a
+    user of the reference's serde API makes (readValue, writeValueAsString, exceptions with kind and offset)."""
+    import subprocess
+
+    import importlib
+
+    exe = importlib.import_module("micronaut3-bug_b200.build").build_facade_demo()
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr

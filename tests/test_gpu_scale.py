@@ -10,21 +10,19 @@ from pj_testlib import abi, pj
 pytestmark = pytest.mark.gpu
 
 
-def caps_for(schema, n, nbytes, items):
-    """Capacities that fit the generated corpora without reserving one input-sized arena per string column."""
-    caps = abi.default_caps(schema, n + 16, nbytes // 2 + 65536, items)
-    return caps
+def caps_for(schema, n, nbytes, items, arena_share=0.5):
+    """Capacities that fit the generated corpora without reserving one input-sized arena per string column
+    (arena_share: the largest part of the input that one string arena can hold)."""
+    return abi.default_caps(schema, n + 16, int(nbytes * arena_share) + 65536, items)
 
 
-def parse_both(native, oracle, schema, text, n, items, ctx_kw=None):
+def parse_both(native, oracle, schema, text, n, items, ctx_kw=None, arena_share=0.5):
     import torch
 
-    want = abi.HostColumns(schema, caps_for(schema, n, text.size, items))
-    st = oracle.lib.pjo_parse(np.uint32(schema).item(), 0, text.ctypes.data, text.size, 0, 1, 1, 0, __import__("ctypes").byref(want.raw))
-    assert st == 0
+    want = oracle.parse(schema, text, caps=caps_for(schema, n, text.size, items, arena_share))
     ctx = native.Context(device=0, **(ctx_kw or {}))
     d_text = torch.from_numpy(text).cuda()
-    cols = pj.DeviceColumns(schema, caps_for(schema, n, text.size, items), "cuda")
+    cols = pj.DeviceColumns(schema, caps_for(schema, n, text.size, items, arena_share), "cuda")
     torch.cuda.synchronize()
     ctx.parse(schema, d_text, cols)
     return want, ctx, d_text, cols
@@ -61,7 +59,7 @@ def test_one_million_pets_with_zipf_lists_escapes_and_blanks(native, oracle):
     flags = abi.PJ_GEN_ZIPF_LISTS | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE
     text = pj.gen_text(abi.PJ_SCHEMA_PET, 0xC3, 0, n, flags)
     assert text.size > 1_000_000_000
-    want, ctx, d_text, cols = parse_both(native, oracle, abi.PJ_SCHEMA_PET, text, n, text.size // 30)
+    want, ctx, d_text, cols = parse_both(native, oracle, abi.PJ_SCHEMA_PET, text, n, text.size // 30, arena_share=1.0)
     assert want.n_errors == 0
     assert_same_by_checksum(oracle, want, ctx, abi.PJ_SCHEMA_PET, cols)
     ctx.close()

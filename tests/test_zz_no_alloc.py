@@ -27,7 +27,7 @@ def reference_index(ctx, d_text, cap):
     return n, d_rs.cpu().numpy().view(np.uint64)
 
 
-def test_static_index_matches_the_allocating_one_twice_in_a_row(ctx):
+def test_static_index_matches_the_allocating_one_twice_in_a_row(ctx, oracle):
     import torch
 
     torch.cuda.set_device(0)
@@ -38,6 +38,8 @@ def test_static_index_matches_the_allocating_one_twice_in_a_row(ctx):
         d_text = torch.from_numpy(np.ascontiguousarray(text)).cuda()
         cap = int(np.count_nonzero(text == 10)) + 8
         want_n, want = reference_index(ctx, d_text, cap)
+        checker = oracle.index(np.ascontiguousarray(text))  # ... and both against the CPU checker's line index
+        assert want_n == checker.size and np.array_equal(want[:want_n], checker)
         d_rs = torch.full((cap,), -1, dtype=torch.int64, device="cuda")
         d_n = torch.full((1,), -1, dtype=torch.int64, device="cuda")
         pj.index_records_static(d_text, d_rs, d_n, stream)
