@@ -9,6 +9,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <chrono>
 #include <condition_variable>
 #include <functional>
@@ -1048,41 +1049,65 @@ struct NcclApi {
 };
 constexpr int PJ_NCCL_UINT64 = 5; /* ncclUint64 */
 
-/* a host thread that runs one job at a time */
+/* A host thread that runs one job at a time. Hand-over in both directions first spins for a while on an atomic
+ * sequence number (a job follows the previous one within microseconds in a steady stream of calls; a condition
+ * variable alone costs tens of microseconds per wake-up) and only then sleeps. */
 struct Worker {
   std::thread th;
   std::mutex m;
   std::condition_variable cv;
   std::function<void()> job;
-  bool has_job = false, stop = false, done = true;
+  std::atomic<uint64_t> submitted{0}, done{0};
+  std::atomic<bool> stop{false};
+  static constexpr int SPINS = 20000;
   void start() {
     th = std::thread([this] {
-      std::unique_lock<std::mutex> lk(m);
+      uint64_t seen = 0;
       for (;;) {
-        cv.wait(lk, [this] { return has_job || stop; });
-        if (stop) return;
-        std::function<void()> j = std::move(job);
-        has_job = false;
-        lk.unlock();
-        j();
-        lk.lock();
-        done = true;
+        int spins = 0;
+        while (submitted.load(std::memory_order_acquire) == seen && !stop.load(std::memory_order_acquire)) {
+          if (++spins < SPINS) { std::this_thread::yield(); continue; }
+          std::unique_lock<std::mutex> lk(m);
+          cv.wait(lk, [&] { return submitted.load(std::memory_order_acquire) != seen || stop.load(std::memory_order_acquire); });
+        }
+        if (stop.load(std::memory_order_acquire)) return;
+        seen = submitted.load(std::memory_order_acquire);
+        job();
+        { std::lock_guard<std::mutex> lk(m); done.store(seen, std::memory_order_release); }
         cv.notify_all();
       }
     });
   }
   void submit(std::function<void()> j) {
-    std::lock_guard<std::mutex> lk(m);
-    job = std::move(j); has_job = true; done = false;
+    { std::lock_guard<std::mutex> lk(m); job = std::move(j); submitted.fetch_add(1, std::memory_order_release); }
     cv.notify_all();
   }
   void wait() {
-    std::unique_lock<std::mutex> lk(m);
-    cv.wait(lk, [this] { return done; });
+    const uint64_t want = submitted.load(std::memory_order_acquire);
+    int spins = 0;
+    while (done.load(std::memory_order_acquire) != want) {
+      if (++spins < SPINS) { std::this_thread::yield(); continue; }
+      std::unique_lock<std::mutex> lk(m);
+      cv.wait(lk, [&] { return done.load(std::memory_order_acquire) == want; });
+    }
   }
   void finish() {
-    { std::lock_guard<std::mutex> lk(m); stop = true; cv.notify_all(); }
+    { std::lock_guard<std::mutex> lk(m); stop.store(true, std::memory_order_release); }
+    cv.notify_all();
     if (th.joinable()) th.join();
+  }
+};
+/* All workers of a group meet here in the middle of a job (every one of them runs the same job at the same time). */
+struct Rendezvous {
+  std::atomic<uint32_t> arrived{0}, generation{0};
+  void meet(uint32_t n) {
+    const uint32_t gen = generation.load(std::memory_order_acquire);
+    if (arrived.fetch_add(1, std::memory_order_acq_rel) + 1 == n) {
+      arrived.store(0, std::memory_order_relaxed);
+      generation.fetch_add(1, std::memory_order_release);
+    } else {
+      while (generation.load(std::memory_order_acquire) == gen) std::this_thread::yield();
+    }
   }
 };
 
@@ -1114,6 +1139,7 @@ struct pj_group {
   std::vector<unsigned long long*> h_table; /* pinned copy per shard */
   bool nccl = false;
   NcclApi api;
+  Rendezvous rendezvous;
   char err[256] = "";
 };
 
@@ -1281,7 +1307,7 @@ pj_status pj_group_parse(pj_group* g, uint32_t schema, uint8_t* const* in, const
       const uint64_t take = len[h] < want - got ? len[h] : want - got;
       if (take) {
         const cudaError_t e = cudaMemcpyPeerAsync(in[i] + len[i] + got, g->devs[i], in[h], g->devs[h], take, c->stream);
-        if (e != cudaSuccess) { S.status = set_err(c, PJ_ERR_CUDA, "cudaMemcpyPeerAsync: %s", cudaGetErrorString(e)); return; }
+        if (e != cudaSuccess) { S.status = set_err(c, PJ_ERR_CUDA, "cudaMemcpyPeerAsync: %s", cudaGetErrorString(e)); break; } /* no early return: every shard must reach the exchange */
       }
       got += take;
     }
@@ -1289,20 +1315,17 @@ pj_status pj_group_parse(pj_group* g, uint32_t schema, uint8_t* const* in, const
     S.slack_bytes = got;
     const bool is_last = goff[i] + len[i] + got == goff[n]; /* the readable bytes reach the end of the stream */
     const bool is_first = goff[i] == 0;                     /* nothing precedes: the line at byte 0 is this shard's */
-    S.status = parse_impl(c, schema, PJ_FRAMING_NDJSON, in[i], len[i], got, is_first, is_last, goff[i], PJ_MEM_DEVICE, &out[i]);
+    if (S.status == PJ_OK) S.status = parse_impl(c, schema, PJ_FRAMING_NDJSON, in[i], len[i], got, is_first, is_last, goff[i], PJ_MEM_DEVICE, &out[i]);
     if (S.status != PJ_OK && S.status != PJ_ERR_CAPACITY) {
       /* the table must still be exchanged by every shard (a collective): deliver zeros */
       cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream);
     }
     if (cudaEventElapsedTime(&S.slack_copy_ms, c->ev[6], c->ev[7]) != cudaSuccess) { S.slack_copy_ms = 0.f; (void)cudaGetLastError(); }
-  });
-  /* The exchange starts only when EVERY shard is through its parse: an all-gather kernel waits on its device for the
-     other devices' kernels, and a cudaMalloc on one of those (a parse growing its scratch) waits for the first device
-     to go idle, because new memory is mapped into the peers: together they would never finish. Nothing allocates
-     from here on. */
-  group_run(g, [&](int i) {
-    DeviceGuard guard(g->devs[i]);
-    pj_group_shard& S = shards[i];
+    /* The exchange starts only when EVERY shard is through its parse: an all-gather kernel waits on its device for the
+       other devices' kernels, and a cudaMalloc on one of those (a parse growing its scratch) waits for the first device
+       to go idle, because new memory is mapped into the peers: together they would never finish. Nothing allocates
+       from here on. */
+    g->rendezvous.meet((uint32_t)n);
     const auto t0 = std::chrono::steady_clock::now();
     const pj_status gs = group_gather(g, i, 0, len[i] ? len[i] : ~0ull);
     S.gather_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
@@ -1327,10 +1350,7 @@ pj_status pj_group_write(pj_group* g, uint32_t schema, const pj_columns* cols, u
     uint64_t out_len = 0;
     S.status = pj_write(c, schema, PJ_FRAMING_NDJSON, &cols[i], out[i], cap[i], PJ_MEM_DEVICE, &out_len);
     if (S.status != PJ_OK && S.status != PJ_ERR_CAPACITY) cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream);
-  });
-  group_run(g, [&](int i) { /* the exchange, once no shard allocates any more (see pj_group_parse) */
-    DeviceGuard guard(g->devs[i]);
-    pj_group_shard& S = shards[i];
+    g->rendezvous.meet((uint32_t)n); /* the exchange, once no shard allocates any more (see pj_group_parse) */
     const auto t0 = std::chrono::steady_clock::now();
     const pj_status gs = group_gather(g, i, 0, 0);
     S.gather_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
