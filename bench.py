@@ -376,6 +376,8 @@ def run_single(args, pj, abi):
         "gpu_launches": launches,
         "tile_kernel": {"threads_per_block": int(last_stats.tile_records), "blocks": int(last_stats.tiles), "fast_records": int(last_stats.fast_records),
                         "phase_cycles_per_block": [int(x) // max(int(last_stats.tiles), 1) for x in last_stats.phase_cycles],
+                        "wide_records": int(last_stats.wide_records), "wide_fast_records": int(last_stats.wide_fast_records),
+                        "wide_cycles_per_block": [int(x) // max(int(last_stats.tiles), 1) for x in last_stats.wide_cycles],
                         "lookback_polls": int(last_stats.lookback_polls), "lookback_rounds": int(last_stats.lookback_rounds)},
         "clocks": clocks,
         "e2e": e2e,

@@ -305,6 +305,11 @@ typedef struct pj_call_stats {
   uint64_t lookback_rounds; /* parse: 32-block look-back rounds, summed over blocks                 */
   uint32_t tile_records;    /* parse: records per block of the tile kernel                       */
   uint32_t tiles;           /* blocks of the tile kernel                                          */
+  uint64_t wide_records;    /* parse: long records walked by a whole warp instead of one thread    */
+  uint64_t wide_fast_records; /* parse: of those, finished by the word-at-a-time tokeniser (the rest took the
+                                 exact parser, lists still spread over the lanes)                  */
+  uint64_t wide_cycles[2];  /* parse: SM cycles the blocks spent in the warps' size pass and emit pass (part of
+                               phase_cycles[1] and [3])                                          */
 } pj_call_stats;
 
 /* Library version as major * 1000 + minor. */

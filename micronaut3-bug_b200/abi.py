@@ -140,7 +140,8 @@ class pj_call_stats(C.Structure):
                 ("main_kernel_ms", C.c_float), ("stage_ms", C.c_float * 8), ("stage_launches", C.c_uint32 * 8),
                 ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
                 ("algorithmic_bytes", C.c_uint64), ("fast_records", C.c_uint64), ("phase_cycles", C.c_uint64 * 4),
-                ("lookback_polls", C.c_uint64), ("lookback_rounds", C.c_uint64), ("tile_records", C.c_uint32), ("tiles", C.c_uint32)]
+                ("lookback_polls", C.c_uint64), ("lookback_rounds", C.c_uint64), ("tile_records", C.c_uint32), ("tiles", C.c_uint32),
+                ("wide_records", C.c_uint64), ("wide_fast_records", C.c_uint64), ("wide_cycles", C.c_uint64 * 2)]
 
 
 class HostColumns:

@@ -405,6 +405,8 @@ pj_status parse_stream(pj_ctx* c, uint32_t schema, const uint8_t* in, uint64_t l
     n_fast += r.n_fast; n_errors += r.n_errors;
     for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] += r.phase_cycles[k];
     c->stats.lookback_polls += r.lookback_polls; c->stats.lookback_rounds += r.lookback_rounds;
+    c->stats.wide_records += r.n_wide; c->stats.wide_fast_records += r.n_wide_fast;
+    c->stats.wide_cycles[0] += r.wide_cycles[0]; c->stats.wide_cycles[1] += r.wide_cycles[1];
     if (r.timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_parse: a bounded device-side wait ran out");
     if (r.over) over = true;
     const uint64_t rows_new = r.n_records;

@@ -35,6 +35,7 @@ struct Rd {
   uint32_t lf_ws;    /* array framing: LF is whitespace; otherwise LF ends the record */
   uint32_t open_end; /* the stream continues past `limit` (a shard's slack ran out) */
   uint32_t opts;     /* PJ_OPT_* bits that change a rule (enum, surrogate, coercion) */
+  uint64_t rec_end;  /* read by list hooks only: offset of the byte that ends the record (its LF, or `limit`) */
 };
 
 struct PS {
@@ -65,11 +66,17 @@ PJ_HD bool fail_first(const Rd& r, PS& s, uint32_t x) {
   return fail_byte(r, s, s.p, is_value_start(x) ? PJ_E_TYPE : PJ_E_SYNTAX, s.p);
 }
 PJ_HD void skip_ws(const Rd& r, PS& s) {
+  /* on locals: the position is written back once, and nothing is read again through `r` after a store */
+  const uint8_t* const in = r.in;
+  const uint64_t limit = r.limit;
+  const bool lf = r.lf_ws != 0;
+  uint64_t p = s.p;
   for (;;) {
-    uint32_t x = rd_get(r, s.p);
-    if (x == ' ' || x == '\t' || x == '\r' || (r.lf_ws && x == '\n')) s.p++;
+    const uint32_t x = p < limit ? ld_byte(in + p) : 0u;
+    if (x == ' ' || x == '\t' || x == '\r' || (lf && x == '\n')) p++;
     else break;
   }
+  s.p = p;
 }
 
 /* ---- string sink ----------------------------------------------------------------------------- */
@@ -112,7 +119,7 @@ PJ_HD bool hex4(const Rd& r, PS& s, uint64_t q, uint32_t* out) {
 }
 
 /* R7. s.p is at the opening quote; on success s.p is after the closing quote. */
-PJ_HD_NOINLINE bool lex_string(const Rd& r, PS& s, Sink& k) {
+PJ_HD bool lex_string_body(const Rd& r, PS& s, Sink& k) {
   uint64_t p = s.p + 1;
   for (;;) {
     uint32_t x = rd_get(r, p);
@@ -184,9 +191,19 @@ PJ_HD_NOINLINE bool lex_string(const Rd& r, PS& s, Sink& k) {
   }
 }
 
+PJ_HD_NOINLINE bool lex_string(const Rd& r0, PS& s, Sink& k0) {
+  /* copies that the byte stores of the sink cannot alias: reader and sink stay in registers while the string is read */
+  const Rd r = r0;
+  Sink k = k0;
+  const bool ok = lex_string_body(r, s, k);
+  k0 = k;
+  return ok;
+}
+
 /* R6. s.p at '-' or a digit. */
 struct Num { uint64_t mag, start; uint32_t neg, is_int, overflow; };
-PJ_HD_NOINLINE bool lex_number(const Rd& r, PS& s, Num& n) {
+PJ_HD_NOINLINE bool lex_number(const Rd& r0, PS& s, Num& n) {
+  const Rd r = r0;
   uint64_t p = s.p;
   n.start = p; n.neg = 0; n.is_int = 1; n.overflow = 0; n.mag = 0;
   uint32_t x = rd_get(r, p);
@@ -579,7 +596,16 @@ PJ_HD_NOINLINE bool parse_flat(const Schema& S, const Rd& r, PS& s, const ObjDes
 /* One record. s.p at the start of the extent. On success returns the model (PJ_TYPE_*), leaves the
  * counts in o.cnt and, in the emit pass, has stored every column at `row_of(type)`.
  * `schema` is PJ_SCHEMA_*; row_* give the model-table row per type for the emit pass. */
-template <bool W>
+/* What parse_record<>() asks before it walks a non-empty list element by element: a hook may take the whole list
+ * (s.p at its first element; on return 1, s.p is behind the `]` and the list's counters in o.cnt are final) or
+ * return 0 and leave everything untouched. */
+struct NoListHook {
+  static constexpr bool enabled = false;
+  template <bool W>
+  static PJ_HD int list(const Schema&, const Rd&, PS&, const FieldDesc&, Out<W>&) { return 0; }
+};
+
+template <bool W, class LH = NoListHook>
 PJ_HD uint32_t parse_record(const Schema& S, const Rd& r, PS& s, uint32_t schema, Out<W>& o, uint64_t rec_index) {
   for (uint32_t i = 0; i < NSLOT; ++i) o.cnt[i] = 0;
   uint32_t type = schema == PJ_SCHEMA_MIXED ? PJ_TYPE_NONE : schema;
@@ -676,6 +702,7 @@ PJ_HD uint32_t parse_record(const Schema& S, const Rd& r, PS& s, uint32_t schema
     v.present |= bit;
     skip_ws(r, s);
     if (rd_get(r, s.p) == ']') { s.p++; continue; }
+    if (LH::enabled && LH::template list<W>(S, r, s, F, o)) continue;
     for (;;) {
       skip_ws(r, s);
       x = rd_get(r, s.p);

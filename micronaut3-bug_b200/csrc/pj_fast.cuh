@@ -226,7 +226,8 @@ PJ_HD_NOINLINE uint64_t fast_string_tail(const uint8_t* ws, uint32_t q, uint32_t
  * *esc = it holds backslash escapes (so raw and decoded bytes differ). Plain strings (printable ASCII, no
  * backslash) are finished here, 8 bytes a step; the rest goes through fast_string_tail(). Refuses what it does not
  * accept, but for the one failure it reports itself: the record ending inside the string. */
-PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len, uint32_t* esc) {
+template <bool TAPE_LIMITS>
+PJ_HD bool fast_string_t(const Win& w, FastState& f, uint32_t* pos, uint32_t* len, uint32_t* esc) {
   uint32_t q = f.p + 1;
   for (;;) {
     const uint64_t m = swar_str_special(wpeek8(w, q));
@@ -249,11 +250,12 @@ PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len,
     if (status != FS_OK) return false;
     q = (uint32_t)r; dec = (uint32_t)(r >> 32) & 0xFFFFFFu; any_esc = (uint32_t)(r >> 56) & 1u;
   }
-  if (dec > TAPE_MAX_STR || f.p + 1 > 0xFFFFu) return false;
+  if (TAPE_LIMITS && (dec > TAPE_MAX_STR || f.p + 1 > 0xFFFFu)) return false; /* what a tape word can hold */
   *pos = f.p + 1; *len = dec; *esc = any_esc;
   f.p = q + 1;
   return true;
 }
+PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len, uint32_t* esc) { return fast_string_t<true>(w, f, pos, len, esc); }
 
 /* A plain short string (key or enum literal, <= 14 bytes) at f.p, packed like the model tables. */
 PJ_HD bool fast_short(const Win& w, FastState& f, uint32_t* len, uint64_t* lo, uint64_t* hi) {
@@ -447,10 +449,23 @@ struct DrainState {
 template <bool DR>
 struct FSinkT {
   static constexpr bool drain = DR;
+  static constexpr bool wide = false;
   Tape* t;
   uint32_t* cnt; /* [NSLOT] bytes / items counted so far */
   DrainState* d;
 };
+/* The sink of a record that all lanes of a warp tokenise together (same bytes, same steps): non-empty lists are
+ * handed to wide_fast_list<>() of pj_wide.cuh, which spreads their elements over the lanes. */
+struct FSinkWide {
+  static constexpr bool drain = true;
+  static constexpr bool wide = true;
+  Tape* t;
+  uint32_t* cnt;
+  DrainState* d;
+  uint32_t rec_end; /* window offset of the byte that ends the record (its line feed, or the limit) */
+};
+template <int OBJ, int I, class S>
+PJ_HD bool wide_fast_list(const Win& w, FastState& f, S& s);
 /* Tape words one list element of flat object E can take: header, scalars, one string per string property. */
 template <int E, int I = 0>
 constexpr uint32_t string_fields() {
@@ -681,7 +696,10 @@ PJ_HD bool root_value(const Win& w, FastState& f, S& s, FVals& v, FVals& cv) {
       f.p++;
       uint32_t j = 0;
       if (fast_ws(w, f) == ']') f.p++;
-      else {
+      else if constexpr (S::wide) {
+        if (!wide_fast_list<OBJ, I>(w, f, s)) return false;
+        j = s.cnt[cnt];
+      } else {
         for (;;) {
           if constexpr (kind == K_LIST_STR) {
             if (wbyte(w, f.p) != '"') return fast_wrong_type(f, wbyte(w, f.p));
@@ -788,15 +806,22 @@ PJ_HD uint32_t fast_record(const Win& w, uint32_t start, uint32_t limit, uint32_
   *err_kind = f.err; *err_pos = f.err_pos;
   return FAST_FAILED;
 }
+template <int SCHEMA, class S>
+PJ_HD bool fast_record_sink(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, S& s);
 template <int SCHEMA, bool DR>
 PJ_HD bool fast_record_body(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, uint32_t* cnt, Tape& t, DrainState* d) {
-  const uint32_t limit = f.limit, lf_ws = f.lf_ws;
-#pragma unroll
-  for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = 0;
-  t.n = 0;
-  v.present = 0; cv.present = 0;
   FSinkT<DR> s;
   s.t = &t; s.cnt = cnt; s.d = d;
+  return fast_record_sink<SCHEMA>(w, f, open_end, type_out, v, cv, s);
+}
+template <int SCHEMA, class S>
+PJ_HD bool fast_record_sink(const Win& w, FastState& f, uint32_t open_end, uint32_t* type_out, FVals& v, FVals& cv, S& s) {
+  const uint32_t limit = f.limit, lf_ws = f.lf_ws;
+  uint32_t* const cnt = s.cnt;
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) cnt[k] = 0;
+  s.t->n = 0;
+  v.present = 0; cv.present = 0;
   if (fast_ws(w, f) != '{' || f.p >= limit) return false;
   f.p++;
   fast_ws(w, f);

@@ -44,6 +44,9 @@ struct DevResult {
   unsigned long long n_fast;  /* records decoded by the speculative pass alone */
   unsigned long long phase_cycles[4]; /* tile kernel, summed over blocks: staging, tokenising, look-back, emit */
   unsigned long long lookback_polls, lookback_rounds;
+  unsigned long long n_wide;       /* records walked by a whole warp */
+  unsigned long long n_wide_fast;  /* of those, finished by the word-at-a-time tokeniser (the rest: the exact parser) */
+  unsigned long long wide_cycles[2]; /* cycles the blocks spent in the warps' size pass / emit pass, summed over blocks */
   unsigned long long first_opener; /* array framing: offset of the first `[` at depth 0 */
   uint32_t arr_final_s;            /* array framing: the input ends inside a string */
   int32_t arr_final_d;             /* array framing: nesting depth at the end of the input */

@@ -22,6 +22,7 @@
 
 #include "pj_kernels.cuh"
 #include "pj_lock.cuh"
+#include "pj_wide.cuh"
 #include "pj_stream.cuh"
 
 namespace pj {
@@ -321,8 +322,7 @@ __device__ __noinline__ void stream_emit_rest(const StreamArgs& a, const StreamG
 
 /* Emits record number `i` (base[] = its start in every arena / child table / model table). */
 template <int SCHEMA>
-__device__ __forceinline__ void stream_emit(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, const StreamLine& L, const Win& w, const Win& wd,
-                                            Tape& tp, const StreamRec<SCHEMA>& r, const uint32_t* base, uint64_t i) {
+__device__ __forceinline__ void stream_emit_head(const StreamArgs& a, const StreamLine& L, const StreamRec<SCHEMA>& r, const uint32_t* base, uint64_t i) {
   colp<uint64_t>(&a.cols, PJ_COL_REC_START)[i] = a.goff + L.gstart;
   colp<uint8_t>(&a.cols, PJ_COL_ERR_KIND)[i] = (uint8_t)r.err;
   colp<uint32_t>(&a.cols, PJ_COL_ERR_OFF)[i] = r.err_off;
@@ -331,6 +331,11 @@ __device__ __forceinline__ void stream_emit(const StreamArgs& a, const StreamGeo
     const uint32_t row = r.type == PJ_TYPE_PET ? base[SLOT_ROWS_PET] : (r.type == PJ_TYPE_ORDER ? base[SLOT_ROWS_ORD] : base[SLOT_ROWS_USR]);
     colp<uint32_t>(&a.cols, PJ_COL_REC_ROW)[i] = r.type == PJ_TYPE_NONE ? 0xFFFFFFFFu : row;
   }
+}
+template <int SCHEMA>
+__device__ __forceinline__ void stream_emit(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, const StreamLine& L, const Win& w, const Win& wd,
+                                            Tape& tp, const StreamRec<SCHEMA>& r, const uint32_t* base, uint64_t i) {
+  stream_emit_head<SCHEMA>(a, L, r, base, i);
   if (r.locked && r.tape_n <= tp.cap) lock_emit<SCHEMA>(w, &a.cols, r.type, r.v, r.cv, tp, base, r.cnt, i);
   else {
     StreamRec<SCHEMA> cold = r;
@@ -342,6 +347,107 @@ __device__ __forceinline__ void stream_emit(const StreamArgs& a, const StreamGeo
     for (uint32_t k = 0; k < NSLOT; ++k) bc[k] = base[k];
     stream_emit_rest<SCHEMA>(a, g, win, lc, wc, tc, cold, bc, i);
   }
+}
+
+/* ---- long records: a warp each (pj_wide.cuh) ----------------------------------------------------------------- */
+static constexpr uint32_t ST_WIDE_MIN = 1024; /* bytes from which a record of a model with lists is walked by a warp */
+static constexpr uint32_t ST_WIDE_CAP = 32;   /* such records per tile; what is beyond stays with its thread */
+struct WideSlot {
+  uint64_t gstart, gend, rec_index; /* input offsets of the record's first byte and of the byte that ends it */
+  uint32_t fits, type, err, err_off;
+  uint32_t fast; /* the word-at-a-time tokeniser accepted it: it emits it too */
+  uint32_t cnt[NSLOT], base[NSLOT];
+};
+template <int SCHEMA>
+__device__ __forceinline__ Rd stream_wide_reader(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, const WideSlot* ws) {
+  const int64_t w0 = (int64_t)g.v0 - (int64_t)g.mis;
+  Rd rd;
+  rd.in = ws->fits ? win - w0 : a.in; rd.lf_ws = 0; rd.open_end = a.is_last ? 0u : 1u; rd.limit = a.limit; rd.opts = a.opts;
+  rd.rec_end = ws->gend;
+  return rd;
+}
+/* The record of a slot as the word-at-a-time tokeniser addresses it: the staged window, or the bytes where they lie. */
+struct WideWin { Win w; uint32_t start, limit, end; };
+__device__ __forceinline__ WideWin stream_wide_win(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, const WideSlot* ws) {
+  WideWin r;
+  int64_t w0;
+  if (ws->fits) { r.w.s = win; w0 = (int64_t)g.v0 - (int64_t)g.mis; }
+  else {
+    const uint32_t mis4 = (uint32_t)(reinterpret_cast<uintptr_t>(a.in + ws->gstart) & 3u);
+    r.w.s = a.in + ws->gstart - mis4; w0 = (int64_t)ws->gstart - mis4;
+  }
+  r.w.w0 = w0;
+  const uint64_t rel = (uint64_t)((int64_t)a.limit - w0), rel_end = (uint64_t)((int64_t)ws->gend - w0);
+  r.limit = rel > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)rel;
+  r.end = rel_end > 0xFFFFFFF0ull ? 0xFFFFFFF0u : (uint32_t)rel_end;
+  r.start = (uint32_t)((int64_t)ws->gstart - w0);
+  return r;
+}
+/* Size pass of one long record, by all lanes of the calling warp: the word-at-a-time tokeniser first, the exact
+ * parser for what that one refuses. */
+template <int SCHEMA>
+__device__ __noinline__ void stream_wide_size(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, uint32_t* tape, WideSlot* ws) {
+  constexpr uint32_t LO = StreamSlots<SCHEMA>::lo, HI = StreamSlots<SCHEMA>::hi;
+  const bool lane0 = (threadIdx.x & 31u) == 0;
+  {
+    const WideWin ww = stream_wide_win(a, g, win, ws);
+    Tape tp;
+    tp.e = tape + threadIdx.x; tp.stride = ST_THREADS; tp.cap = ST_TAPE_CAP; tp.n = 0;
+    uint32_t cnt[NSLOT], type = PJ_TYPE_NONE, err = 0, fpos = 0;
+    uint32_t verdict = ww.end - ww.start < 0x7FFF0000u
+                           ? wide_outline<SCHEMA>(ww.w, ww.start, ww.limit, ww.end, a.is_last ? 0u : 1u, nullptr, nullptr, 0, tp, cnt, &type, &err, &fpos)
+                           : (uint32_t)FAST_REFUSED;
+    if (verdict == FAST_FAILED && opt_decides(a.opts, err)) verdict = FAST_REFUSED; /* the exact parser knows the options */
+    __syncwarp();
+    if (verdict != FAST_REFUSED) {
+      if (lane0) {
+        const bool ok = verdict == FAST_ACCEPTED;
+        ws->fast = ok ? 1u : 0u;
+        ws->type = ok ? type : (uint32_t)PJ_TYPE_NONE;
+        ws->err = ok ? 0u : err;
+        ws->err_off = ok ? 0u : fpos - ww.start;
+#pragma unroll
+        for (uint32_t k = 0; k < NSLOT; ++k) ws->cnt[k] = ok ? cnt[k] : 0u;
+        if (ok) atomicAdd(&a.res->n_wide_fast, 1ull);
+      }
+      return;
+    }
+  }
+  const Rd rd = stream_wide_reader<SCHEMA>(a, g, win, ws);
+  PS s;
+  s.p = ws->gstart; s.err = 0; s.err_pos = 0;
+  Out<false> so;
+  so.cols = &a.cols;
+  const uint32_t type = parse_record<false, WarpListHook>(c_schema, rd, s, (uint32_t)SCHEMA, so, 0);
+  __syncwarp();
+  if (lane0) {
+    ws->fast = 0;
+    ws->type = s.err ? (uint32_t)PJ_TYPE_NONE : type;
+    ws->err = s.err;
+    ws->err_off = s.err ? (uint32_t)(s.err_pos - ws->gstart) : 0u;
+#pragma unroll
+    for (uint32_t k = 0; k < NSLOT; ++k) ws->cnt[k] = (k >= LO && k < HI && !s.err) ? so.cnt[k] : 0u;
+  }
+}
+/* Emit pass of one long record that the size pass accepted. */
+template <int SCHEMA>
+__device__ __noinline__ void stream_wide_emit(const StreamArgs& a, const StreamGeom& g, const uint8_t* win, uint32_t* tape, const WideSlot* ws) {
+  if (ws->fast) {
+    const WideWin ww = stream_wide_win(a, g, win, ws);
+    Tape tp;
+    tp.e = tape + threadIdx.x; tp.stride = ST_THREADS; tp.cap = ST_TAPE_CAP; tp.n = 0;
+    uint32_t t_d, e_d, p_d;
+    wide_outline<SCHEMA>(ww.w, ww.start, ww.limit, ww.end, a.is_last ? 0u : 1u, &a.cols, ws->base, ws->rec_index, tp, nullptr, &t_d, &e_d, &p_d);
+    return;
+  }
+  const Rd rd = stream_wide_reader<SCHEMA>(a, g, win, ws);
+  PS s;
+  s.p = ws->gstart; s.err = 0; s.err_pos = 0;
+  Out<true> o;
+  o.cols = &a.cols;
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) { o.base[k] = ws->base[k]; o.room[k] = ws->cnt[k]; }
+  parse_record<true, WarpListHook>(c_schema, rd, s, (uint32_t)SCHEMA, o, ws->rec_index);
 }
 
 /* Looks, with the whole block, for the first line feed at or after input offset `from` (the end of the one line of a
@@ -449,18 +555,170 @@ __device__ __noinline__ void stream_overflow_tile(const StreamArgs& a, const Str
   if (tile == a.ntiles - 1) stream_close_offsets(a, tid, sh_base, sh_tot);
 }
 
-template <int SCHEMA>
-__global__ void __launch_bounds__(ST_THREADS, 512 / ST_THREADS) k_parse_stream(const __grid_constant__ StreamArgs a) {
-  constexpr uint32_t LO = StreamSlots<SCHEMA>::lo, HI = StreamSlots<SCHEMA>::hi, MASK = StreamSlots<SCHEMA>::mask;
+/* Which owned line a thread takes (>= nown: none). A tile with at most an eighth, a quarter or half as many lines as
+ * threads gives every 8th, 4th or 2nd thread a line: its warps share the work, and fewer lanes of a warp sit on
+ * records that make them take different paths. The order of the lines along the threads stays, so the scans do. */
+__device__ __forceinline__ uint32_t stream_line_of_thread(uint32_t tid, uint32_t nown) {
+  const uint32_t sh = nown <= ST_THREADS / 8 ? 3u : (nown <= ST_THREADS / 4 ? 2u : (nown <= ST_THREADS / 2 ? 1u : 0u));
+  return (tid & ((1u << sh) - 1u)) ? ST_NONE : (tid >> sh);
+}
+
+/* Everything a tile does once its line list stands: thread j takes owned line j, tokenises it, the tile's counts go
+ * through the look-back, every record is emitted. SPECIAL = the tile holds a line that runs out of the window or a
+ * long record of a model with lists: the block finds the end of the former together, and whole warps walk the
+ * latter (pj_wide.cuh). The common case is compiled without any of that. */
+template <int SCHEMA, bool SPECIAL>
+__device__ __forceinline__ void stream_tile_rest(const StreamArgs& a, const StreamGeom& g, uint8_t* win, const uint16_t* list, uint32_t* tape,
+                                                 uint32_t tile, uint32_t nlf, uint32_t nown, long long c0, long long c1) {
+  constexpr uint32_t MASK = StreamSlots<SCHEMA>::mask;
   constexpr uint32_t NWARPS = ST_THREADS / 32;
-  extern __shared__ __align__(16) uint8_t smem[];
-  __shared__ uint32_t sh_scan[33];
+  constexpr bool LISTS = SCHEMA == PJ_SCHEMA_PET || SCHEMA == PJ_SCHEMA_MIXED;
   __shared__ uint32_t sh_warp[ST_NLB][NWARPS];
   __shared__ uint32_t sh_tot[ST_NLB], sh_base[ST_NLB];
-  __shared__ uint32_t sh_tile, sh_ok;
+  __shared__ uint32_t sh_ok;
   __shared__ unsigned long long sh_end;
-  __shared__ __align__(8) unsigned long long sh_mbar;
+  __shared__ uint32_t sh_nwide;
+  __shared__ WideSlot sh_wide[SPECIAL ? ST_WIDE_CAP : 1];
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t mis = g.mis;
+
+  StreamLine L;
+  L.s = 0; L.fits = 0; L.gstart = 0;
+  bool is_rec = false;
+  const uint32_t nlist = nlf < ST_LF_CAP ? nlf : ST_LF_CAP;
+  const uint32_t j = stream_line_of_thread(tid, nown); /* a tile with few lines spreads them over its warps */
+  if (j < nown) {
+    L.s = list[j];
+    L.fits = (j + 1 < nlist) || g.to_limit;
+    L.gstart = g.v0 + L.s - mis;
+    is_rec = stream_is_record(win, L.s, g, a.in, a.limit, (int)a.is_last);
+  }
+  uint64_t end_known = ~0ull;
+  bool wide = false;
+  uint32_t wslot = 0;
+  if (SPECIAL) {
+    if (tid == 0) sh_nwide = 0;
+    /* at most one line of a tile runs out of the window (the last one): the block finds its end together */
+    if (__syncthreads_or(is_rec && !L.fits)) {
+      const uint64_t e = stream_find_end(a, g.v0 + ST_WIN_BYTES - mis, tid, &sh_end);
+      if (is_rec && !L.fits) end_known = e;
+    }
+    /* long records of the models with lists leave the thread-per-record path */
+    if (LISTS && is_rec) {
+      const uint32_t e_w = (j + 1 < nlist) ? (uint32_t)list[j + 1] - 1u : g.hi_valid;
+      const uint64_t gend = L.fits ? g.v0 + e_w - mis : end_known;
+      if (gend != ~0ull && gend - L.gstart >= ST_WIDE_MIN) {
+        wslot = atomicAdd(&sh_nwide, 1u);
+        if (wslot < ST_WIDE_CAP) {
+          wide = true;
+          sh_wide[wslot].gstart = L.gstart; sh_wide[wslot].gend = gend; sh_wide[wslot].fits = L.fits;
+        }
+      }
+    }
+  }
+  Tape tp;
+  tp.e = tape + tid; tp.stride = ST_THREADS; tp.cap = ST_TAPE_CAP; tp.n = 0;
+  StreamRec<SCHEMA> r;
+  Win w, wd;
+  r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0; r.locked = 0; r.direct = 0; r.tape_n = 0;
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
+  stream_tokenise<SCHEMA>(a, g, win, is_rec && !wide, L, end_known, tp, r, w, wd);
+  uint32_t nw = 0;
+  if (SPECIAL) {
+    __syncthreads();
+    nw = sh_nwide < ST_WIDE_CAP ? sh_nwide : ST_WIDE_CAP;
+    if (nw) {
+      if (tid == 0) atomicAdd(&a.res->n_wide, (unsigned long long)nw);
+      const long long w0c = clock64();
+      for (uint32_t q = warp; q < nw; q += NWARPS) stream_wide_size<SCHEMA>(a, g, win, tape, &sh_wide[q]);
+      __syncthreads();
+      if (tid == 0) atomicAdd(&a.res->wide_cycles[0], (unsigned long long)(clock64() - w0c));
+      if (wide) {
+        r.type = sh_wide[wslot].type; r.err = sh_wide[wslot].err; r.err_off = sh_wide[wslot].err_off;
+#pragma unroll
+        for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = sh_wide[wslot].cnt[k];
+      }
+    }
+  }
+  {
+    uint32_t pk = (r.err ? 1u : 0u) | (r.fast << 16);
+    for (int d = 16; d; d >>= 1) pk += __shfl_down_sync(0xFFFFFFFFu, pk, d);
+    if (lane == 0 && (pk & 0xFFFF)) atomicAdd(&a.res->n_errors, (unsigned long long)(pk & 0xFFFF));
+    if (lane == 0 && (pk >> 16)) atomicAdd(&a.res->n_fast, (unsigned long long)(pk >> 16));
+  }
+
+  /* ---- positions inside the tile, then the look-back ---- */
+  uint32_t base[ST_NLB];
+#pragma unroll
+  for (uint32_t k = 0; k < ST_NLB; ++k) {
+    if (!((MASK >> k) & 1u)) { base[k] = 0; continue; }
+    const uint32_t mine_k = k == ST_REC ? (is_rec ? 1u : 0u) : r.cnt[k];
+    const uint32_t inc = warp_incl_scan(mine_k);
+    if (lane == 31) sh_warp[k][warp] = inc;
+    base[k] = inc - mine_k;
+  }
+  __syncthreads();
+  const long long c2 = clock64();
+#pragma unroll
+  for (uint32_t k = 0; k < ST_NLB; ++k) {
+    if (!((MASK >> k) & 1u)) continue;
+#pragma unroll
+    for (uint32_t q = 0; q < NWARPS; ++q) if (q < warp) base[k] += sh_warp[k][q];
+  }
+  if (warp == 0) stream_resolve<MASK>(a, tile, lane, &sh_warp[0][0], NWARPS, sh_tot, sh_base, &sh_ok);
+  __syncthreads();
+  const long long c3 = clock64();
+  if (!sh_ok) return;
+
+  /* ---- emit ---- */
+  if (is_rec) {
+    uint32_t gb[NSLOT];
+#pragma unroll
+    for (uint32_t k = 0; k < NSLOT; ++k) gb[k] = base[k] + sh_base[k];
+    const uint64_t i = (uint64_t)sh_base[ST_REC] + base[ST_REC];
+    if (SPECIAL && wide && !r.err) { /* its warp writes the rest */
+      stream_emit_head<SCHEMA>(a, L, r, gb, i);
+      sh_wide[wslot].rec_index = i;
+#pragma unroll
+      for (uint32_t k = 0; k < NSLOT; ++k) sh_wide[wslot].base[k] = gb[k];
+    } else stream_emit<SCHEMA>(a, g, win, L, w, wd, tp, r, gb, i);
+  }
+  if (SPECIAL && nw) {
+    __syncthreads();
+    const long long w1c = clock64();
+    for (uint32_t q = warp; q < nw; q += NWARPS)
+      if (!sh_wide[q].err) stream_wide_emit<SCHEMA>(a, g, win, tape, &sh_wide[q]);
+    __syncthreads();
+    if (tid == 0) atomicAdd(&a.res->wide_cycles[1], (unsigned long long)(clock64() - w1c));
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const long long c4 = clock64();
+    atomicAdd(&a.res->phase_cycles[0], (unsigned long long)(c1 - c0));
+    atomicAdd(&a.res->phase_cycles[1], (unsigned long long)(c2 - c1));
+    atomicAdd(&a.res->phase_cycles[2], (unsigned long long)(c3 - c2));
+    atomicAdd(&a.res->phase_cycles[3], (unsigned long long)(c4 - c3));
+  }
+  /* the last tile closes the offset columns */
+  if (tile == a.ntiles - 1) stream_close_offsets(a, tid, sh_base, sh_tot);
+}
+/* The tiles with a line that leaves the window or with long records: out of line, so that the common tile keeps its
+ * registers. */
+template <int SCHEMA>
+__device__ __noinline__ void stream_special_tile(const StreamArgs& a, const StreamGeom& g, uint8_t* win, const uint16_t* list, uint32_t* tape,
+                                                 uint32_t tile, uint32_t nlf, uint32_t nown, long long c0, long long c1) {
+  stream_tile_rest<SCHEMA, true>(a, g, win, list, tape, tile, nlf, nown, c0, c1);
+}
+
+template <int SCHEMA>
+__global__ void __launch_bounds__(ST_THREADS, 512 / ST_THREADS) k_parse_stream(const __grid_constant__ StreamArgs a) {
+  constexpr bool LISTS = SCHEMA == PJ_SCHEMA_PET || SCHEMA == PJ_SCHEMA_MIXED;
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ uint32_t sh_scan[33];
+  __shared__ uint32_t sh_tile;
+  __shared__ __align__(8) unsigned long long sh_mbar;
+  const uint32_t tid = threadIdx.x;
   uint8_t* win = smem;
   uint16_t* lfb = reinterpret_cast<uint16_t*>(smem + ST_SMEM_WIN);
   uint16_t* list = reinterpret_cast<uint16_t*>(smem + ST_SMEM_WIN + ST_SMEM_LFB);
@@ -516,78 +774,16 @@ __global__ void __launch_bounds__(ST_THREADS, 512 / ST_THREADS) k_parse_stream(c
   __syncthreads();
   const long long c1 = clock64();
 
-  /* ---- thread j takes owned line j ---- */
-  StreamLine L;
-  L.s = 0; L.fits = 0; L.gstart = 0;
-  bool is_rec = false;
-  const uint32_t nlist = nlf < ST_LF_CAP ? nlf : ST_LF_CAP;
-  if (tid < nown) {
-    L.s = list[tid];
-    L.fits = (tid + 1 < nlist) || g.to_limit;
-    L.gstart = g.v0 + L.s - mis;
-    is_rec = stream_is_record(win, L.s, g, a.in, a.limit, (int)a.is_last);
+  /* a line that leaves the window, or a long record of a model with lists, sends the tile the other way */
+  bool special = false;
+  if (tid < nown) { /* any thread may look at any line here */
+    const uint32_t nlist = nlf < ST_LF_CAP ? nlf : ST_LF_CAP;
+    const bool has_next = tid + 1 < nlist;
+    const uint32_t len = (has_next ? (uint32_t)list[tid + 1] : g.hi_valid) - (uint32_t)list[tid];
+    special = !(has_next || g.to_limit) || (LISTS && len >= ST_WIDE_MIN);
   }
-  /* at most one line of a tile runs out of the window (the last one): the block finds its end together */
-  uint64_t end_known = ~0ull;
-  if (__syncthreads_or(is_rec && !L.fits)) {
-    const uint64_t e = stream_find_end(a, g.v0 + ST_WIN_BYTES - mis, tid, &sh_end);
-    if (is_rec && !L.fits) end_known = e;
-  }
-  Tape tp;
-  tp.e = tape + tid; tp.stride = ST_THREADS; tp.cap = ST_TAPE_CAP; tp.n = 0;
-  StreamRec<SCHEMA> r;
-  Win w, wd;
-  r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0; r.locked = 0; r.direct = 0; r.tape_n = 0;
-#pragma unroll
-  for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
-  stream_tokenise<SCHEMA>(a, g, win, is_rec, L, end_known, tp, r, w, wd);
-  {
-    uint32_t pk = (r.err ? 1u : 0u) | (r.fast << 16);
-    for (int d = 16; d; d >>= 1) pk += __shfl_down_sync(0xFFFFFFFFu, pk, d);
-    if (lane == 0 && (pk & 0xFFFF)) atomicAdd(&a.res->n_errors, (unsigned long long)(pk & 0xFFFF));
-    if (lane == 0 && (pk >> 16)) atomicAdd(&a.res->n_fast, (unsigned long long)(pk >> 16));
-  }
-
-  /* ---- positions inside the tile, then the look-back ---- */
-  uint32_t base[ST_NLB];
-#pragma unroll
-  for (uint32_t k = 0; k < ST_NLB; ++k) {
-    if (!((MASK >> k) & 1u)) { base[k] = 0; continue; }
-    const uint32_t mine_k = k == ST_REC ? (is_rec ? 1u : 0u) : r.cnt[k];
-    const uint32_t inc = warp_incl_scan(mine_k);
-    if (lane == 31) sh_warp[k][warp] = inc;
-    base[k] = inc - mine_k;
-  }
-  __syncthreads();
-  const long long c2 = clock64();
-#pragma unroll
-  for (uint32_t k = 0; k < ST_NLB; ++k) {
-    if (!((MASK >> k) & 1u)) continue;
-#pragma unroll
-    for (uint32_t q = 0; q < NWARPS; ++q) if (q < warp) base[k] += sh_warp[k][q];
-  }
-  if (warp == 0) stream_resolve<MASK>(a, tile, lane, &sh_warp[0][0], NWARPS, sh_tot, sh_base, &sh_ok);
-  __syncthreads();
-  const long long c3 = clock64();
-  if (!sh_ok) return;
-
-  /* ---- emit ---- */
-  if (is_rec) {
-    uint32_t gb[NSLOT];
-#pragma unroll
-    for (uint32_t k = 0; k < NSLOT; ++k) gb[k] = base[k] + sh_base[k];
-    stream_emit<SCHEMA>(a, g, win, L, w, wd, tp, r, gb, (uint64_t)sh_base[ST_REC] + base[ST_REC]);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    const long long c4 = clock64();
-    atomicAdd(&a.res->phase_cycles[0], (unsigned long long)(c1 - c0));
-    atomicAdd(&a.res->phase_cycles[1], (unsigned long long)(c2 - c1));
-    atomicAdd(&a.res->phase_cycles[2], (unsigned long long)(c3 - c2));
-    atomicAdd(&a.res->phase_cycles[3], (unsigned long long)(c4 - c3));
-  }
-  /* the last tile closes the offset columns */
-  if (tile == a.ntiles - 1) stream_close_offsets(a, tid, sh_base, sh_tot);
+  if (__syncthreads_or(special)) stream_special_tile<SCHEMA>(a, g, win, list, tape, tile, nlf, nown, c0, c1);
+  else stream_tile_rest<SCHEMA, false>(a, g, win, list, tape, tile, nlf, nown, c0, c1);
 }
 
 }  // namespace pj
