@@ -392,7 +392,7 @@ __device__ __noinline__ void stream_wide_size(const StreamArgs& a, const StreamG
   {
     const WideWin ww = stream_wide_win(a, g, win, ws);
     Tape tp;
-    tp.e = tape + threadIdx.x; tp.stride = ST_THREADS; tp.cap = ST_TAPE_CAP; tp.n = 0;
+    tp.e = tape + threadIdx.x; tp.stride = ST_THREADS; tp.cap = TAPE_MIN_CAP; tp.n = 0;
     uint32_t cnt[NSLOT], type = PJ_TYPE_NONE, err = 0, fpos = 0;
     uint32_t verdict = ww.end - ww.start < 0x7FFF0000u
                            ? wide_outline<SCHEMA>(ww.w, ww.start, ww.limit, ww.end, a.is_last ? 0u : 1u, nullptr, nullptr, 0, tp, cnt, &type, &err, &fpos)
@@ -435,7 +435,7 @@ __device__ __noinline__ void stream_wide_emit(const StreamArgs& a, const StreamG
   if (ws->fast) {
     const WideWin ww = stream_wide_win(a, g, win, ws);
     Tape tp;
-    tp.e = tape + threadIdx.x; tp.stride = ST_THREADS; tp.cap = ST_TAPE_CAP; tp.n = 0;
+    tp.e = tape + threadIdx.x; tp.stride = ST_THREADS; tp.cap = TAPE_MIN_CAP; tp.n = 0;
     uint32_t t_d, e_d, p_d;
     wide_outline<SCHEMA>(ww.w, ww.start, ww.limit, ww.end, a.is_last ? 0u : 1u, &a.cols, ws->base, ws->rec_index, tp, nullptr, &t_d, &e_d, &p_d);
     return;
@@ -577,8 +577,9 @@ __device__ __forceinline__ void stream_tile_rest(const StreamArgs& a, const Stre
   __shared__ uint32_t sh_tot[ST_NLB], sh_base[ST_NLB];
   __shared__ uint32_t sh_ok;
   __shared__ unsigned long long sh_end;
-  __shared__ uint32_t sh_nwide;
+  __shared__ uint32_t sh_nwide, sh_wnext[2];
   __shared__ WideSlot sh_wide[SPECIAL ? ST_WIDE_CAP : 1];
+  __shared__ uint32_t sh_wtape[SPECIAL ? ST_THREADS * TAPE_MIN_CAP : 1]; /* the warps' scratch tapes: the threads' own hold records that wait for emission */
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t mis = g.mis;
 
@@ -597,7 +598,7 @@ __device__ __forceinline__ void stream_tile_rest(const StreamArgs& a, const Stre
   bool wide = false;
   uint32_t wslot = 0;
   if (SPECIAL) {
-    if (tid == 0) sh_nwide = 0;
+    if (tid == 0) { sh_nwide = 0; sh_wnext[0] = 0; sh_wnext[1] = 0; }
     /* at most one line of a tile runs out of the window (the last one): the block finds its end together */
     if (__syncthreads_or(is_rec && !L.fits)) {
       const uint64_t e = stream_find_end(a, g.v0 + ST_WIN_BYTES - mis, tid, &sh_end);
@@ -623,15 +624,21 @@ __device__ __forceinline__ void stream_tile_rest(const StreamArgs& a, const Stre
   r.type = PJ_TYPE_NONE; r.err = 0; r.err_off = 0; r.fast = 0; r.locked = 0; r.direct = 0; r.tape_n = 0;
 #pragma unroll
   for (uint32_t k = 0; k < NSLOT; ++k) r.cnt[k] = 0;
+  if (SPECIAL) __syncthreads(); /* the slots of the long records stand */
   stream_tokenise<SCHEMA>(a, g, win, is_rec && !wide, L, end_known, tp, r, w, wd);
   uint32_t nw = 0;
-  if (SPECIAL) {
-    __syncthreads();
+  if (SPECIAL) { /* every warp goes on to its share of the long records as soon as its own threads are done */
     nw = sh_nwide < ST_WIDE_CAP ? sh_nwide : ST_WIDE_CAP;
     if (nw) {
       if (tid == 0) atomicAdd(&a.res->n_wide, (unsigned long long)nw);
       const long long w0c = clock64();
-      for (uint32_t q = warp; q < nw; q += NWARPS) stream_wide_size<SCHEMA>(a, g, win, tape, &sh_wide[q]);
+      for (;;) { /* the warps take the long records as they get free: they differ a lot in length */
+        uint32_t q = 0;
+        if (lane == 0) q = atomicAdd(&sh_wnext[0], 1u);
+        q = __shfl_sync(0xFFFFFFFFu, q, 0);
+        if (q >= nw) break;
+        stream_wide_size<SCHEMA>(a, g, win, sh_wtape, &sh_wide[q]);
+      }
       __syncthreads();
       if (tid == 0) atomicAdd(&a.res->wide_cycles[0], (unsigned long long)(clock64() - w0c));
       if (wide) {
@@ -687,8 +694,13 @@ __device__ __forceinline__ void stream_tile_rest(const StreamArgs& a, const Stre
   if (SPECIAL && nw) {
     __syncthreads();
     const long long w1c = clock64();
-    for (uint32_t q = warp; q < nw; q += NWARPS)
-      if (!sh_wide[q].err) stream_wide_emit<SCHEMA>(a, g, win, tape, &sh_wide[q]);
+    for (;;) {
+      uint32_t q = 0;
+      if (lane == 0) q = atomicAdd(&sh_wnext[1], 1u);
+      q = __shfl_sync(0xFFFFFFFFu, q, 0);
+      if (q >= nw) break;
+      if (!sh_wide[q].err) stream_wide_emit<SCHEMA>(a, g, win, sh_wtape, &sh_wide[q]);
+    }
     __syncthreads();
     if (tid == 0) atomicAdd(&a.res->wide_cycles[1], (unsigned long long)(clock64() - w1c));
   }

@@ -368,7 +368,7 @@ struct WideElem { /* evaluated where the class is instantiated, not inside devic
 /* One element that is a flat object, onto the lane's tape (header, scalars, strings) as root_value() lays it out.
  * *bytes: decoded bytes of its string property. */
 template <int OBJ, int I>
-__device__ __forceinline__ bool wide_object_to_tape(const Win& w, const FastState& f, uint32_t pos, Tape& lt, uint32_t* bytes, uint32_t* after) {
+__device__ __noinline__ bool wide_object_to_tape(const Win& w, const FastState& f, uint32_t pos, Tape& lt, uint32_t* bytes, uint32_t* after) {
   constexpr int E = FK<OBJ, I>::child;
   constexpr uint32_t cnt = FK<OBJ, I>::cnt, SS = WideElem<E>::string_slot;
   static_assert(1 + WideElem<E>::scalars + WideElem<E>::strings <= TAPE_MIN_CAP, "a list element fits an empty tape");
@@ -388,6 +388,45 @@ __device__ __forceinline__ bool wide_object_to_tape(const Win& w, const FastStat
   *bytes = SS < NSLOT ? lcnt[SS < NSLOT ? SS : 0] : 0u;
   *after = lf.p;
   return true;
+}
+
+__device__ __forceinline__ uint32_t wide_max(uint32_t x) {
+#pragma unroll
+  for (int d = 16; d; d >>= 1) { const uint32_t y = __shfl_xor_sync(0xFFFFFFFFu, x, d); x = y > x ? y : x; }
+  return x;
+}
+/* a string that is not plain (escapes, bytes beyond ASCII): its decoded length and the offset behind its closing quote */
+static __device__ __noinline__ bool wide_fancy_string(const Win& w, const FastState& f, uint32_t pos, uint32_t* bytes, uint32_t* behind) {
+  FastState lf = f;
+  lf.p = pos; lf.err = 0; lf.err_pos = 0;
+  uint32_t spos, sesc;
+  if (!fast_string_t<false>(w, lf, &spos, bytes, &sesc)) return false;
+  *behind = lf.p;
+  return true;
+}
+static __device__ __noinline__ uint32_t wide_emit_fancy_string(const Win& w, const FastState& f, uint32_t pos, uint8_t* dst) {
+  FastState lf = f;
+  lf.p = pos; lf.err = 0; lf.err_pos = 0;
+  uint32_t spos = 0, slen = 0, sesc = 0;
+  fast_string_t<false>(w, lf, &spos, &slen, &sesc);
+  if (sesc) copy_decoded(dst, w.s, spos, slen); else copy_win(dst, w, spos, slen);
+  return slen;
+}
+/* element number j of the list, a flat object at `pos`, into its row of the child table; its string at cursor `at` of
+ * its arena. Returns the string's decoded bytes. */
+template <int OBJ, int I>
+__device__ __noinline__ uint32_t wide_emit_object(const Win& w, const FastState& f, uint32_t pos, Tape& ltape, const DevCols* c, const uint32_t* base, uint32_t j, uint32_t at) {
+  constexpr int E = FK<OBJ, I>::child;
+  constexpr uint32_t cnt = FK<OBJ, I>::cnt, SS = WideElem<E>::string_slot;
+  uint32_t bytes = 0, behind = 0;
+  wide_object_to_tape<OBJ, I>(w, f, pos, ltape, &bytes, &behind);
+  uint32_t cur[NSLOT];
+#pragma unroll
+  for (uint32_t k = 0; k < NSLOT; ++k) cur[k] = 0;
+  cur[cnt] = j;
+  if constexpr (SS < NSLOT) cur[SS] = at;
+  for (uint32_t k = 0; k < ltape.n;) k = replay_word<OBJ>(w, c, ltape, k, tape_get(ltape, k), base, cur);
+  return bytes;
 }
 
 template <int OBJ, int I, class S>
@@ -464,38 +503,40 @@ __device__ __noinline__ bool wide_fast_list_impl(const Win& w, FastState& f, S& 
       }
     }
 
-    /* ---- first walk: sizes, separators, links ---- */
+    /* ---- first walk: sizes, separators, links. The lanes walk in step: as many rounds as the busiest lane has
+       elements, one exit, a lane that is done (or has found something wrong) idles through the rest ---- */
+    const uint32_t rounds = wide_max((uint32_t)__popc(starts));
     uint32_t bad = WIDE_NONE, end_rel = WIDE_NONE, my_n = 0, my_b = 0, endx = 0, my_pending = 0;
     {
       uint32_t m = starts;
-      bool first = lane == first_lane;
-      while (m) {
-        const uint32_t b = (uint32_t)__ffs((int)m) - 1u;
-        m &= m - 1u;
+      bool go = true, first = lane == first_lane;
+      for (uint32_t it = 0; it < rounds; ++it) {
+        const bool act = go && m != 0;
+        const uint32_t b = act ? (uint32_t)__ffs((int)m) - 1u : 0u;
+        if (act) m &= m - 1u;
         const uint32_t rel = 32u * lane + b;
         const uint32_t pos = (uint32_t)(cb + (int32_t)rel);
         const uint32_t succ = m ? 32u * lane + (uint32_t)(__ffs((int)m) - 1) : next_first;
-        if (first && pos != pending) { bad = rel; break; }
-        first = false;
-        uint32_t bytes = 0, behind = 0, nxt, ex;
+        bool ok = act && !(first && pos != pending);
+        if (act) first = false;
+        uint32_t bytes = 0, behind = 0, nxt = 0, ex = 0;
         if constexpr (objs) {
-          if (!wide_object_to_tape<OBJ, I>(w, f, pos, ltape, &bytes, &behind)) { bad = rel; break; }
+          if (ok) ok = wide_object_to_tape<OBJ, I>(w, f, pos, ltape, &bytes, &behind);
         } else {
-          const uint32_t close = wide_plain_close(wq, b);
+          const uint32_t close = ok ? wide_plain_close(wq, b) : WIDE_NONE;
           if (close != WIDE_NONE) { bytes = close - rel - 1u; behind = (uint32_t)(cb + (int32_t)close) + 1u; }
+          else if (ok) ok = wide_fancy_string(w, f, pos, &bytes, &behind);
+        }
+        if (ok) ok = wide_gap32(w, f.limit, behind, &nxt, &ex);
+        if (ok && !ex && succ != WIDE_NONE && (uint32_t)(cb + (int32_t)succ) != nxt) ok = false;
+        if (act) {
+          if (!ok) { bad = rel; go = false; }
           else {
-            FastState lf = f;
-            lf.p = pos; lf.err = 0; lf.err_pos = 0;
-            uint32_t spos, sesc;
-            if (!fast_string_t<false>(w, lf, &spos, &bytes, &sesc)) { bad = rel; break; }
-            behind = lf.p;
+            my_n++; my_b += bytes;
+            if (ex) { end_rel = rel; endx = ex; go = false; }
+            else if (succ == WIDE_NONE) my_pending = nxt;
           }
         }
-        if (!wide_gap32(w, f.limit, behind, &nxt, &ex)) { bad = rel; break; }
-        my_n++; my_b += bytes;
-        if (ex) { end_rel = rel; endx = ex; break; }
-        if (succ == WIDE_NONE) my_pending = nxt;
-        else if ((uint32_t)(cb + (int32_t)succ) != nxt) { bad = rel; break; }
       }
     }
     const uint32_t END = wide_min(end_rel), BAD = wide_min(bad);
@@ -506,37 +547,24 @@ __device__ __noinline__ bool wide_fast_list_impl(const Win& w, FastState& f, S& 
     /* ---- second walk (emitting pass): every element knows its place now ---- */
     if (emit) {
       uint32_t m = starts, j = d.cur[cnt] + n_el + ex_n, at = d.cur[SS < NSLOT ? SS : 0] + tot + ex_b;
-      while (m) {
-        const uint32_t b = (uint32_t)__ffs((int)m) - 1u;
-        m &= m - 1u;
+      for (uint32_t it = 0; it < rounds; ++it) {
+        const uint32_t b = m ? (uint32_t)__ffs((int)m) - 1u : 0u;
         const uint32_t rel = 32u * lane + b;
-        if (rel > END) break; /* END == WIDE_NONE: no element is beyond it */
+        const bool act = m != 0 && rel <= END; /* END == WIDE_NONE: no element is beyond it */
+        m &= m - 1u;
         const uint32_t pos = (uint32_t)(cb + (int32_t)rel);
         if constexpr (objs) {
-          uint32_t bytes, behind;
-          wide_object_to_tape<OBJ, I>(w, f, pos, ltape, &bytes, &behind);
-          uint32_t cur[NSLOT];
-#pragma unroll
-          for (uint32_t k = 0; k < NSLOT; ++k) cur[k] = 0;
-          cur[cnt] = j;
-          if constexpr (SS < NSLOT) cur[SS] = at;
-          for (uint32_t k = 0; k < ltape.n;) k = replay_word<OBJ>(w, d.c, ltape, k, tape_get(ltape, k), d.base, cur);
-          at += bytes;
+          if (act) at += wide_emit_object<OBJ, I>(w, f, pos, ltape, d.c, d.base, j, at);
         } else {
-          uint8_t* dst = colp<uint8_t>(d.c, col + 2) + d.base[cnt + 1] + at;
-          colp<uint32_t>(d.c, col + 1)[(uint64_t)d.base[cnt] + j] = d.base[cnt + 1] + at;
-          const uint32_t close = wide_plain_close(wq, b);
-          if (close != WIDE_NONE) { copy_win(dst, w, pos + 1u, close - rel - 1u); at += close - rel - 1u; }
-          else {
-            FastState lf = f;
-            lf.p = pos; lf.err = 0; lf.err_pos = 0;
-            uint32_t spos = 0, slen = 0, sesc = 0;
-            fast_string_t<false>(w, lf, &spos, &slen, &sesc);
-            if (sesc) copy_decoded(dst, w.s, spos, slen); else copy_win(dst, w, spos, slen);
-            at += slen;
+          const uint32_t close = act ? wide_plain_close(wq, b) : WIDE_NONE;
+          if (act) {
+            uint8_t* dst = colp<uint8_t>(d.c, col + 2) + d.base[cnt + 1] + at;
+            colp<uint32_t>(d.c, col + 1)[(uint64_t)d.base[cnt] + j] = d.base[cnt + 1] + at;
+            if (close != WIDE_NONE) { copy_win(dst, w, pos + 1u, close - rel - 1u); at += close - rel - 1u; }
+            else at += wide_emit_fancy_string(w, f, pos, dst);
           }
         }
-        j++;
+        if (act) j++;
       }
     }
     n_el += wide_sum(my_n); tot += wide_sum(my_b);

@@ -8,6 +8,7 @@ import os
 import random
 import re
 import subprocess
+import sys
 
 import numpy as np
 import pytest
@@ -28,10 +29,15 @@ G = abi  # generator flags live in the abi module
 def emu(native):  # `native` builds libpetjson.so, whose generator the tests use
     csrc = os.path.join(ROOT, "micronaut3-bug_b200", "csrc")
     deps = [SRC] + [os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith((".cuh", ".h"))]
-    if not os.path.exists(LIB) or any(os.path.getmtime(d) > os.path.getmtime(LIB) for d in deps):
-        subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-I", os.path.join(ROOT, "include"), "-I", csrc,
-                        "-x", "c++", SRC, "-o", LIB], check=True)
-    return C.CDLL(LIB)
+    # PJ_EMU_SANITIZE=1 (set by test_device_code_under_sanitizers for its child process): the same sources with
+    # AddressSanitizer and UndefinedBehaviorSanitizer, every finding fatal
+    san = os.environ.get("PJ_EMU_SANITIZE") == "1"
+    lib = LIB.replace(".so", "_san.so") if san else LIB
+    flags = ["-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=all"] if san else ["-O2"]
+    if not os.path.exists(lib) or any(os.path.getmtime(d) > os.path.getmtime(lib) for d in deps):
+        subprocess.run(["g++", *flags, "-std=c++17", "-fPIC", "-shared", "-I", os.path.join(ROOT, "include"), "-I", csrc,
+                        "-x", "c++", SRC, "-o", lib], check=True)
+    return C.CDLL(lib)
 
 
 def garbage_columns(schema, n, nbytes):
@@ -318,3 +324,18 @@ def test_option_switches_on_mutated_text(emu, oracle, opts):
             got, _ = emu_parse_tiles(emu, oracle, schema, body, lock=lock, opts=opts)
             assert same_result(want, got) == "", (opts, it, schema, lock)
     emu.emu_set_options(u32(0))
+
+
+def test_device_code_under_sanitizers():
+    """The device-side parsers, line index and writers, compiled for the host with AddressSanitizer and
+    UndefinedBehaviorSanitizer, run a slice of the tests above in a child process: an out-of-bounds read of a window,
+    a tape or a column, a misaligned word load or a shift by 64 ends the child."""
+    asan = subprocess.run(["gcc", "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    if not os.path.isabs(asan) or not os.path.exists(asan):
+        pytest.skip("no libasan beside this gcc")
+    env = dict(os.environ, PJ_EMU_SANITIZE="1", LD_PRELOAD=asan, ASAN_OPTIONS="detect_leaks=0:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1")
+    pick = "stream_line_index or lockstep_tokeniser_edges or common_failures or (mutated_text and 1) or tiny_records_and_long_lines or integer_text or array_framing or option_switches_known"
+    r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-p", "no:cacheprovider", os.path.abspath(__file__), "-k", pick],
+                       env=env, capture_output=True, text=True, cwd=HERE, timeout=1500)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "passed" in r.stdout and "deselected" in r.stdout
