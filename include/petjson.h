@@ -432,12 +432,14 @@ typedef struct pj_group_shard {
   uint64_t first_row[4];   /* rows of the model tables that precede the shard's, indexed by PJ_TYPE_*     */
   uint64_t bytes;          /* parse: input bytes the shard owns; write: text bytes it produced             */
   uint64_t slack_bytes;    /* parse: bytes of the following shards that were copied behind this one        */
-  const uint64_t* table_dev; /* DEVICE memory of the shard's GPU: the gathered table [ndev][PJ_GROUP_NCOUNT],
-                                valid until the next call on the group                                   */
+  const uint64_t* table_dev; /* DEVICE memory of the shard's GPU: the gathered table [ndev][PJ_GROUP_NCOUNT]. The
+                                all-gather that fills it is enqueued on a stream of the group's own and not waited
+                                for (the answer above comes from host copies): call pj_group_sync() before
+                                anything reads it. Valid until the next call on the group                   */
   pj_status status;        /* this shard's own status (the call returns the first one that is not PJ_OK)   */
   float slack_copy_ms;     /* parse: CUDA-event time of the device-to-device copy of the slack bytes        */
-  float gather_ms;         /* host time from "this shard's kernels are done" to "the table is back": the
-                              counter kernel, the all-gather (which waits for the slowest shard) and the read-back */
+  float gather_ms;         /* host time to enqueue the exchange of the device tables (counter kernel and
+                              all-gather); the caller's answer comes from the host copies of the counters   */
   uint32_t reserved;
 } pj_group_shard;
 
@@ -453,6 +455,8 @@ pj_ctx* pj_group_ctx(pj_group* grp, int32_t i);
 const char* pj_group_last_error(const pj_group* grp);
 /* 1 when the group exchanges its table with NCCL, 0 when it goes through the host */
 int32_t pj_group_uses_nccl(const pj_group* grp);
+/* Waits until the device tables (pj_group_shard.table_dev) of the last call are complete on every shard. */
+pj_status pj_group_sync(pj_group* grp);
 
 /* Replaces ObjectMapper#readValue (MyEntityConfig.java:34) for a stream spread over the group's GPUs.
  * in[g]: shard g's bytes in device g's memory, len[g] of them, followed by room[g] writable bytes (at least

@@ -67,6 +67,8 @@ def lib() -> C.CDLL:
         L.pj_group_last_error.argtypes = [C.c_void_p]
         L.pj_group_last_error.restype = C.c_char_p
         L.pj_group_uses_nccl.argtypes = [C.c_void_p]
+        L.pj_group_sync.argtypes = [C.c_void_p]
+        L.pj_group_sync.restype = C.c_int
         L.pj_group_parse.argtypes = [C.c_void_p, u32, C.POINTER(C.c_void_p), C.POINTER(u64), C.POINTER(u64), u64, C.POINTER(abi.pj_columns),
                                      C.POINTER(abi.pj_group_shard)]
         L.pj_group_write.argtypes = [C.c_void_p, u32, C.POINTER(abi.pj_columns), C.POINTER(C.c_void_p), C.POINTER(u64), C.POINTER(abi.pj_group_shard)]
@@ -348,6 +350,12 @@ class Group:
         lib().pj_last_stats(lib().pj_group_ctx(self._h, i), C.byref(s))
         return s
 
+    def sync(self) -> None:
+        """pj_group_sync: the device tables (pj_group_shard.table_dev) of the last call are complete on return."""
+        st = lib().pj_group_sync(self._h)
+        if st != abi.PJ_OK:
+            raise PetJsonError(st, "pj_group_sync", (lib().pj_group_last_error(self._h) or b"").decode())
+
     def _cols_array(self, cols):
         arr = (abi.pj_columns * len(cols))()
         for k, c in enumerate(cols):
@@ -369,6 +377,27 @@ class Group:
         if st != abi.PJ_OK and not (allow_capacity and st == abi.PJ_ERR_CAPACITY):
             raise PetJsonError(st, "pj_group_parse", (lib().pj_group_last_error(self._h) or b"").decode())
         return list(shards)
+
+    def prepare_parse(self, schema: int, bufs, lengths, cols, slack: int = 65536):
+        """The argument arrays of parse(), built once for callers that parse into the same buffers again and again
+        (a service loop, the benchmark): run it with parse_prepared()."""
+        n = len(self.devices)
+        return {"schema": schema, "slack": slack, "cols": list(cols), "keep": list(bufs),
+                "ptrs": (C.c_void_p * n)(*[int(b.data_ptr()) for b in bufs]),
+                "lens": (u64 * n)(*[int(x) for x in lengths]),
+                "room": (u64 * n)(*[int(b.numel()) - int(x) for b, x in zip(bufs, lengths)]),
+                "arr": self._cols_array(cols), "shards": (abi.pj_group_shard * n)()}
+
+    def parse_prepared(self, prep, allow_capacity: bool = False):
+        """One pj_group_parse call with prepared arguments; the columns' counters are refreshed, the shard table of the
+        prepared object is returned (valid until the next call)."""
+        st = lib().pj_group_parse(self._h, prep["schema"], prep["ptrs"], prep["lens"], prep["room"], prep["slack"], prep["arr"], prep["shards"])
+        arr = prep["arr"]
+        for k, c in enumerate(prep["cols"]):
+            C.memmove(C.byref(c.raw), C.byref(arr[k]), C.sizeof(abi.pj_columns))
+        if st != abi.PJ_OK and not (allow_capacity and st == abi.PJ_ERR_CAPACITY):
+            raise PetJsonError(st, "pj_group_parse", (lib().pj_group_last_error(self._h) or b"").decode())
+        return prep["shards"]
 
     def write(self, schema: int, cols, outs, allow_capacity: bool = False):
         """cols[g]: DeviceColumns on device g; outs[g]: a uint8 CUDA tensor on device g. Returns the list of pj_group_shard

@@ -1139,6 +1139,8 @@ struct pj_group {
   std::vector<unsigned long long*> d_mine;  /* [PJ_GROUP_NCOUNT] on the shard's device */
   std::vector<unsigned long long*> d_table; /* [ndev][PJ_GROUP_NCOUNT] on the shard's device */
   std::vector<unsigned long long*> h_table; /* pinned copy per shard */
+  std::vector<cudaStream_t> xs;             /* the exchange's own stream per shard: the next call's kernels do not wait for it */
+  std::vector<cudaEvent_t> ev_cnt, ev_xdone; /* counters written (shard's stream) / exchange finished (its own stream) */
   bool nccl = false;
   NcclApi api;
   Rendezvous rendezvous;
@@ -1161,38 +1163,50 @@ void group_run(pj_group* g, F&& fn) {
   for (int i = 0; i < g->ndev; ++i) g->workers[i]->wait();
 }
 
-/* After every shard's kernels are enqueued: its counters go into the table that every device ends up with.
- * `res_index`: which result block of the context holds the call's last totals; `bytes`: PJ_GC_BYTES (0: the
- * writer's byte count from the result block). Called on the shard's thread, its device current. */
+/* The counters of one shard as the table holds them, from the host copy of the result block of its last launch
+ * (the same rule as k_group_counters). */
+void group_host_row(const DevResult& res, uint64_t bytes, unsigned long long* row) {
+  for (uint32_t k = 0; k < PJ_GROUP_NCOUNT; ++k) {
+    unsigned long long v = 0;
+    if (k == PJ_GC_RECORDS) v = res.n_records;
+    else if (k == PJ_GC_ERRORS) v = res.n_errors;
+    else if (k == PJ_GC_BYTES) v = bytes ? bytes : res.out_bytes;
+    else if (k == PJ_GC_ROWS_PET) v = res.total[SLOT_ROWS_PET];
+    else if (k == PJ_GC_ROWS_ORDER) v = res.total[SLOT_ROWS_ORD];
+    else if (k == PJ_GC_ROWS_USER) v = res.total[SLOT_ROWS_USR];
+    else if (k >= PJ_GC_COUNTER0 && k < PJ_GC_COUNTER0 + NSLOT) v = res.total[k - PJ_GC_COUNTER0];
+    row[k] = v;
+  }
+}
+/* The exchange of the counter table. A shard's call has read its result block back already, so the HOST table (row i
+ * of h_table[0], written by shard i's thread before the rendezvous) is complete once every thread has passed the
+ * rendezvous, and the caller's answer needs nothing else. The DEVICE tables are produced without the host, and
+ * without the shard's stream, waiting for them: the counters of the result block are gathered by k_group_counters on
+ * the shard's stream, and ncclAllGather runs on a stream of its own behind an event — an all-gather of eight ranks
+ * takes longer than a tenth of a parse step, and the next step's kernels have no reason to queue behind it. (When
+ * the device list repeats a device the host table is uploaded instead.) Called on the shard's thread, its device
+ * current. */
 pj_status group_gather(pj_group* g, int i, int res_index, uint64_t bytes) {
   pj_ctx* c = g->ctx[i];
-  k_group_counters<<<1, 32, 0, c->stream>>>(c->d_res + res_index, bytes, g->d_mine[i]);
-  if (cudaGetLastError() != cudaSuccess) return PJ_ERR_CUDA;
   if (g->nccl) {
-    const int r = g->api.AllGather(g->d_mine[i], g->d_table[i], PJ_GROUP_NCOUNT, PJ_NCCL_UINT64, g->comms[i], c->stream);
+    if (cudaStreamWaitEvent(c->stream, g->ev_xdone[i], 0) != cudaSuccess) return PJ_ERR_CUDA; /* the exchange before this one has read d_mine */
+    k_group_counters<<<1, 32, 0, c->stream>>>(c->d_res + res_index, bytes, g->d_mine[i]);
+    if (cudaGetLastError() != cudaSuccess) return PJ_ERR_CUDA;
+    if (cudaEventRecord(g->ev_cnt[i], c->stream) != cudaSuccess || cudaStreamWaitEvent(g->xs[i], g->ev_cnt[i], 0) != cudaSuccess) return PJ_ERR_CUDA;
+    const int r = g->api.AllGather(g->d_mine[i], g->d_table[i], PJ_GROUP_NCOUNT, PJ_NCCL_UINT64, g->comms[i], g->xs[i]);
     if (r != 0) return set_err(c, PJ_ERR_NCCL, "ncclAllGather: %s", g->api.GetErrorString(r));
-    if (cudaMemcpyAsync(g->h_table[i], g->d_table[i], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess) return PJ_ERR_CUDA;
+    if (cudaEventRecord(g->ev_xdone[i], g->xs[i]) != cudaSuccess) return PJ_ERR_CUDA;
   } else {
-    /* through the host: own counters down now, the assembled table up once every shard has delivered (group_spread) */
-    if (cudaMemcpyAsync(g->h_table[i] + (size_t)i * PJ_GROUP_NCOUNT, g->d_mine[i], sizeof(unsigned long long) * PJ_GROUP_NCOUNT, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess) return PJ_ERR_CUDA;
+    cudaStreamSynchronize(g->xs[i]); /* the upload before this one has read h_table[i] */
+    if (i) memcpy(g->h_table[i], g->h_table[0], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev);
+    if (cudaMemcpyAsync(g->d_table[i], g->h_table[i], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev, cudaMemcpyHostToDevice, g->xs[i]) != cudaSuccess) return PJ_ERR_CUDA;
   }
-  if (cudaStreamSynchronize(c->stream) != cudaSuccess) return PJ_ERR_CUDA;
   return PJ_OK;
 }
-/* host exchange, second half: every shard's row of the table to every device */
-pj_status group_spread(pj_group* g) {
-  if (g->nccl) return PJ_OK;
-  for (int i = 1; i < g->ndev; ++i) memcpy(g->h_table[0] + (size_t)i * PJ_GROUP_NCOUNT, g->h_table[i] + (size_t)i * PJ_GROUP_NCOUNT, sizeof(unsigned long long) * PJ_GROUP_NCOUNT);
-  for (int i = 1; i < g->ndev; ++i) memcpy(g->h_table[i], g->h_table[0], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev);
-  pj_status st = PJ_OK;
-  group_run(g, [&](int i) {
-    DeviceGuard guard(g->devs[i]);
-    pj_ctx* c = g->ctx[i];
-    if (cudaMemcpyAsync(g->d_table[i], g->h_table[i], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev, cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
-        cudaStreamSynchronize(c->stream) != cudaSuccess)
-      st = PJ_ERR_CUDA;
-  });
-  return st;
+/* the device table of shard i is complete (for a caller that wants to read it) */
+pj_status group_wait_table(pj_group* g, int i) {
+  DeviceGuard guard(g->devs[i]);
+  return cudaStreamSynchronize(g->xs[i]) == cudaSuccess ? PJ_OK : PJ_ERR_CUDA;
 }
 void group_fill(pj_group* g, pj_group_shard* shards, bool offsets_from_bytes) {
   uint64_t off = 0, rec = 0, rows[4] = {0, 0, 0, 0};
@@ -1243,6 +1257,14 @@ pj_status pj_group_create(int32_t ndev, const int32_t* devs, const pj_options* o
       st = set_err(nullptr, PJ_ERR_NOMEM, "pj_group_create: allocation failed on device %d", devs[i]);
     }
     g->d_mine.push_back(mine); g->d_table.push_back(table); g->h_table.push_back(host);
+    cudaStream_t xs = nullptr;
+    cudaEvent_t e1 = nullptr, e2 = nullptr;
+    if (st == PJ_OK && (cudaStreamCreateWithFlags(&xs, cudaStreamNonBlocking) != cudaSuccess || cudaEventCreateWithFlags(&e1, cudaEventDisableTiming) != cudaSuccess ||
+                        cudaEventCreateWithFlags(&e2, cudaEventDisableTiming) != cudaSuccess)) {
+      (void)cudaGetLastError();
+      st = set_err(nullptr, PJ_ERR_CUDA, "pj_group_create: stream / event creation failed on device %d", devs[i]);
+    }
+    g->xs.push_back(xs); g->ev_cnt.push_back(e1); g->ev_xdone.push_back(e2);
     /* every device may read its neighbours' input buffers (the slack copy) */
     for (int k = 0; k < ndev && st == PJ_OK; ++k) {
       if (devs[k] == devs[i]) continue;
@@ -1269,9 +1291,17 @@ pj_status pj_group_create(int32_t ndev, const int32_t* devs, const pj_options* o
 void pj_group_destroy(pj_group* g) {
   if (!g) return;
   for (Worker* w : g->workers) { w->finish(); delete w; }
+  for (size_t i = 0; i < g->ctx.size(); ++i) {
+    DeviceGuard guard(g->devs[i]);
+    if (g->ctx[i]) cudaStreamSynchronize(g->ctx[i]->stream);
+    if (i < g->xs.size() && g->xs[i]) cudaStreamSynchronize(g->xs[i]);
+  }
   for (size_t i = 0; i < g->comms.size(); ++i) if (g->comms[i]) g->api.CommDestroy(g->comms[i]);
   for (size_t i = 0; i < g->d_mine.size(); ++i) {
     DeviceGuard guard(g->devs[i]);
+    if (i < g->xs.size() && g->xs[i]) cudaStreamDestroy(g->xs[i]);
+    if (i < g->ev_cnt.size() && g->ev_cnt[i]) cudaEventDestroy(g->ev_cnt[i]);
+    if (i < g->ev_xdone.size() && g->ev_xdone[i]) cudaEventDestroy(g->ev_xdone[i]);
     if (g->d_mine[i]) cudaFree(g->d_mine[i]);
     if (g->d_table[i]) cudaFree(g->d_table[i]);
     if (g->h_table[i]) cudaFreeHost(g->h_table[i]);
@@ -1284,6 +1314,11 @@ int32_t pj_group_size(const pj_group* g) { return g ? g->ndev : 0; }
 pj_ctx* pj_group_ctx(pj_group* g, int32_t i) { return g && i >= 0 && i < g->ndev ? g->ctx[i] : nullptr; }
 const char* pj_group_last_error(const pj_group* g) { return g ? g->err : g_create_error; }
 int32_t pj_group_uses_nccl(const pj_group* g) { return g && g->nccl ? 1 : 0; }
+pj_status pj_group_sync(pj_group* g) {
+  if (!g) return PJ_ERR_ARG;
+  for (int i = 0; i < g->ndev; ++i) if (group_wait_table(g, i) != PJ_OK) return group_err(g, PJ_ERR_CUDA, "pj_group_sync: shard %d", i);
+  return PJ_OK;
+}
 
 pj_status pj_group_parse(pj_group* g, uint32_t schema, uint8_t* const* in, const uint64_t* len, const uint64_t* room, uint64_t slack,
                          pj_columns* out, pj_group_shard* shards) {
@@ -1321,7 +1356,9 @@ pj_status pj_group_parse(pj_group* g, uint32_t schema, uint8_t* const* in, const
     if (S.status != PJ_OK && S.status != PJ_ERR_CAPACITY) {
       /* the table must still be exchanged by every shard (a collective): deliver zeros */
       cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream);
+      memset(c->h_res, 0, sizeof(DevResult));
     }
+    group_host_row(c->h_res[0], len[i] ? len[i] : ~0ull, g->h_table[0] + (size_t)i * PJ_GROUP_NCOUNT);
     if (cudaEventElapsedTime(&S.slack_copy_ms, c->ev[6], c->ev[7]) != cudaSuccess) { S.slack_copy_ms = 0.f; (void)cudaGetLastError(); }
     /* The exchange starts only when EVERY shard is through its parse: an all-gather kernel waits on its device for the
        other devices' kernels, and a cudaMalloc on one of those (a parse growing its scratch) waits for the first device
@@ -1333,7 +1370,7 @@ pj_status pj_group_parse(pj_group* g, uint32_t schema, uint8_t* const* in, const
     S.gather_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     if (S.status == PJ_OK) S.status = gs;
   });
-  pj_status st = group_spread(g);
+  pj_status st = PJ_OK;
   group_fill(g, shards, false);
   for (int i = 0; i < n; ++i) if (shards[i].bytes == ~0ull) shards[i].bytes = 0;
   for (int i = 0; i < n && st == PJ_OK; ++i) if (shards[i].status != PJ_OK) { st = shards[i].status; group_err(g, st, "shard %d: %s", i, pj_last_error(g->ctx[i])); }
@@ -1351,14 +1388,15 @@ pj_status pj_group_write(pj_group* g, uint32_t schema, const pj_columns* cols, u
     memset(&S, 0, sizeof S);
     uint64_t out_len = 0;
     S.status = pj_write(c, schema, PJ_FRAMING_NDJSON, &cols[i], out[i], cap[i], PJ_MEM_DEVICE, &out_len);
-    if (S.status != PJ_OK && S.status != PJ_ERR_CAPACITY) cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream);
+    if (S.status != PJ_OK && S.status != PJ_ERR_CAPACITY) { cudaMemsetAsync(c->d_res, 0, sizeof(DevResult), c->stream); memset(c->h_res, 0, sizeof(DevResult)); }
+    group_host_row(c->h_res[0], 0, g->h_table[0] + (size_t)i * PJ_GROUP_NCOUNT);
     g->rendezvous.meet((uint32_t)n); /* the exchange, once no shard allocates any more (see pj_group_parse) */
     const auto t0 = std::chrono::steady_clock::now();
     const pj_status gs = group_gather(g, i, 0, 0);
     S.gather_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     if (S.status == PJ_OK) S.status = gs;
   });
-  pj_status st = group_spread(g);
+  pj_status st = PJ_OK;
   group_fill(g, shards, true);
   for (int i = 0; i < n && st == PJ_OK; ++i) if (shards[i].status != PJ_OK) { st = shards[i].status; group_err(g, st, "shard %d: %s", i, pj_last_error(g->ctx[i])); }
   return st;

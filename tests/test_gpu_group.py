@@ -90,7 +90,8 @@ def test_group_parse_matches_the_checker_shard_by_shard(native, oracle, devices)
                 for t in (1, 2, 3):
                     rows0[t] += cols[g].n_rows(t)
                 starts.append(cols[g].get("rec_start"))
-                # the gathered table, as it lies on the shard's device
+                # the gathered table, as it lies on the shard's device (filled behind the call's back: wait for it)
+                grp.sync()
                 tab = read_device_u64(shards[g].table_dev, abi.PJ_GROUP_NCOUNT * n, devices[g]).reshape(n, abi.PJ_GROUP_NCOUNT)
                 for h in range(n):
                     assert int(tab[h, abi.PJ_GC_BYTES]) == bounds[h + 1] - bounds[h]
