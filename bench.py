@@ -48,7 +48,7 @@ SLACK = 64 * 1024
 FALLBACK_HBM_GBS = 6650.0  # an earlier measurement, used only when MEASURED_PEAKS.json is absent
 # dram__bytes_read.sum + dram__bytes_write.sum of the parse kernel per record, from one ncu capture per workload at
 # 500 000 records (traffic grows with the record count); None = no capture of that workload
-TRAFFIC_BYTES_PER_RECORD = {"pet": 417, "mixed": None, "zipf": None, "array1k": None}
+TRAFFIC_BYTES_PER_RECORD = {"pet": 413, "mixed": None, "zipf": None, "array1k": None}
 
 
 def measured_peak():

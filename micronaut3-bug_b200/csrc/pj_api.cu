@@ -655,6 +655,9 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   if (e == cudaSuccess) e = tile_init_3(&c->schema);
   if (e == cudaSuccess) e = tile_init_4(&c->schema);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(k_write_tile, cudaFuncAttributeMaxDynamicSharedMemorySize, WTILE_SMEM_BYTES);
+#ifdef PJ_WT_CARVEOUT
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(k_write_tile, cudaFuncAttributePreferredSharedMemoryCarveout, PJ_WT_CARVEOUT);
+#endif
   if (e != cudaSuccess) return fail_create(e, "cudaFuncSetAttribute");
   build_schema(&c->schema);
   e = cudaMemcpyToSymbol(c_schema, &c->schema, sizeof(Schema));
@@ -917,7 +920,7 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
   wa.out = d_out; wa.cap = cap; wa.res = c->d_res; wa.cols = dcols;
   {
     /* the single-pass tile writer; stages: [0] state reset and the look at the string arenas, [1] the closing kernel, [2] the tile kernel */
-    const uint64_t ntiles = n ? (n + TILE_THREADS - 1) / TILE_THREADS : 1;
+    const uint64_t ntiles = n ? (n + WT_THREADS - 1) / WT_THREADS : 1;
     { pj_status st = ensure(c, &c->tiles, 256 + ntiles * 16 + 256); if (st) return st; }
     WTileArgs ta;
     ta.w = wa;
@@ -949,7 +952,7 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
     stage.next();
     cudaEvent_t ev_tile0 = c->ev[8], ev_tile1 = c->ev[9];
     PJ_CUDA(c, cudaEventRecord(ev_tile0, c->stream));
-    k_write_tile<<<(unsigned)ntiles, TILE_THREADS, WTILE_SMEM_BYTES, c->stream>>>(ta);
+    k_write_tile<<<(unsigned)ntiles, WT_THREADS, WTILE_SMEM_BYTES, c->stream>>>(ta);
     PJ_CUDA(c, cudaEventRecord(ev_tile1, c->stream));
     k_write_close<<<1, 32, 0, c->stream>>>(wa);
     count_launch(c, 2); count_launch(c, 1);
@@ -968,7 +971,7 @@ pj_status pj_write(pj_ctx* c, uint32_t schema, uint32_t framing, const pj_column
     c->stats.main_kernel_ms = c->stats.stage_ms[2];
   }
   for (int k = 0; k < 4; ++k) c->stats.phase_cycles[k] = c->h_res->phase_cycles[k];
-  c->stats.tiles = (uint32_t)(n ? (n + TILE_THREADS - 1) / TILE_THREADS : 1);
+  c->stats.tiles = (uint32_t)(n ? (n + WT_THREADS - 1) / WT_THREADS : 1);
   if (c->h_res->timeout) return set_err(c, PJ_ERR_TIMEOUT, "pj_write: a bounded device-side wait ran out");
   *out_len = c->h_res->out_bytes;
   c->stats.algorithmic_bytes = col_bytes + *out_len;

@@ -683,7 +683,18 @@ __global__ void __launch_bounds__(TILE_THREADS, SCHEMA == PJ_SCHEMA_MIXED ? 3 : 
  * copies the window to the output with 16-byte stores. A tile whose text does not fit the window is
  * written to global memory directly. Text is produced once and written to HBM once.
  * ================================================================================================ */
-static constexpr uint32_t WTILE_WIN_BYTES = 40 * 1024;
+#ifndef PJ_WT_THREADS
+#define PJ_WT_THREADS 128 /* records (= threads) per writer tile */
+#endif
+#ifndef PJ_WT_WIN_KB
+#define PJ_WT_WIN_KB 40 /* text window per tile in shared memory */
+#endif
+#ifndef PJ_WT_BLOCKS
+#define PJ_WT_BLOCKS 5 /* resident blocks per SM the kernel is compiled for */
+#endif
+static constexpr uint32_t WT_THREADS = PJ_WT_THREADS;
+static_assert(WT_THREADS % 32 == 0 && WT_THREADS >= 96, "the copy-out of the window's odd ends uses threads 32.. and 64..");
+static constexpr uint32_t WTILE_WIN_BYTES = PJ_WT_WIN_KB * 1024;
 static constexpr uint32_t WTILE_SMEM_BYTES = WTILE_WIN_BYTES + 32;
 
 struct WTileArgs {
@@ -781,8 +792,8 @@ __device__ __forceinline__ void prefetch_row(const DevCols* c, uint64_t row) {
   }
 }
 
-static __global__ void __launch_bounds__(TILE_THREADS, 5) k_write_tile(const __grid_constant__ WTileArgs a) {
-  constexpr uint32_t NWARPS = TILE_THREADS / 32;
+static __global__ void __launch_bounds__(WT_THREADS, PJ_WT_BLOCKS) k_write_tile(const __grid_constant__ WTileArgs a) {
+  constexpr uint32_t NWARPS = WT_THREADS / 32;
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ uint32_t sh_warp[NWARPS];
   __shared__ uint32_t sh_tile, sh_ok;
@@ -792,7 +803,7 @@ static __global__ void __launch_bounds__(TILE_THREADS, 5) k_write_tile(const __g
   __syncthreads();
   const uint32_t tile = sh_tile;
   if (tile >= a.ntiles) return;
-  const uint64_t i = (uint64_t)tile * TILE_THREADS + tid;
+  const uint64_t i = (uint64_t)tile * WT_THREADS + tid;
   uint32_t type = PJ_TYPE_NONE;
   uint64_t row = 0;
   const bool plain = !a.w.res->needs_escape; /* no string of the columns holds a byte to escape */
@@ -859,7 +870,7 @@ static __global__ void __launch_bounds__(TILE_THREADS, 5) k_write_tile(const __g
       if (tid >= 32 && tid < 32 + (lo16 - pad)) gbase[pad + tid - 32] = smem[pad + tid - 32];
       if (tid >= 64 && tid < 64 + (end - hi16)) gbase[hi16 + tid - 64] = smem[hi16 + tid - 64];
     } else {
-      for (uint32_t b = pad + tid; b < end; b += TILE_THREADS) gbase[b] = smem[b];
+      for (uint32_t b = pad + tid; b < end; b += WT_THREADS) gbase[b] = smem[b];
     }
   } else if (located) {
     WOut w; w.dst = dst0 + loc; w.n = 0; w.hexa = a.w.hexa;
