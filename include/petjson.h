@@ -466,6 +466,14 @@ pj_status pj_group_sync(pj_group* grp);
 pj_status pj_group_parse(pj_group* grp, uint32_t schema, uint8_t* const* in, const uint64_t* len, const uint64_t* room,
                          uint64_t slack, pj_columns* out, pj_group_shard* shards);
 
+/* The same for a stream that lies in HOST memory (io.micronaut.serde.ObjectMapper.readValue(byte[], ...) of a large
+ * body, MyEntityConfig.java:34): `text` holds all shards back to back, shard i is len[i] bytes, and the bytes behind a
+ * shard are its slack. Every shard's thread runs the host-buffer route of pj_parse on its device (pieces whose copies
+ * overlap the kernels of the pieces before them; pinned memory makes the overlap real), all devices side by side.
+ * out[i] may be host or device columns. */
+pj_status pj_group_parse_host(pj_group* grp, uint32_t schema, const uint8_t* text, const uint64_t* len, uint64_t slack, pj_columns* out,
+                              pj_group_shard* shards);
+
 /* Replaces ObjectMapper#writeValueAsBytes (MyEntityController.java:48-51) for tables spread over the group's GPUs:
  * device g serialises cols[g] (as pj_write, NDJSON framing) into out[g] (cap[g] bytes, device g's memory). The
  * text of the whole is the concatenation of the outputs in shard order; shards[g].global_offset says where shard

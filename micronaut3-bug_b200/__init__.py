@@ -68,6 +68,8 @@ def lib() -> C.CDLL:
         L.pj_group_last_error.restype = C.c_char_p
         L.pj_group_uses_nccl.argtypes = [C.c_void_p]
         L.pj_group_sync.argtypes = [C.c_void_p]
+        L.pj_group_parse_host.argtypes = [C.c_void_p, u32, C.c_void_p, C.POINTER(u64), u64, C.POINTER(abi.pj_columns), C.POINTER(abi.pj_group_shard)]
+        L.pj_group_parse_host.restype = C.c_int
         L.pj_group_sync.restype = C.c_int
         L.pj_group_parse.argtypes = [C.c_void_p, u32, C.POINTER(C.c_void_p), C.POINTER(u64), C.POINTER(u64), u64, C.POINTER(abi.pj_columns),
                                      C.POINTER(abi.pj_group_shard)]
@@ -311,7 +313,7 @@ class Group:
     the library. `devices` may repeat a device (several shards on one GPU; the counter table then goes through the
     host instead of NCCL)."""
 
-    def __init__(self, devices, inclusion: int = abi.PJ_INCLUDE_NON_EMPTY, tile_bytes: int = 0, spin_limit_us: int = 0):
+    def __init__(self, devices, inclusion: int = abi.PJ_INCLUDE_NON_EMPTY, tile_bytes: int = 0, spin_limit_us: int = 0, host_piece_bytes: int = 0):
         self.devices = [int(d) for d in devices]
         self._h = C.c_void_p()
         opt = abi.pj_options()
@@ -319,6 +321,7 @@ class Group:
         opt.inclusion = inclusion
         opt.tile_bytes = tile_bytes
         opt.spin_limit_us = spin_limit_us
+        opt.host_piece_bytes = host_piece_bytes
         devs = (i32 * len(self.devices))(*self.devices)
         st = lib().pj_group_create(len(self.devices), devs, C.byref(opt), C.byref(self._h))
         if st != abi.PJ_OK:
@@ -398,6 +401,22 @@ class Group:
         if st != abi.PJ_OK and not (allow_capacity and st == abi.PJ_ERR_CAPACITY):
             raise PetJsonError(st, "pj_group_parse", (lib().pj_group_last_error(self._h) or b"").decode())
         return prep["shards"]
+
+    def parse_host(self, schema: int, text, lengths, cols, slack: int = 65536, allow_capacity: bool = False):
+        """pj_group_parse_host: `text` is one uint8 numpy array in host memory (pinned for full speed) holding all shards
+        back to back, lengths[g] the bytes of shard g, cols[g] HostColumns or DeviceColumns. Returns the shard table."""
+        n = len(self.devices)
+        text = np.ascontiguousarray(text, dtype=np.uint8)
+        assert int(sum(lengths)) <= text.size
+        lens = (u64 * n)(*[int(x) for x in lengths])
+        arr = self._cols_array(cols)
+        shards = (abi.pj_group_shard * n)()
+        st = lib().pj_group_parse_host(self._h, schema, C.c_void_p(text.ctypes.data), lens, slack, arr, shards)
+        for k, c in enumerate(cols):
+            C.memmove(C.byref(c.raw), C.byref(arr[k]), C.sizeof(abi.pj_columns))
+        if st != abi.PJ_OK and not (allow_capacity and st == abi.PJ_ERR_CAPACITY):
+            raise PetJsonError(st, "pj_group_parse_host", (lib().pj_group_last_error(self._h) or b"").decode())
+        return list(shards)
 
     def write(self, schema: int, cols, outs, allow_capacity: bool = False):
         """cols[g]: DeviceColumns on device g; outs[g]: a uint8 CUDA tensor on device g. Returns the list of pj_group_shard

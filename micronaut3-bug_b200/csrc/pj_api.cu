@@ -1189,9 +1189,9 @@ void group_host_row(const DevResult& res, uint64_t bytes, unsigned long long* ro
  * takes longer than a tenth of a parse step, and the next step's kernels have no reason to queue behind it. (When
  * the device list repeats a device the host table is uploaded instead.) Called on the shard's thread, its device
  * current. */
-pj_status group_gather(pj_group* g, int i, int res_index, uint64_t bytes) {
+pj_status group_gather(pj_group* g, int i, int res_index, uint64_t bytes, bool from_host = false) {
   pj_ctx* c = g->ctx[i];
-  if (g->nccl) {
+  if (g->nccl && !from_host) {
     if (cudaStreamWaitEvent(c->stream, g->ev_xdone[i], 0) != cudaSuccess) return PJ_ERR_CUDA; /* the exchange before this one has read d_mine */
     k_group_counters<<<1, 32, 0, c->stream>>>(c->d_res + res_index, bytes, g->d_mine[i]);
     if (cudaGetLastError() != cudaSuccess) return PJ_ERR_CUDA;
@@ -1200,7 +1200,7 @@ pj_status group_gather(pj_group* g, int i, int res_index, uint64_t bytes) {
     if (r != 0) return set_err(c, PJ_ERR_NCCL, "ncclAllGather: %s", g->api.GetErrorString(r));
     if (cudaEventRecord(g->ev_xdone[i], g->xs[i]) != cudaSuccess) return PJ_ERR_CUDA;
   } else {
-    cudaStreamSynchronize(g->xs[i]); /* the upload before this one has read h_table[i] */
+    cudaStreamSynchronize(g->xs[i]); /* the upload (or all-gather) before this one is through with the tables */
     if (i) memcpy(g->h_table[i], g->h_table[0], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev);
     if (cudaMemcpyAsync(g->d_table[i], g->h_table[i], sizeof(unsigned long long) * PJ_GROUP_NCOUNT * g->ndev, cudaMemcpyHostToDevice, g->xs[i]) != cudaSuccess) return PJ_ERR_CUDA;
   }
@@ -1370,6 +1370,46 @@ pj_status pj_group_parse(pj_group* g, uint32_t schema, uint8_t* const* in, const
     g->rendezvous.meet((uint32_t)n);
     const auto t0 = std::chrono::steady_clock::now();
     const pj_status gs = group_gather(g, i, 0, len[i] ? len[i] : ~0ull);
+    S.gather_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    if (S.status == PJ_OK) S.status = gs;
+  });
+  pj_status st = PJ_OK;
+  group_fill(g, shards, false);
+  for (int i = 0; i < n; ++i) if (shards[i].bytes == ~0ull) shards[i].bytes = 0;
+  for (int i = 0; i < n && st == PJ_OK; ++i) if (shards[i].status != PJ_OK) { st = shards[i].status; group_err(g, st, "shard %d: %s", i, pj_last_error(g->ctx[i])); }
+  return st;
+}
+
+pj_status pj_group_parse_host(pj_group* g, uint32_t schema, const uint8_t* text, const uint64_t* len, uint64_t slack, pj_columns* out,
+                              pj_group_shard* shards) {
+  if (!g) return PJ_ERR_ARG;
+  if (!len || !out || !shards || schema < PJ_SCHEMA_PET || schema > PJ_SCHEMA_MIXED) return group_err(g, PJ_ERR_ARG, "pj_group_parse_host: bad argument");
+  const int n = g->ndev;
+  std::vector<uint64_t> goff(n + 1, 0);
+  for (int i = 0; i < n; ++i) goff[i + 1] = goff[i] + len[i];
+  if (!text && goff[n]) return group_err(g, PJ_ERR_ARG, "pj_group_parse_host: no text");
+  group_run(g, [&](int i) {
+    DeviceGuard guard(g->devs[i]);
+    pj_ctx* c = g->ctx[i];
+    pj_group_shard& S = shards[i];
+    memset(&S, 0, sizeof S);
+    S.global_offset = goff[i];
+    /* the bytes behind a shard ARE its slack: the shards are ranges of one buffer */
+    const uint64_t behind = goff[n] - goff[i + 1];
+    const uint64_t got = slack < behind ? slack : behind;
+    S.slack_bytes = got;
+    S.status = parse_impl(c, schema, PJ_FRAMING_NDJSON, text + goff[i], len[i], got, goff[i] == 0, got == behind, goff[i], PJ_MEM_HOST, &out[i]);
+    unsigned long long* row = g->h_table[0] + (size_t)i * PJ_GROUP_NCOUNT;
+    memset(row, 0, sizeof(unsigned long long) * PJ_GROUP_NCOUNT);
+    if (S.status == PJ_OK || S.status == PJ_ERR_CAPACITY) {
+      /* a call in pieces leaves its totals in the result block of the last piece; errors were added up on the host */
+      const uint32_t last = c->stats.pieces ? c->stats.pieces - 1 : 0;
+      group_host_row(c->h_res[last < 16 ? last : 15], len[i] ? len[i] : ~0ull, row);
+      row[PJ_GC_ERRORS] = out[i].n_errors;
+    }
+    g->rendezvous.meet((uint32_t)n);
+    const auto t0 = std::chrono::steady_clock::now();
+    const pj_status gs = group_gather(g, i, 0, 0, true); /* the device tables from the host table: the result blocks hold per-piece figures */
     S.gather_ms = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     if (S.status == PJ_OK) S.status = gs;
   });

@@ -100,6 +100,40 @@ def test_group_parse_matches_the_checker_shard_by_shard(native, oracle, devices)
             assert rec0 == whole.n_records
 
 
+@pytest.mark.parametrize("devices", device_sets(), ids=lambda d: "dev" + "".join(map(str, d)))
+@pytest.mark.parametrize("piece", [0, 5000])
+def test_group_parse_of_a_host_stream(native, oracle, devices, piece):
+    """pj_group_parse_host: the shards are ranges of one host buffer; every shard goes through the host-buffer route
+    (in pieces when `piece` is set), host columns out."""
+    rng = random.Random(3 + len(devices))
+    schema = 4
+    text = pj.gen_text(schema, 12, 0, 5000, abi.PJ_GEN_MALFORMED | abi.PJ_GEN_WHITESPACE)
+    whole = oracle.parse(schema, text)
+    n = len(devices)
+    with native.Group(devices, host_piece_bytes=piece) as grp:
+        for trial in range(2):
+            cuts = sorted(rng.sample(range(1, text.size), n - 1)) if trial else [text.size * k // n for k in range(1, n)]
+            bounds = [0] + cuts + [text.size]
+            cols = [abi.HostColumns(schema, abi.default_caps(schema, nrec_bound(text[bounds[g]:bounds[g + 1]]) + 4, bounds[g + 1] - bounds[g] + 65536)) for g in range(n)]
+            shards = grp.parse_host(schema, text, [bounds[g + 1] - bounds[g] for g in range(n)], cols)
+            starts, rec0 = [], 0
+            for g in range(n):
+                lo, hi = bounds[g], bounds[g + 1]
+                slack = int(shards[g].slack_bytes)
+                assert slack == min(65536, text.size - hi)
+                want = oracle.parse(schema, text[lo:hi + slack], slack=slack, is_first=lo == 0, is_last=hi + slack == text.size, goff=lo)
+                assert same_result(want, cols[g]) == "", (trial, g)
+                assert (int(shards[g].global_offset), int(shards[g].first_record), int(shards[g].bytes)) == (lo, rec0, hi - lo)
+                rec0 += cols[g].n_records
+                starts.append(cols[g].get("rec_start"))
+            grp.sync()
+            tab = read_device_u64(shards[0].table_dev, abi.PJ_GROUP_NCOUNT * n, devices[0]).reshape(n, abi.PJ_GROUP_NCOUNT)
+            for h in range(n):
+                assert int(tab[h, abi.PJ_GC_RECORDS]) == cols[h].n_records and int(tab[h, abi.PJ_GC_ERRORS]) == cols[h].n_errors
+            assert np.array_equal(np.concatenate(starts), whole.get("rec_start")), trial
+            assert rec0 == whole.n_records
+
+
 @pytest.mark.parametrize("devices", device_sets()[:1] + device_sets()[2:3], ids=lambda d: "dev" + "".join(map(str, d)))
 def test_group_write_concatenates_to_the_checkers_text(native, oracle, devices):
     import torch
