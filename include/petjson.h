@@ -121,7 +121,8 @@ enum {
   PJ_ERR_CUDA = 3,      /* a CUDA call failed (text via pj_last_error)                         */
   PJ_ERR_TIMEOUT = 4,   /* a bounded device-side wait ran out; the context stays usable        */
   PJ_ERR_NOMEM = 5,     /* host or device allocation failed                                    */
-  PJ_ERR_TOO_LARGE = 6, /* input (plus slack) or output does not fit 32-bit offsets (>= 4 GiB) */
+  PJ_ERR_TOO_LARGE = 6, /* the input is larger than one call takes: 4 GiB (32-bit offsets), or 32 GiB for NDJSON in
+                           device memory, which is parsed in ranges (pj_options.device_piece_bytes)        */
   PJ_ERR_NCCL = 7       /* pj_group_*: an NCCL call failed or the library could not be loaded    */
 };
 
@@ -277,6 +278,13 @@ typedef struct pj_options {
   uint32_t spin_limit_us;    /* bound, in microseconds, of every wait of a thread block on another one or on
                                 its staging copy; when one runs out the call answers PJ_ERR_TIMEOUT and the
                                 context stays usable. 0 = 2 seconds.                               */
+  uint32_t device_piece_bytes; /* pj_parse* with NDJSON that lies on the device: the input is parsed as byte ranges
+                                of this many bytes (at most 16 of them, at most 2 GiB each), one launch per range,
+                                each starting from the totals the one before it left on the device. 0 = only
+                                inputs of 4 GiB and more are cut (into ranges of 2 GiB): that is what lets one
+                                call take up to 32 GiB although a launch addresses its bytes with 32-bit offsets.
+                                The result does not depend on it.                                   */
+  uint32_t reserved;
 } pj_options;
 
 typedef struct pj_ctx pj_ctx;
@@ -343,7 +351,9 @@ pj_status pj_columns_sizes(uint32_t schema, uint64_t max_records, uint64_t max_i
  * buffers (all in out->mem_kind memory). Columns of other schemas are ignored; a column of this
  * schema with ptr == NULL is PJ_ERR_ARG. When the record count itself exceeds the per-record
  * buffers, only n_records and the per-record counts are exact in the PJ_ERR_CAPACITY answer.
- * len must be < 4 GiB. */
+ * len must be < 4 GiB; NDJSON in device memory may be up to 32 GiB (it is parsed in ranges of 2 GiB, see
+ * pj_options.device_piece_bytes) as long as every arena and child table of the result stays below 2^32 entries
+ * (PJ_ERR_CAPACITY otherwise). */
 pj_status pj_parse(pj_ctx* ctx, uint32_t schema, uint32_t framing, const uint8_t* in,
                    uint64_t len, uint32_t in_kind, pj_columns* out);
 
@@ -354,7 +364,7 @@ pj_status pj_parse(pj_ctx* ctx, uint32_t schema, uint32_t framing, const uint8_t
  * predecessor, which reads them from its slack. `is_last` tells that the stream ends at
  * len + slack. `global_offset` is added to PJ_COL_REC_START. A record whose end is not reached
  * within the slack fails with PJ_E_TOO_LONG at the number of bytes that were available.
- * len + slack must be < 4 GiB. */
+ * len + slack must be < 4 GiB (device memory: 32 GiB, as for pj_parse). */
 pj_status pj_parse_shard(pj_ctx* ctx, uint32_t schema, const uint8_t* in, uint64_t len,
                          uint64_t slack, int32_t is_first, int32_t is_last, uint64_t global_offset,
                          uint32_t in_kind, pj_columns* out);

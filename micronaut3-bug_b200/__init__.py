@@ -201,7 +201,7 @@ class Context:
     """One pj_ctx: a (device, stream) pair with its scratch memory. Not for concurrent use."""
 
     def __init__(self, device: int = -1, inclusion: int = abi.PJ_INCLUDE_NON_EMPTY, stream: int | None = None, flags: int = 0,
-                 host_piece_bytes: int = 0, tile_bytes: int = 0, spin_limit_us: int = 0):
+                 host_piece_bytes: int = 0, tile_bytes: int = 0, spin_limit_us: int = 0, device_piece_bytes: int = 0):
         self._h = C.c_void_p()
         opt = abi.pj_options()
         opt.device = device
@@ -211,6 +211,7 @@ class Context:
         opt.host_piece_bytes = host_piece_bytes
         opt.tile_bytes = tile_bytes
         opt.spin_limit_us = spin_limit_us
+        opt.device_piece_bytes = device_piece_bytes
         st = lib().pj_create(C.byref(opt), C.byref(self._h))
         if st != abi.PJ_OK:
             raise PetJsonError(st, "pj_create", (lib().pj_last_error(None) or b"").decode())

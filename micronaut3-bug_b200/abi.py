@@ -123,7 +123,8 @@ class pj_columns(C.Structure):
 
 class pj_options(C.Structure):
     _fields_ = [("device", C.c_int32), ("inclusion", C.c_int32), ("stream", C.c_void_p),
-                ("flags", C.c_uint32), ("host_piece_bytes", C.c_uint32), ("tile_bytes", C.c_uint32), ("spin_limit_us", C.c_uint32)]
+                ("flags", C.c_uint32), ("host_piece_bytes", C.c_uint32), ("tile_bytes", C.c_uint32), ("spin_limit_us", C.c_uint32),
+                ("device_piece_bytes", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 PJ_GROUP_NCOUNT = 24

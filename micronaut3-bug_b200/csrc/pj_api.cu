@@ -115,6 +115,7 @@ struct pj_ctx {
   cudaStream_t s_in = nullptr, s_out = nullptr;
   cudaEvent_t ev_in[16] = {};
   uint32_t piece_bytes = 0;
+  uint64_t dev_piece_bytes = 0; /* pj_options.device_piece_bytes */
   uint32_t opt_flags = 0;
   bool stall_once = false; /* PJ_OPT_TEST_STALL_ONCE, not yet used up */
   Schema schema;
@@ -239,6 +240,7 @@ pj_status plan_columns(pj_ctx* c, uint32_t schema, pj_columns* out, uint64_t lim
     else if (room < pp->slot_cap[it.rows_slot]) pp->slot_cap[it.rows_slot] = room;
   }
   if (cap_all > (1ull << 32)) cap_all = 1ull << 32;
+  for (uint32_t k = 0; k < NSLOT; ++k) if (pp->slot_cap[k] > 0xFFFFFFFFull) pp->slot_cap[k] = 0xFFFFFFFFull; /* offsets into arenas and child tables are 32-bit */
   /* no more records than candidate line starts (NDJSON: a record needs a byte and an LF) or separators (array) */
   if (!array && cap_all > limit / 2 + 2) cap_all = limit / 2 + 2;
   if (array && cap_all > limit + 2) cap_all = limit + 2;
@@ -321,7 +323,23 @@ pj_status parse_stream(pj_ctx* c, uint32_t schema, const uint8_t* in, uint64_t l
     }
     cut[++np] = len;
   }
-  const bool pipe = np > 1;
+  /* Input that lies on the device and is too long for 32-bit offsets (or whenever pj_options.device_piece_bytes asks
+     for it) is parsed as byte ranges of at most 2 GiB, each with the bytes behind it as its slack: the rule that gives
+     the lines of a stream to shards gives them to these ranges, and every launch starts from the totals the one before
+     it left on the device. */
+  bool ranges = false;
+  if (!host_in && len && (limit >= (1ull << 32) || c->dev_piece_bytes)) {
+    uint64_t piece = c->dev_piece_bytes ? c->dev_piece_bytes : (1ull << 31);
+    if (piece < 64) piece = 64;
+    if (piece > (1ull << 31)) piece = 1ull << 31;
+    const uint64_t want = (len + piece - 1) / piece;
+    if (want > MAX_PIECES) return set_err(c, PJ_ERR_TOO_LARGE, "pj_parse: %llu input bytes are more than %d ranges of %llu bytes", (unsigned long long)len, (int)MAX_PIECES, (unsigned long long)piece);
+    np = (int)want;
+    for (int k = 1; k < np; ++k) cut[k] = (uint64_t)k * piece;
+    cut[np] = len;
+    ranges = true;
+  }
+  const bool pipe = np > 1 && !ranges;
   if (pipe) { pj_status st = ensure_pipe_streams(c); if (st) return st; }
   cudaStream_t s_in = pipe ? c->s_in : c->stream, s_out = pipe ? c->s_out : c->stream;
   /* whatever goes wrong from here on, no copy may still be running when the call returns */
@@ -370,6 +388,14 @@ pj_status parse_stream(pj_ctx* c, uint32_t schema, const uint8_t* in, uint64_t l
     sa.in = d_in ? d_in + cut[p] : d_in;
     sa.len = plen; sa.limit = plen + (p == np - 1 ? slack : 0); sa.goff = goff + cut[p];
     sa.is_first = (uint32_t)is_first; sa.is_last = (uint32_t)is_last;
+    if (ranges) {
+      const uint64_t rest = len - cut[p + 1] + slack; /* readable bytes behind the range */
+      const uint64_t room = 0xFFFFFFF0ull - plen;
+      const uint64_t sl = rest < room ? rest : room;
+      sa.limit = plen + sl;
+      sa.is_first = p == 0 ? (uint32_t)is_first : 0u;
+      sa.is_last = (is_last && sl == rest) ? 1u : 0u;
+    }
     sa.tile_bytes = tile_bytes; sa.ntiles = (uint32_t)nt[p];
     sa.spin_limit_ns = c->spin_ns;
     sa.opts = c->opt_flags;
@@ -572,7 +598,9 @@ pj_status parse_impl(pj_ctx* c, uint32_t schema, uint32_t framing, const uint8_t
   const bool array = framing == PJ_FRAMING_ARRAY;
   if (array && (slack || !is_first || !is_last)) return set_err(c, PJ_ERR_ARG, "pj_parse: array framing cannot be sharded");
   const uint64_t limit = len + slack;
-  if (limit >= (1ull << 32)) return set_err(c, PJ_ERR_TOO_LARGE, "pj_parse: %llu input bytes do not fit 32-bit offsets", (unsigned long long)limit);
+  /* one launch addresses its input with 32-bit offsets; NDJSON that lies on the device is cut into ranges (parse_stream) */
+  if (limit >= (1ull << 32) && (array || in_kind != PJ_MEM_DEVICE))
+    return set_err(c, PJ_ERR_TOO_LARGE, "pj_parse: %llu input bytes do not fit 32-bit offsets", (unsigned long long)limit);
   DeviceGuard guard(c->device);
   c->stats = pj_call_stats{};
   return array ? parse_array(c, schema, in, len, in_kind, out) : parse_stream(c, schema, in, len, slack, is_first, is_last, goff, in_kind, out);
@@ -627,6 +655,7 @@ pj_status pj_create(const pj_options* opt, pj_ctx** out) {
   c->opt_flags = opt ? opt->flags : 0;
   c->stall_once = (c->opt_flags & PJ_OPT_TEST_STALL_ONCE) != 0;
   c->piece_bytes = opt ? opt->host_piece_bytes : 0;
+  c->dev_piece_bytes = opt ? opt->device_piece_bytes : 0;
   c->tile_bytes_opt = opt ? opt->tile_bytes : 0;
   if (opt && opt->spin_limit_us) c->spin_ns = (unsigned long long)opt->spin_limit_us * 1000ull;
   DeviceGuard guard(dev);

@@ -510,3 +510,29 @@ def test_cpp_object_mapper_mirror(native):
     exe = importlib.import_module("micronaut3-bug_b200.build").build_facade_demo()
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("schema", [1, 4])
+@pytest.mark.parametrize("piece", [64, 1000, 4096, 100000])
+def test_device_input_parsed_in_ranges(native, oracle, schema, piece):
+    """pj_options.device_piece_bytes: device-resident NDJSON cut into byte ranges (what a call of 4 GiB and more does
+    with ranges of 2 GiB): records that start in one range and end in the next, ranges that hold no line start at
+    all, errors at the seams."""
+    text = pj.gen_text(schema, 21, 0, 3000, abi.PJ_GEN_MALFORMED | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE)
+    if piece * 16 < text.size:
+        text = text[: int(np.nonzero(text[: piece * 16] == 10)[0][-1]) + 1]  # at most 16 ranges
+    want = oracle.parse(schema, text)
+    with native.Context(device_piece_bytes=piece) as ctx:
+        assert same_result(want, gpu_parse_device(ctx, schema, text)) == ""
+        assert ctx.stats().pieces == -(-text.size // piece)
+        # a shard of the same bytes: slack behind the last range, a first range that does not own the line at byte 0
+        cut = text.size // 2
+        lo, hi = cut, text.size - 300
+        shard = oracle.parse(schema, text[lo:], slack=text.size - hi, is_first=False, is_last=True, goff=lo)
+        import torch
+
+        t = torch.from_numpy(text[lo:].copy()).cuda()
+        out = pj.DeviceColumns(schema, abi.default_caps(schema, nrec_bound(text[lo:]), text.size - lo), "cuda")
+        if (hi - lo) <= piece * 16:
+            ctx.parse_shard(schema, t, hi - lo, text.size - hi, False, True, lo, out)
+            assert same_result(shard, out) == ""

@@ -86,3 +86,50 @@ def test_ten_million_pets_written_back_byte_for_byte(native, oracle):
     m = ctx.write(abi.PJ_SCHEMA_PET, cols, d_out)
     assert m == text.size and torch.equal(d_out[:m], d_text)
     ctx.close()
+
+
+def test_more_than_four_gib_in_one_call(native, oracle):
+    """One pj_parse call on 4.3 GB of device-resident NDJSON (a launch addresses its input with 32-bit offsets: the call
+    cuts the input into ranges of 2 GiB, each launch starting from the totals of the one before it). Compared, column
+    by column, with the values the generator knows the text to hold."""
+    import torch
+    from concurrent.futures import ThreadPoolExecutor
+
+    n, parts = 14_700_000, 12
+    per = n // parts
+    with ThreadPoolExecutor(max_workers=parts) as pool:  # the generator is plain C behind ctypes: the threads run side by side
+        texts = list(pool.map(lambda k: pj.gen_text(abi.PJ_SCHEMA_PET, 0xC5, k * per, per, 0), range(parts)))
+        sizes = [t.size for t in texts]
+        wants = list(pool.map(lambda k: pj.gen_columns(abi.PJ_SCHEMA_PET, 0xC5, k * per, per, 0, sizes[k]), range(parts)))
+    total = sum(sizes)
+    assert total >= 1 << 32
+    d_text = torch.empty(total + 64, dtype=torch.uint8, device="cuda")
+    at = 0
+    for t in texts:
+        d_text[at: at + t.size].copy_(torch.from_numpy(t))
+        at += t.size
+    del texts
+    cols = pj.DeviceColumns(abi.PJ_SCHEMA_PET, caps_for(abi.PJ_SCHEMA_PET, n, total, 3 * n, arena_share=0.34), "cuda")
+    torch.cuda.synchronize()
+    with native.Context(device=0) as ctx:
+        ctx.parse(abi.PJ_SCHEMA_PET, d_text[:total], cols)
+        assert ctx.stats().pieces == 3
+        assert (cols.n_records, cols.n_errors) == (n, 0)
+        # record starts: the generator's parts are record ranges, so their first offsets are the running sizes
+        starts = cols.get("rec_start")
+        assert starts.dtype == np.uint64 and int(starts[-1]) > 1 << 32 and bool(np.all(np.diff(starts.astype(np.int64)) > 0))
+        first = np.cumsum([0] + sizes[:-1])
+        assert np.array_equal(starts[::per][:parts], first.astype(np.uint64))
+        # fixed-width columns part by part against the generator's values
+        ids = cols.get("pet_id")
+        for k, w in enumerate(wants):
+            assert np.array_equal(ids[k * per:(k + 1) * per], w.get("pet_id")), k
+            assert np.array_equal(starts[k * per:(k + 1) * per] - np.uint64(first[k]), w.get("rec_start")), k
+        # arenas: total sizes, and the bytes of the parts that straddle the 2 GiB seams
+        names = cols.get("pet_name_data")
+        assert names.size == sum(w.count(abi.COL_BY_NAME["pet_name_data"].id) for w in wants)
+        off = 0
+        for k, w in enumerate(wants):
+            m = w.count(abi.COL_BY_NAME["pet_name_data"].id)
+            assert np.array_equal(names[off: off + m], w.get("pet_name_data")), k
+            off += m
