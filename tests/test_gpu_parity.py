@@ -536,3 +536,27 @@ def test_device_input_parsed_in_ranges(native, oracle, schema, piece):
         if (hi - lo) <= piece * 16:
             ctx.parse_shard(schema, t, hi - lo, text.size - hi, False, True, lo, out)
             assert same_result(shard, out) == ""
+
+
+def test_mixed_stream_records_filed_under_the_wrong_model(ctx, oracle):
+    """The stream kernel hands the lines of a mixed tile to its threads grouped by the model their first keys suggest.
+    Records whose first keys suggest one model and whose later keys make them another (unknown keys that look like
+    known ones, `status` first, blanks in front of the keys) must come out as in line order all the same."""
+    base = bytes(pj.gen_text(4, 31, 0, 6000, abi.PJ_GEN_MALFORMED)).split(b"\n")[:-1]
+    traps = [b'{"id":7,"cat":1,"quantity":2,"petId":3}',            # looks like a Pet (category), is an Order
+             b'{"id":8,"usable":true,"name":"rex","photoUrls":[]}',  # looks like a User, is a Pet
+             b'{"id":9,"quality":"x","username":"u","email":"e@x"}',  # looks like an Order, is a User
+             b'{"status":"sold","id":1,"name":"a","photoUrls":["p"]}',  # decides nothing at first
+             b'{ "id":10, "petId":4, "quantity":1 }',                  # blanks: no guess
+             b'{"id":11,"cat":1}']                                     # looks like a Pet, is nothing: ambiguous
+    rng = random.Random(5)
+    for every in (9, 53, 400):
+        lines = []
+        for k, ln in enumerate(base):
+            lines.append(ln)
+            if k % every == every - 1:
+                lines.append(rng.choice(traps))
+        text = as_u8(b"\n".join(lines) + b"\n")
+        want = oracle.parse(4, text)
+        assert same_result(want, gpu_parse_device(ctx, 4, text)) == "", every
+        assert same_result(want, gpu_parse_host(ctx, 4, text)) == "", every
