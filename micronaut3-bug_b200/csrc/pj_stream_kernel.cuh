@@ -757,8 +757,14 @@ __global__ void __launch_bounds__(ST_THREADS, 512 / ST_THREADS) k_parse_stream(c
       }
     }
   }
-  if (__syncthreads_or(stage_failed)) { /* the block leaves together; the copy may still be in flight: the results of the call are void */
-    if (tid == 0) atomicExch(&a.res->timeout, 1u);
+  if (__syncthreads_or(stage_failed)) { /* the block gives up together: the results of the call are void */
+    if (tid == 0) {
+      atomicExch(&a.res->timeout, 1u);
+      /* the copy may still be in flight, and the block's shared memory must not pass to another block before it has
+         landed: one thread stays and waits for it, again with a limit */
+      const unsigned long long t1 = global_ns();
+      while (!mbar_try_wait(&sh_mbar, 0) && global_ns() - t1 <= a.spin_limit_ns) __nanosleep(256);
+    }
     return;
   }
   if (tid < ST_WIN_PAD) win[g.hi_valid + tid] = '\n';
