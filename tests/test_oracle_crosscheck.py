@@ -80,8 +80,30 @@ KNOWN = {1: {"id", "category", "name", "photoUrls", "tags", "status"},
          3: {"id", "username", "firstName", "lastName", "email", "password", "phone", "userStatus"}}
 
 
+def test_long_lists_decode_like_python_json(oracle, native):
+    """The checker on the records the warp path of the GPU library is tested with (lists of hundreds of elements, blanks,
+    escapes and bytes beyond ASCII in the elements): every decoded value against Python's json."""
+    import random
+
+    from test_gpu_wide import pet, url
+
+    rng = random.Random(17)
+    specials = ['\\"', "\\\\", "\\u00e9", "\\ud83d\\ude00", "é", "€", "😀", "\\n\\t", "\\/"]
+    photo = lambda k: '"' + url(rng, rng.randint(0, 40)) + (rng.choice(specials) if k % 3 == 0 else "") + '"'
+    tag = lambda k: '{"id":%d,"name":"%s%s"}' % (k, url(rng, 5), rng.choice(specials) if k % 2 else "")
+    lines = [pet(rng, n, m, blanks=b) for n, m, b in [(0, 0, False), (300, 0, False), (0, 200, True), (700, 300, True), (64, 64, False)]]
+    lines += [pet(rng, 150, 80, photo=photo, tag=tag, blanks=bool(j & 1)) for j in range(6)]
+    text = as_u8(("\n".join(lines) + "\n").encode())
+    parsed = oracle.parse(1, text)
+    assert parsed.n_errors == 0
+    got = records(parsed.as_dict(), 1)
+    assert len(got) == len(lines)
+    for line, rec in zip(lines, got):
+        assert rec == _strip_nulls(json.loads(line))
+
+
 @pytest.mark.parametrize("schema", [1, 2, 3])
-@pytest.mark.parametrize("flags", [0, abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE | abi.PJ_GEN_SPARSE])
+@pytest.mark.parametrize("flags", [0, abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE | abi.PJ_GEN_SPARSE, abi.PJ_GEN_ZIPF_LISTS | abi.PJ_GEN_ESCAPES | abi.PJ_GEN_WHITESPACE])
 def test_decoded_values_equal_python_json(oracle, native, schema, flags):
     text = pj.gen_text(schema, 99, 0, 500, flags)
     got = records(oracle.parse(schema, text).as_dict(), schema)
