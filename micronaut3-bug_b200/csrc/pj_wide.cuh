@@ -34,10 +34,8 @@ namespace pj {
 static constexpr uint32_t WIDE_NONE = 0xFFFFFFFFu;
 static constexpr uint32_t WIDE_STEP = 1024; /* bytes a warp classifies per step */
 
-#if defined(__CUDACC__)
-
 /* bytes escaped by an odd run of backslashes (32 bytes; carry_in: the first byte is escaped) */
-__device__ __forceinline__ uint32_t wide_escaped(uint32_t bs, uint32_t carry_in) {
+PJ_HD uint32_t wide_escaped(uint32_t bs, uint32_t carry_in) {
   const uint32_t even = 0x55555555u;
   bs &= ~carry_in;
   const uint32_t follows = (bs << 1) | carry_in;
@@ -46,11 +44,46 @@ __device__ __forceinline__ uint32_t wide_escaped(uint32_t bs, uint32_t carry_in)
   const uint32_t invert = sum << 1;
   return (even ^ invert) & follows;
 }
-__device__ __forceinline__ uint32_t wide_prefix_xor(uint32_t x) {
+PJ_HD uint32_t wide_prefix_xor(uint32_t x) {
   x ^= x << 1; x ^= x << 2; x ^= x << 4; x ^= x << 8; x ^= x << 16;
   return x;
 }
-__device__ __forceinline__ uint32_t wide_low_mask(int64_t n) { return n <= 0 ? 0u : (n >= 32 ? 0xFFFFFFFFu : ((1u << (uint32_t)n) - 1u)); }
+PJ_HD uint32_t wide_low_mask(int64_t n) { return n <= 0 ? 0u : (n >= 32 ? 0xFFFFFFFFu : ((1u << (uint32_t)n) - 1u)); }
+/* bit 7 of every byte of w that equals c / is below 0x20 */
+PJ_HD uint64_t wide_flags_eq(uint64_t w, uint32_t c) {
+  const uint64_t x = w ^ (0x0101010101010101ull * c);
+  return ~((((x & 0x7F7F7F7F7F7F7F7Full) + 0x7F7F7F7F7F7F7F7Full) | x)) & 0x8080808080808080ull;
+}
+PJ_HD uint64_t wide_flags_ctrl(uint64_t w) {
+  const uint64_t x = w & 0xE0E0E0E0E0E0E0E0ull;
+  return ~((((x & 0x7F7F7F7F7F7F7F7Full) + 0x7F7F7F7F7F7F7F7Full) | x)) & 0x8080808080808080ull;
+}
+PJ_HD uint32_t wide_movemask(uint64_t flags) { return (uint32_t)(((flags >> 7) * 0x0102040810204080ull) >> 56); }
+
+/* parity of the run of backslashes that ends a 32-byte block (B: its backslash mask, not all ones): the carry into the
+ * block behind it. Independent of the carry INTO the block, because the run does not span it. */
+PJ_HD uint32_t wide_carry_out(uint32_t B) {
+  uint32_t n = 0;
+  while (n < 32 && ((B >> (31 - n)) & 1u)) ++n; /* leading ones */
+  return n & 1u;
+}
+/* The masks of one lane's 32 bytes p[0..32) (valid: which of them belong to the list): backslashes, quotes, `{`, bytes
+ * that are control characters or not ASCII. */
+PJ_HD void wide_block_masks(const uint8_t* p, uint32_t valid, uint32_t* B, uint32_t* Q, uint32_t* C, uint32_t* X) {
+  uint32_t b = 0, q = 0, c = 0, x = 0;
+  for (int h = 0; h < 4; ++h) {
+    uint64_t w = 0;
+    for (int k = 0; k < 8; ++k) w |= (uint64_t)p[8 * h + k] << (8 * k);
+    b |= wide_movemask(wide_flags_eq(w, '\\')) << (8 * h);
+    q |= wide_movemask(wide_flags_eq(w, '"')) << (8 * h);
+    c |= wide_movemask(wide_flags_eq(w, '{')) << (8 * h);
+    x |= wide_movemask(wide_flags_ctrl(w) | (w & 0x8080808080808080ull)) << (8 * h);
+  }
+  *B = b & valid; *Q = q & valid; *C = c & valid; *X = x & valid;
+}
+
+#if defined(__CUDACC__)
+
 __device__ __forceinline__ uint32_t wide_min(uint32_t x) {
 #pragma unroll
   for (int d = 16; d; d >>= 1) { const uint32_t y = __shfl_xor_sync(0xFFFFFFFFu, x, d); x = y < x ? y : x; }
@@ -67,17 +100,6 @@ __device__ __forceinline__ uint32_t wide_excl(uint32_t x, uint32_t lane) {
   for (int d = 1; d < 32; d <<= 1) { const uint32_t y = __shfl_up_sync(0xFFFFFFFFu, inc, d); if ((int)lane >= d) inc += y; }
   return inc - x;
 }
-
-/* bit 7 of every byte of w that equals c / is below 0x20 */
-__device__ __forceinline__ uint64_t wide_flags_eq(uint64_t w, uint32_t c) {
-  const uint64_t x = w ^ (0x0101010101010101ull * c);
-  return ~((((x & 0x7F7F7F7F7F7F7F7Full) + 0x7F7F7F7F7F7F7F7Full) | x)) & 0x8080808080808080ull;
-}
-__device__ __forceinline__ uint64_t wide_flags_ctrl(uint64_t w) {
-  const uint64_t x = w & 0xE0E0E0E0E0E0E0E0ull;
-  return ~((((x & 0x7F7F7F7F7F7F7F7Full) + 0x7F7F7F7F7F7F7F7Full) | x)) & 0x8080808080808080ull;
-}
-__device__ __forceinline__ uint32_t wide_movemask(uint64_t flags) { return (uint32_t)(((flags >> 7) * 0x0102040810204080ull) >> 56); }
 
 /* The separator behind an element: blanks, then `,` blanks (*nxt = where the next element has to start) or `]`
  * (*endx = the offset behind it). False for anything else. */

@@ -433,3 +433,34 @@ extern "C" int emu_stream_index(const uint8_t* in, uint64_t len, uint64_t slack,
   *n_out = n;
   return 0;
 }
+
+/* ---- the mask algebra of the long-record path (pj_wide.cuh), lane after lane ---------------------------------------
+ * What a warp does side by side is done here one 32-byte block after the other with the same formulas: backslash /
+ * quote masks, escaped bytes with the carry from the block before, string interiors by prefix XOR with the running
+ * parity. Per byte: quotes_out = it is an unescaped quote, instr_out = it lies in a string (from the opening quote up
+ * to, not including, the closing one), special_out = control character or beyond ASCII. Returns 1 when a block
+ * consists of backslashes only (the case the device code refuses). */
+#include "pj_wide.cuh"
+extern "C" int emu_wide_masks(const uint8_t* buf, uint64_t n, uint8_t* quotes_out, uint8_t* instr_out, uint8_t* special_out) {
+  using namespace pj;
+  uint32_t esc_c = 0, str_c = 0;
+  for (uint64_t off = 0; off < n; off += 32) {
+    uint8_t blk[32];
+    for (uint32_t k = 0; k < 32; ++k) blk[k] = off + k < n ? buf[off + k] : 0;
+    const uint32_t valid = wide_low_mask((int64_t)(n - off));
+    uint32_t B, Q, C, X;
+    wide_block_masks(blk, valid, &B, &Q, &C, &X);
+    if (B == 0xFFFFFFFFu) return 1;
+    const uint32_t cout = wide_carry_out(B);
+    const uint32_t Qu = Q & ~wide_escaped(B, esc_c);
+    const uint32_t instr = wide_prefix_xor(Qu) ^ (str_c ? 0xFFFFFFFFu : 0u);
+    for (uint32_t k = 0; k < 32 && off + k < n; ++k) {
+      quotes_out[off + k] = (Qu >> k) & 1u;
+      instr_out[off + k] = (instr >> k) & 1u;
+      special_out[off + k] = (X >> k) & 1u;
+    }
+    esc_c = cout;
+    str_c ^= (uint32_t)__builtin_popcount(Qu) & 1u;
+  }
+  return 0;
+}

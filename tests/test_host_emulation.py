@@ -326,6 +326,46 @@ def test_option_switches_on_mutated_text(emu, oracle, opts):
     emu.emu_set_options(u32(0))
 
 
+def test_mask_algebra_of_the_long_record_path(emu):
+    """pj_wide.cuh finds the elements of long lists from 32-byte masks: escaped bytes (odd runs of backslashes, carried
+    from block to block), unescaped quotes, string interiors by prefix XOR. The same formulas, block after block on
+    the host, against a byte-at-a-time state machine: random text rich in backslashes and quotes, runs of every
+    length across the block edges."""
+    rng = random.Random(23)
+
+    def reference(b):
+        quotes, instr, special = np.zeros(len(b), np.uint8), np.zeros(len(b), np.uint8), np.zeros(len(b), np.uint8)
+        escaped, inside = False, False
+        for k, x in enumerate(b):
+            is_q = x == 0x22 and not escaped
+            if is_q:
+                inside = not inside
+            quotes[k], instr[k] = is_q, inside
+            special[k] = x < 0x20 or x >= 0x80
+            escaped = (x == 0x5C) and not escaped
+        return quotes, instr, special
+
+    cases = []
+    for run in range(0, 70):
+        for lead in (0, 1, 29, 30, 31, 32, 33):
+            cases.append(b"a" * lead + b"\\" * run + b'"x"' + b"b" * 5 + b'"\\""')
+    alphabet = [b"\\", b'"', b"a", b",", b" ", b"\x01", b"\xc3\xa9", b"{", b"}"]
+    for _ in range(300):
+        cases.append(b"".join(rng.choice(alphabet) for _ in range(rng.randint(1, 300))))
+    checked = 0
+    for b in cases:
+        buf = as_u8(b)
+        q, s_, x = np.zeros(buf.size, np.uint8), np.zeros(buf.size, np.uint8), np.zeros(buf.size, np.uint8)
+        refused = emu.emu_wide_masks(C.c_void_p(buf.ctypes.data), u64(buf.size), C.c_void_p(q.ctypes.data), C.c_void_p(s_.ctypes.data), C.c_void_p(x.ctypes.data))
+        if refused:  # a block of nothing but backslashes
+            assert any(bytes(buf[k:k + 32]) == b"\\" * 32 for k in range(0, buf.size, 32))
+            continue
+        rq, rs, rx = reference(bytes(buf))
+        assert np.array_equal(q, rq) and np.array_equal(s_, rs) and np.array_equal(x, rx), b
+        checked += 1
+    assert checked > 500
+
+
 def test_device_code_under_sanitizers():
     """The device-side parsers, line index and writers, compiled for the host with AddressSanitizer and
     UndefinedBehaviorSanitizer, run a slice of the tests above in a child process: an out-of-bounds read of a window,
@@ -334,7 +374,7 @@ def test_device_code_under_sanitizers():
     if not os.path.isabs(asan) or not os.path.exists(asan):
         pytest.skip("no libasan beside this gcc")
     env = dict(os.environ, PJ_EMU_SANITIZE="1", LD_PRELOAD=asan, ASAN_OPTIONS="detect_leaks=0:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1")
-    pick = "stream_line_index or lockstep_tokeniser_edges or common_failures or (mutated_text and 1) or tiny_records_and_long_lines or integer_text or array_framing or option_switches_known"
+    pick = "mask_algebra or stream_line_index or lockstep_tokeniser_edges or common_failures or (mutated_text and 1) or tiny_records_and_long_lines or integer_text or array_framing or option_switches_known"
     r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-p", "no:cacheprovider", os.path.abspath(__file__), "-k", pick],
                        env=env, capture_output=True, text=True, cwd=HERE, timeout=1500)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
