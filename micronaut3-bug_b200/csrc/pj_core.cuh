@@ -27,6 +27,15 @@
 #define PJ_HD_NOINLINE
 #endif
 
+/* PJ_COLD: functions of the fall-back paths (the word-at-a-time tokeniser and its emitter, the exact parser). With
+ * -DPJ_COLD_OUTLINE they are compiled once and called instead of being expanded at every place that can reach them:
+ * the kernels' machine code shrinks several times over. Off by default until it has been measured on the GPU. */
+#if defined(PJ_COLD_OUTLINE)
+#define PJ_COLD PJ_HD_NOINLINE
+#else
+#define PJ_COLD PJ_HD
+#endif
+
 namespace pj {
 
 struct Rd {
@@ -606,7 +615,7 @@ struct NoListHook {
 };
 
 template <bool W, class LH = NoListHook>
-PJ_HD uint32_t parse_record(const Schema& S, const Rd& r, PS& s, uint32_t schema, Out<W>& o, uint64_t rec_index) {
+PJ_COLD uint32_t parse_record(const Schema& S, const Rd& r, PS& s, uint32_t schema, Out<W>& o, uint64_t rec_index) {
   for (uint32_t i = 0; i < NSLOT; ++i) o.cnt[i] = 0;
   uint32_t type = schema == PJ_SCHEMA_MIXED ? PJ_TYPE_NONE : schema;
   const ObjDesc* O = type == PJ_TYPE_PET ? &S.obj[OBJ_PET] : (type == PJ_TYPE_ORDER ? &S.obj[OBJ_ORDER] : &S.obj[OBJ_USER]);

@@ -227,7 +227,7 @@ PJ_HD_NOINLINE uint64_t fast_string_tail(const uint8_t* ws, uint32_t q, uint32_t
  * backslash) are finished here, 8 bytes a step; the rest goes through fast_string_tail(). Refuses what it does not
  * accept, but for the one failure it reports itself: the record ending inside the string. */
 template <bool TAPE_LIMITS>
-PJ_HD bool fast_string_t(const Win& w, FastState& f, uint32_t* pos, uint32_t* len, uint32_t* esc) {
+PJ_COLD bool fast_string_t(const Win& w, FastState& f, uint32_t* pos, uint32_t* len, uint32_t* esc) {
   uint32_t q = f.p + 1;
   for (;;) {
     const uint64_t m = swar_str_special(wpeek8(w, q));
@@ -258,7 +258,7 @@ PJ_HD bool fast_string_t(const Win& w, FastState& f, uint32_t* pos, uint32_t* le
 PJ_HD bool fast_string(const Win& w, FastState& f, uint32_t* pos, uint32_t* len, uint32_t* esc) { return fast_string_t<true>(w, f, pos, len, esc); }
 
 /* A plain short string (key or enum literal, <= 14 bytes) at f.p, packed like the model tables. */
-PJ_HD bool fast_short(const Win& w, FastState& f, uint32_t* len, uint64_t* lo, uint64_t* hi) {
+PJ_COLD bool fast_short(const Win& w, FastState& f, uint32_t* len, uint64_t* lo, uint64_t* hi) {
   const uint64_t a = wpeek8(w, f.p + 1);
   const uint64_t ma = swar_str_special(a);
   uint32_t n;
@@ -279,7 +279,7 @@ PJ_HD bool fast_short(const Win& w, FastState& f, uint32_t* len, uint64_t* lo, u
 }
 
 /* An integer at f.p: -?(0|[1-9][0-9]{0,18}) not followed by '.', 'e', 'E'. */
-PJ_HD bool fast_int(const Win& w, FastState& f, bool is64, int64_t* out) {
+PJ_COLD bool fast_int(const Win& w, FastState& f, bool is64, int64_t* out) {
   uint32_t p = f.p;
   const bool neg = wbyte(w, p) == '-';
   if (neg) p++;
@@ -314,7 +314,7 @@ PJ_HD bool fast_int(const Win& w, FastState& f, bool is64, int64_t* out) {
 /* RFC 3339 date-time in the n bytes at window offset pos (plain ASCII, no escapes), decoded exactly as
  * parse_datetime() of pj_core.cuh decodes it; false for anything that function would reject. The fixed
  * part `YYYY-MM-DDThh:mm:ss` is checked as two 8-byte words and one 4-byte word. */
-PJ_HD bool fast_datetime(const Win& w, uint32_t pos, uint32_t n, int64_t* epoch, int32_t* nanos, int32_t* off) {
+PJ_COLD bool fast_datetime(const Win& w, uint32_t pos, uint32_t n, int64_t* epoch, int32_t* nanos, int32_t* off) {
   if (n < 20 || n > 35) return false;
   const uint64_t a = wpeek8(w, pos), b = wpeek8(w, pos + 8);
   const uint32_t c = wpeek4(w, pos + 16);
@@ -474,7 +474,7 @@ constexpr uint32_t string_fields() {
 }
 enum { TAPE_MIN_CAP = 8 }; /* the largest unit pushed between two drain points is well below this */
 template <int OBJ, int I = 0>
-PJ_HD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32_t k, uint32_t word, const uint32_t* base, uint32_t* cur);
+PJ_COLD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32_t k, uint32_t word, const uint32_t* base, uint32_t* cur);
 /* replays what the tape holds into the columns and empties it (a call, not inlined: it is met at many places) */
 template <int OBJ>
 PJ_HD_NOINLINE void tape_drain(const Win w, const Tape t, DrainState* d) { /* by value: the caller's tape stays in registers */
@@ -488,7 +488,7 @@ PJ_HD void tape_room(const Win& w, S& s, uint32_t need) {
 }
 
 /* n bytes from window offset pos to dst (global memory): bytes up to 4-byte alignment of dst, then words */
-PJ_HD void copy_win(uint8_t* dst, const Win& w, uint32_t pos, uint32_t n) {
+PJ_COLD void copy_win(uint8_t* dst, const Win& w, uint32_t pos, uint32_t n) {
   while (n && (reinterpret_cast<uintptr_t>(dst) & 3u)) { *dst++ = (uint8_t)wbyte(w, pos++); n--; }
   while (n >= 4) { *reinterpret_cast<uint32_t*>(dst) = wpeek4(w, pos); dst += 4; pos += 4; n -= 4; }
   while (n) { *dst++ = (uint8_t)wbyte(w, pos++); n--; }
@@ -546,7 +546,7 @@ PJ_HD bool fast_null(const Win& w, FastState& f) {
 }
 /* Value of scalar property I of OBJ at f.p (kinds I64, I32, BOOL, STR, ENUM, DATETIME), or null. */
 template <int OBJ, int I, class S>
-PJ_HD bool fast_scalar(const Win& w, FastState& f, S& s, FVals& v) {
+PJ_COLD bool fast_scalar(const Win& w, FastState& f, S& s, FVals& v) {
   constexpr uint32_t kind = FK<OBJ, I>::kind, slot = FK<OBJ, I>::cnt;
   if (v.present & (1u << I)) return false; /* repeated key */
   const uint32_t x = wbyte(w, f.p);
@@ -603,7 +603,7 @@ PJ_HD bool fast_colon(const Win& w, FastState& f) {
 }
 /* key at f.p -> property index of OBJ, positioned at the value; -1: refuse */
 template <int OBJ>
-PJ_HD int fast_key(const Win& w, FastState& f) {
+PJ_COLD int fast_key(const Win& w, FastState& f) {
   if (wbyte(w, f.p) != '"') return -1;
   uint32_t len; uint64_t lo, hi;
   if (!fast_short(w, f, &len, &lo, &hi)) return -1;
@@ -649,7 +649,7 @@ PJ_HD int flat_inorder(const Win& w, FastState& f, S& s, FVals& v, int state) {
 }
 /* Flat object at f.p == '{'. */
 template <int OBJ, class S>
-PJ_HD bool fast_flat(const Win& w, FastState& f, S& s, FVals& v) {
+PJ_COLD bool fast_flat(const Win& w, FastState& f, S& s, FVals& v) {
   v.present = 0;
   f.p++;
   if (fast_ws(w, f) == '}') { f.p++; return true; }
@@ -681,7 +681,7 @@ PJ_HD void tape_put_scalars(Tape& t, uint32_t at, const FVals& v) {
 
 /* Property I of a model root at f.p: scalars as above; an embedded object into cv; lists item by item. */
 template <int OBJ, int I, class S>
-PJ_HD bool root_value(const Win& w, FastState& f, S& s, FVals& v, FVals& cv) {
+PJ_COLD bool root_value(const Win& w, FastState& f, S& s, FVals& v, FVals& cv) {
   constexpr uint32_t kind = FK<OBJ, I>::kind, cnt = FK<OBJ, I>::cnt;
   if constexpr (kind <= K_ENUM || kind == K_DATETIME) { tape_room<OBJ>(w, s, 1); return fast_scalar<OBJ, I>(w, f, s, v); }
   else {
@@ -767,7 +767,7 @@ PJ_HD int root_inorder(const Win& w, FastState& f, S& s, FVals& v, FVals& cv, in
 /* Members of a model root. f.p is after `{ ws*`, or at the value of property `pending` (>= 0) whose key
  * was read already. Ends after the closing brace. */
 template <int OBJ, class S>
-PJ_HD bool fast_root(const Win& w, FastState& f, S& s, FVals& v, FVals& cv, int pending) {
+PJ_COLD bool fast_root(const Win& w, FastState& f, S& s, FVals& v, FVals& cv, int pending) {
   int state = 1;
   if (pending >= 0) {
     if (!root_dispatch<OBJ>(pending, w, f, s, v, cv)) return false;
@@ -881,7 +881,7 @@ PJ_HD bool fast_record_sink(const Win& w, FastState& f, uint32_t open_end, uint3
 /* Fixed-width values, string offsets and list offsets of one object at `row`. ELEM: the object is a
  * list element, whose string offsets are stored by store_elem_str_offsets. */
 template <int OBJ, bool ELEM, int I = 0>
-PJ_HD void store_vals(const DevCols* c, const FVals& v, uint64_t row, const uint32_t* base) {
+PJ_COLD void store_vals(const DevCols* c, const FVals& v, uint64_t row, const uint32_t* base) {
   if constexpr (I == 0) colp<uint8_t>(c, CObj<OBJ>::present_col)[row] = (uint8_t)v.present;
   if constexpr (I < CObj<OBJ>::N) {
     constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col, cnt = FK<OBJ, I>::cnt;
@@ -934,7 +934,7 @@ PJ_HD bool replay_flat_string(const Win& w, const DevCols* c, uint32_t word, con
  * the property it belongs to by an unrolled chain over the properties and emits it. cur[] holds, per slot,
  * the bytes (byte slots) or items (item slots) emitted so far. */
 template <int OBJ, int I>
-PJ_HD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32_t k, uint32_t word, const uint32_t* base, uint32_t* cur) {
+PJ_COLD uint32_t replay_word(const Win& w, const DevCols* c, const Tape& t, uint32_t k, uint32_t word, const uint32_t* base, uint32_t* cur) {
   if constexpr (I >= CObj<OBJ>::N) return k + 1;
   else {
     constexpr uint32_t kind = FK<OBJ, I>::kind, col = FK<OBJ, I>::col, cnt = FK<OBJ, I>::cnt;
@@ -983,7 +983,7 @@ PJ_HD void store_embedded(const DevCols* c, const FVals& v, const FVals& cv, uin
 
 /* cur[]: bytes / items of the record already emitted per slot (zeros, unless the tape was emptied on the way) */
 template <int OBJ>
-PJ_HD void emit_root(const Win& w, const DevCols* c, const FVals& v, const FVals& cv, const Tape& t, uint64_t row, const uint32_t* base, uint32_t* cur) {
+PJ_COLD void emit_root(const Win& w, const DevCols* c, const FVals& v, const FVals& cv, const Tape& t, uint64_t row, const uint32_t* base, uint32_t* cur) {
   store_vals<OBJ, false>(c, v, row, base);
   store_embedded<OBJ>(c, v, cv, row, base);
   for (uint32_t k = 0; k < t.n;) k = replay_word<OBJ>(w, c, t, k, tape_get(t, k), base, cur);
